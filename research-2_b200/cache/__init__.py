@@ -1,0 +1,3 @@
+from .manager import CacheError, CacheManager, GroupSpec, OutOfPages
+
+__all__ = ["CacheError", "CacheManager", "GroupSpec", "OutOfPages"]

@@ -1,0 +1,265 @@
+"""The scheduler seen from Python: a handle on the native one (csrc/host/scheduler.h).
+
+Exceptions carry the reference's names (kelpie-engine/kelpie_engine/sdk/engine.py:58-93):
+Full, TooLong, ExceedsKvPool, Stalled, CommitError.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from ..cache import _host
+from ..cache.manager import CacheManager, GroupSpec, group_array
+
+STATE_NAMES = {0: "free", 1: "waiting", 2: "running", 3: "finished_eos", 4: "finished_length", 5: "cancelled"}
+ENTRY_PREFILL, ENTRY_DECODE = 0, 1
+ORDERS = {"running_first": 0, "waiting_first": 1}
+MAX_STOP_TOKENS = 8
+
+
+class Full(RuntimeError):
+    """Every request slot is taken."""
+
+
+class TooLong(ValueError):
+    """prompt + max_new_tokens exceeds max_seq_len."""
+
+
+class ExceedsKvPool(ValueError):
+    """The request could never fit the cache pool, even alone."""
+
+
+class Stalled(RuntimeError):
+    """A plan scheduled nothing, preempted nobody, and work is pending."""
+
+    def __init__(self, req_id: int, n_work: int, need_pages: int, free_pages: int):
+        super().__init__(
+            f"stalled: request {req_id} needs {need_pages} pages for its next {n_work} tokens, "
+            f"{free_pages} are free and nothing else can make progress"
+        )
+        self.req_id, self.n_work, self.need_pages, self.free_pages = req_id, n_work, need_pages, free_pages
+
+
+class CommitError(RuntimeError):
+    """The tokens handed to commit do not fit the plan; nothing was applied."""
+
+
+@dataclass(frozen=True)
+class SchedulerConfig:
+    max_requests: int
+    max_seq_len: int
+    max_batch_tokens: int
+    max_batch_reqs: int
+    vocab_size: int
+    eos_token: int | None = None
+    order: str = "running_first"
+    reserve_ratio: float = 0.0
+
+
+@dataclass(frozen=True)
+class Plan:
+    """One step's entries, decode entries first (kelpie-core/src/scheduler.zig:1315-1328)."""
+
+    req: np.ndarray
+    start: np.ndarray
+    rows: np.ndarray
+    emits: np.ndarray
+    kind: np.ndarray
+    input_ids: np.ndarray
+    temperature: np.ndarray
+    top_k: np.ndarray
+    sample_pos: np.ndarray
+    key0: np.ndarray
+    key1: np.ndarray
+
+    @property
+    def n_entries(self) -> int:
+        return len(self.req)
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.input_ids)
+
+    def token_lists(self) -> list[np.ndarray]:
+        out, at = [], 0
+        for n in self.rows:
+            out.append(self.input_ids[at: at + n])
+            at += int(n)
+        return out
+
+
+@dataclass(frozen=True)
+class Poll:
+    new_tokens: list[int]
+    finished: bool
+    reason: str  # the request's state: running, waiting, finished_eos, finished_length
+
+
+@dataclass(frozen=True)
+class StepEvent:
+    step: int
+    n_entries: int
+    n_tokens: int
+    n_prefill_rows: int
+    n_decode: int
+    n_admitted: int
+    n_preempted: int
+    n_finished: int
+    n_running: int
+    n_waiting: int
+    kv_free: int
+    t_plan_ns: int
+    t_commit_ns: int
+
+
+def _copy(ptr, n: int, dtype) -> np.ndarray:
+    if n == 0:
+        return np.zeros(0, dtype=dtype)
+    return np.ctypeslib.as_array(ptr, shape=(n,)).astype(dtype, copy=True)
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, groups: list[GroupSpec]):
+        self._lib = _host.lib()
+        self.config = config
+        self.groups = list(groups)
+        if config.order not in ORDERS:
+            raise ValueError(f"order must be one of {sorted(ORDERS)}, got {config.order!r}")
+        c = _host.SchedulerConfigC(
+            config.max_requests, config.max_seq_len, config.max_batch_tokens, config.max_batch_reqs,
+            ORDERS[config.order], config.reserve_ratio,
+            -1 if config.eos_token is None else config.eos_token, config.vocab_size,
+        )
+        handle = self._lib.r2_sched_create(C.byref(c), group_array(self.groups), len(self.groups))
+        if not handle:
+            raise ValueError(f"scheduler: {_host.last_error()}")
+        self._h = C.c_void_p(handle)
+        self.cache = CacheManager(self.groups, config.max_requests, config.max_seq_len, _borrowed=self)
+
+    def _cache_handle(self) -> int:
+        return self._lib.r2_sched_cache(self._h)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.r2_sched_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    # ---- requests --------------------------------------------------------------------------
+    def submit(  # noqa: PLR0913
+        self, prompt, max_new_tokens: int, temperature: float = 0.0, top_k: int = 0, seed: int = 0,
+        stop_token_ids=(),
+    ) -> int:
+        """Queue a request; it is admitted at a later plan. Checks in the reference's order
+        (kelpie-core/src/c_api.zig:774-807; kelpie_engine/sdk/engine.py:298-305)."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)
+        stops = np.ascontiguousarray(list(stop_token_ids), dtype=np.int32)
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if not math.isfinite(temperature) or temperature < 0:
+            raise ValueError(f"temperature must be finite and >= 0, got {temperature}")
+        if not 0 <= top_k <= self.config.vocab_size:
+            raise ValueError(f"top_k must be in [0, {self.config.vocab_size}], got {top_k}")
+        if len(stops) > MAX_STOP_TOKENS:
+            raise ValueError(f"at most {MAX_STOP_TOKENS} stop tokens, got {len(stops)}")
+        if max_new_tokens < 0:
+            raise ValueError(f"max_new_tokens must be >= 0, got {max_new_tokens}")
+        rid = self._lib.r2_sched_submit(
+            self._h, prompt.ctypes.data_as(_host.I32P), len(prompt), max_new_tokens, temperature, top_k,
+            seed & 0xFFFFFFFFFFFFFFFF, stops.ctypes.data_as(_host.I32P), len(stops),
+        )
+        if rid >= 0:
+            return rid
+        if rid == -1:
+            raise Full(f"all {self.config.max_requests} request slots are taken")
+        if rid == -2:
+            raise TooLong(
+                f"prompt ({len(prompt)}) + max_new_tokens ({max(1, max_new_tokens)}) exceeds max_seq_len "
+                f"({self.config.max_seq_len})"
+            )
+        if rid == -5:
+            raise ExceedsKvPool(
+                f"a request of {len(prompt)} + {max(1, max_new_tokens)} tokens needs more pages than the pool has"
+            )
+        if rid == -3:
+            raise ValueError("bad request: a prompt token lies outside the vocabulary")
+        raise ValueError(f"submit refused with status {rid}")
+
+    def cancel(self, rid: int) -> None:
+        if self._lib.r2_sched_cancel(self._h, rid) != 0:
+            raise KeyError(f"no request {rid}")
+
+    def poll(self, rid: int) -> Poll:
+        cap = self.config.max_seq_len
+        out = np.zeros(cap, dtype=np.int32)
+        finished, state = C.c_int32(0), C.c_int32(0)
+        n = self._lib.r2_sched_poll(self._h, rid, out.ctypes.data_as(_host.I32P), cap, C.byref(finished), C.byref(state))
+        if n < 0:
+            raise KeyError(f"no request {rid}")
+        return Poll([int(t) for t in out[:n]], bool(finished.value), STATE_NAMES[state.value])
+
+    def request_info(self, rid: int) -> dict:
+        vals = [C.c_int32(0) for _ in range(5)]
+        if self._lib.r2_sched_request_info(self._h, rid, *[C.byref(v) for v in vals]) != 0:
+            raise KeyError(f"no request {rid}")
+        state, n_prompt, n_tokens, n_computed, n_preempted = (v.value for v in vals)
+        return {"state": STATE_NAMES[state], "n_prompt": n_prompt, "n_tokens": n_tokens,
+                "n_computed": n_computed, "n_preempted": n_preempted}
+
+    # ---- steps -----------------------------------------------------------------------------
+    def plan(self) -> Plan:
+        """The next step's entries (possibly none). Raises Stalled when nothing can run."""
+        p = _host.PlanC()
+        status = self._lib.r2_sched_plan(self._h, C.byref(p))
+        if status != 0:
+            raise RuntimeError("plan() while the previous plan has not been committed")
+        r, t = p.n_entries, p.n_tokens
+        plan = Plan(
+            _copy(p.req, r, np.int32), _copy(p.start, r, np.int32), _copy(p.rows, r, np.int32),
+            _copy(p.emits, r, np.int32), _copy(p.kind, r, np.int32), _copy(p.input_ids, t, np.int32),
+            _copy(p.temperature, r, np.float32), _copy(p.top_k, r, np.int32), _copy(p.sample_pos, r, np.int32),
+            _copy(p.key0, r, np.uint32), _copy(p.key1, r, np.uint32),
+        )
+        stall = _host.StallC()
+        if self._lib.r2_sched_stall(self._h, C.byref(stall)):
+            self._lib.r2_sched_commit(self._h, None, 0)  # the empty plan is closed so that the caller can go on
+            raise Stalled(stall.req_id, stall.n_work, stall.need_pages, stall.free_pages)
+        return plan
+
+    def commit(self, tokens) -> None:
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        status = self._lib.r2_sched_commit(self._h, tokens.ctypes.data_as(_host.I32P), len(tokens))
+        if status == -9:
+            raise CommitError("commit without a plan")
+        if status != 0:
+            raise CommitError("the tokens do not fit the plan (wrong count or a token outside the vocabulary)")
+
+    def event(self) -> StepEvent:
+        e = _host.StepEventC()
+        self._lib.r2_sched_event(self._h, C.byref(e))
+        return StepEvent(*(getattr(e, name) for name, _ in _host.StepEventC._fields_))
+
+    def counts(self) -> tuple[int, int]:
+        a, b = C.c_int32(0), C.c_int32(0)
+        self._lib.r2_sched_counts(self._h, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def has_work(self) -> bool:
+        running, waiting = self.counts()
+        return running + waiting > 0
+
+    def set(self, **knobs) -> None:  # noqa: A003
+        """Live knobs, applied at the next plan (kelpie-core/src/scheduler.zig:36-52)."""
+        ids = {"max_batch_tokens": 0, "max_batch_reqs": 1, "order": 2, "reserve_ratio": 3}
+        for name, value in knobs.items():
+            if name not in ids:
+                raise KeyError(f"unknown knob {name!r}; known: {sorted(ids)}")
+            v = ORDERS[value] if name == "order" else value
+            if self._lib.r2_sched_set(self._h, ids[name], float(v)) != 0:
+                raise ValueError(f"{name}={value!r} is out of range")

@@ -1,0 +1,235 @@
+"""Python faces of the CUDA kernels: argument checks on the host, then one C call.
+
+Every function here launches hand-written sm_100a code from `csrc/kernels/` on the current
+CUDA stream. There is no CPU fallback and no library model or attention code: if the extension
+cannot be built or loaded, the call raises. Checks that a sanitizer would make on the device
+are made here on the host: dtypes, contiguity, shapes, and that index tensors are int32.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..csrc.build import kernel_library
+
+F32, BF16 = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_new": ACT_GELU_TANH, "gelu": ACT_GELU_ERF}
+
+_STATUS = {-1: "unsupported dtype", -2: "bad shape", -3: "bad alignment", -4: "unsupported size or option"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: refused ({_STATUS.get(status, status)})")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} must have {dim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _rows(t: torch.Tensor, name: str) -> int:
+    """Row stride of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with contiguous rows, got shape {tuple(t.shape)} stride {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+_libs: dict[str, C.CDLL] = {}
+
+
+def _lib(source: str) -> C.CDLL:
+    lib = _libs.get(source)
+    if lib is None:
+        lib = kernel_library(source)
+        _libs[source] = lib
+    return lib
+
+
+def build_all() -> None:
+    """Compile every kernel library (what `__graft_entry__.build()` calls)."""
+    for source in ("rowwise", "gemm_simt", "attention_simt", "sampling"):
+        _lib(source)
+
+
+# ---------------------------------------------------------------------------------------------
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, positions: torch.Tensor | None = None,
+          pos_table: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] (+ pos_table[positions[t]]) as float32 [T, width]."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(table, "table", dim=2)
+    n, width = ids.shape[0], table.shape[1]
+    if not table.is_contiguous():
+        raise KernelError("table must be contiguous")
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype, 2)
+        _need(positions, "positions", torch.int32, 1)
+        if pos_table.shape[1] != width or not pos_table.is_contiguous() or positions.shape[0] != n:
+            raise KernelError("pos_table / positions do not fit the token table")
+    if out is None:
+        out = torch.empty(n, width, dtype=torch.float32, device=ids.device)
+    _need(out, "out", torch.float32, 2)
+    fn = _lib("rowwise").r2_embed
+    status = fn(_p(ids), _p(positions), _p(table), _p(pos_table), _p(out), n, width, table.shape[0],
+                0 if pos_table is None else pos_table.shape[0], dtype_code(table.dtype), _stream())
+    _check(status, "embed")
+    return out
+
+
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """LayerNorm of float32 rows; `rows` (int32) picks input rows, else all rows in order."""
+    _need(x, "x", torch.float32, 2)
+    _need(gamma, "gamma", torch.float32, 1)
+    _need(beta, "beta", torch.float32, 1)
+    if not x.is_contiguous() or gamma.shape[0] != x.shape[1] or beta.shape[0] != x.shape[1]:
+        raise KernelError(f"layer_norm: x {tuple(x.shape)} gamma {tuple(gamma.shape)} beta {tuple(beta.shape)}")
+    n = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n = rows.shape[0]
+    if out is None:
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+    status = _lib("rowwise").r2_layer_norm(_p(x), _p(rows), _p(gamma), _p(beta), _p(out), n, x.shape[1],
+                                          C.c_float(eps), dtype_code(out.dtype), _stream())
+    _check(status, "layer_norm")
+    return out
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: bool = False,
+           act: str | None = None, residual: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """act(a @ w + bias) (+ residual). `w` is [K, N], or [N, K] with w_is_nk. `a` and `w`
+    share a dtype; bias and residual are float32; a float32 residual makes a float32 result."""
+    _need(a, "a", dim=2)
+    _need(w, "w", a.dtype, 2)
+    m, k = a.shape
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    if (w.shape[1] if w_is_nk else w.shape[0]) != k:
+        raise KernelError(f"linear: a {tuple(a.shape)} does not fit w {tuple(w.shape)} (w_is_nk={w_is_nk})")
+    lda, ldw = _rows(a, "a"), _rows(w, "w")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError(f"linear: bias {tuple(bias.shape)} does not fit n={n}")
+    if out_dtype is None:
+        out_dtype = torch.float32 if residual is not None else a.dtype
+    ldr = 0
+    if residual is not None:
+        _need(residual, "residual", torch.float32, 2)
+        if tuple(residual.shape) != (m, n):
+            raise KernelError(f"linear: residual {tuple(residual.shape)} is not [{m}, {n}]")
+        ldr = _rows(residual, "residual")
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    if tuple(out.shape) != (m, n):
+        raise KernelError(f"linear: out {tuple(out.shape)} is not [{m}, {n}]")
+    if act not in ACTIVATIONS:
+        raise KernelError(f"linear: unknown activation {act!r}; known: {sorted(k for k in ACTIVATIONS if k)}")
+    status = _lib("gemm_simt").r2_gemm_simt(
+        _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
+        ACTIVATIONS[act], dtype_code(a.dtype), dtype_code(out.dtype), _stream())
+    _check(status, "linear")
+    return out
+
+
+def kv_write(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+             slot_mapping: torch.Tensor, n_kv_heads: int, head_dim: int, page_size: int, page_stride: int,
+             n_pages: int) -> None:
+    """Scatter this step's keys and values [T, n_kv_heads * head_dim] into their cache slots."""
+    _need(k_src, "k_src", dim=2)
+    _need(v_src, "v_src", k_src.dtype, 2)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    if k_cache.dtype != k_src.dtype or v_cache.dtype != k_src.dtype:
+        raise KernelError("kv_write: the cache and the new keys/values must share a dtype")
+    n = k_src.shape[0]
+    if k_src.shape[1] != n_kv_heads * head_dim or v_src.shape != k_src.shape or slot_mapping.shape[0] < n:
+        raise KernelError("kv_write: shapes do not fit")
+    stride = _rows(k_src, "k_src")
+    if _rows(v_src, "v_src") != stride:
+        raise KernelError("kv_write: k and v must share a row stride")
+    status = _lib("rowwise").r2_kv_write(_p(k_src), _p(v_src), stride, _p(k_cache), _p(v_cache), _p(slot_mapping), n,
+                                        n_kv_heads, head_dim, page_size, C.c_longlong(page_stride), n_pages,
+                                        dtype_code(k_src.dtype), _stream())
+    _check(status, "kv_write")
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int,
+                    n_pages: int, block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
+                    seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                    window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * head_dim]."""
+    _need(q, "q", dim=2)
+    for name, t in (("row_entry", row_entry), ("positions", positions), ("seq_lens", seq_lens)):
+        _need(t, name, torch.int32, 1)
+    _need(block_tables, "block_tables", torch.int32, 2)
+    if not block_tables.is_contiguous():
+        raise KernelError("block_tables must be contiguous")
+    n = q.shape[0]
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"attention: q {tuple(q.shape)} is not [T, {n_heads} * {head_dim}]")
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise KernelError("attention: q and the cache must share a dtype")
+    if head_dim % 16 != 0:
+        raise KernelError(f"attention: head sizes come in steps of 16, got {head_dim}")
+    if out is None:
+        out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
+    status = _lib("attention_simt").r2_attention_simt(
+        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
+        page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
+        n_kv_heads, head_dim, C.c_float(scale), window, n_pages, dtype_code(q.dtype), _stream())
+    _check(status, "paged_attention")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, key0: torch.Tensor,
+           key1: torch.Tensor, sample_pos: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits [R, V] -> int32 [R]."""
+    _need(logits, "logits", torch.float32, 2)
+    n, vocab = logits.shape
+    _need(temperature, "temperature", torch.float32, 1)
+    _need(top_k, "top_k", torch.int32, 1)
+    _need(sample_pos, "sample_pos", torch.int32, 1)
+    for name, t in (("key0", key0), ("key1", key1)):
+        if not t.is_cuda or t.dtype not in (torch.int32, torch.uint32) or t.dim() != 1:
+            raise KernelError(f"{name} must be a 1-D CUDA tensor of 32-bit integers")
+    if min(temperature.shape[0], top_k.shape[0], key0.shape[0], key1.shape[0], sample_pos.shape[0]) < n:
+        raise KernelError("sample: a per-row parameter is shorter than the logits")
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    status = _lib("sampling").r2_sample(_p(logits), _rows(logits, "logits"), n, vocab, _p(temperature), _p(top_k),
+                                       _p(key0), _p(key1), _p(sample_pos), _p(out), _stream())
+    _check(status, "sample")
+    return out
