@@ -35,7 +35,8 @@ class BatchLayout:
         sizes = [
             ("input_ids", self.t_cap), ("positions", self.t_cap), ("row_entry", self.t_cap),
             ("q_start", self.r_cap + 1), ("seq_lens", self.r_cap), ("state_slot", self.r_cap),
-            ("fresh", self.r_cap), ("logit_rows", self.w_cap), ("slot_mapping", g * self.t_cap),
+            ("fresh", self.r_cap), ("logit_rows", self.w_cap), ("temperature", self.w_cap), ("top_k", self.w_cap),
+            ("key0", self.w_cap), ("key1", self.w_cap), ("sample_pos", self.w_cap), ("slot_mapping", g * self.t_cap),
             ("block_tables", self.r_cap * sum(self.table_widths)),
         ]
         out, at = {}, 0
@@ -108,6 +109,21 @@ class StepBatch:
         self.n_logit_rows = len(rows)
         self.logit_rows[: len(rows)] = rows
         self.logit_rows[len(rows):] = 0
+
+    def set_sampling(self, temperature, top_k, key0, key1, sample_pos) -> None:
+        """Per logit row: temperature (> 0), top_k, the request's Philox key, and the position
+        of the token that is drawn. Rows beyond the count are greedy and inert."""
+        n = self.n_logit_rows
+        self.temperature.view(np.float32)[:n] = np.asarray(temperature, dtype=np.float32)
+        self.temperature.view(np.float32)[n:] = 1.0
+        self.top_k[:n] = np.asarray(top_k, dtype=np.int32)
+        self.top_k[n:] = 1
+        self.key0[:n] = np.asarray(key0, dtype=np.uint32).view(np.int32)
+        self.key1[:n] = np.asarray(key1, dtype=np.uint32).view(np.int32)
+        self.sample_pos[:n] = np.asarray(sample_pos, dtype=np.int32)
+        self.key0[n:] = 0
+        self.key1[n:] = 0
+        self.sample_pos[n:] = 0
 
     def last_rows(self) -> np.ndarray:
         """The last row of each entry (the reference's `last_rows`, sdk/device.py:130)."""

@@ -32,7 +32,7 @@ class Engine:
         from .step import StepFunction
 
         opts = (options or EngineOptions()).validated(model.max_seq_len)
-        step_fn = StepFunction(model, opts.block_size, opts.num_slabs, opts.max_requests)
+        step_fn = StepFunction(model, opts.block_size, opts.num_slabs, opts.max_requests, capture=bool(opts.capture))
         scheduler = Scheduler(
             SchedulerConfig(
                 max_requests=opts.max_requests, max_seq_len=opts.max_seq_len, max_batch_tokens=opts.max_batch_tokens,
@@ -95,10 +95,12 @@ class Engine:
         self._plan = None
 
     def build_batch(self, plan: Plan):
-        batch = self.step_fn.new_batch(plan.n_tokens, plan.n_entries, plan.n_entries)
+        decode_only = bool((plan.rows == 1).all())
+        batch = self.step_fn.new_batch(plan.n_tokens, plan.n_entries, plan.n_entries, decode_only=decode_only)
         batch.set_entries(plan.req, plan.start, plan.token_lists())
         self.scheduler.cache.fill(batch)
         batch.set_logit_rows(batch.last_rows())
+        batch.set_sampling(plan.temperature, plan.top_k, plan.key0, plan.key1, plan.sample_pos)
         return batch
 
     def step(self) -> StepEvent | None:
@@ -106,9 +108,8 @@ class Engine:
         plan = self.plan()
         if plan is None:
             return None
-        logits = self.step_fn(self.build_batch(plan))
-        tokens = self.sampler(logits, plan.temperature, plan.top_k, plan.key0, plan.key1, plan.sample_pos)
-        self.commit(np.asarray(tokens, dtype=np.int32))
+        tokens = self.step_fn.step_and_sample(self.build_batch(plan))
+        self.commit(tokens.cpu().numpy() if hasattr(tokens, "cpu") else np.asarray(tokens, dtype=np.int32))
         event = self.scheduler.event()
         if self.keep_events:
             self.events.append(event)

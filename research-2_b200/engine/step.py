@@ -1,11 +1,16 @@
 """The step function: one batch of (request, its next tokens) in, logits at the wanted rows out.
 
 It runs only the tokens it is given, as one batch, against the cache that earlier steps left,
-and returns float32 logits [n_logit_rows, vocab]. It owns the cache memory (the arena and the
-state tensors) and writes it in place; the cache manager and the scheduler own the indices.
-Reference shape of this seam: `Step.forward(plan) -> logits`
-(kelpie-models/kelpie_models/sdk/step.py:102-184), `to_device`
-(kelpie-models/kelpie_models/sdk/device.py:124-149).
+and returns float32 logits [n_logit_rows, vocab]; `sample` turns them into one token per row
+on the device. It owns the cache memory (the arena and the state tensors) and writes it in
+place; the cache manager and the scheduler own the indices. Reference shape of this seam:
+`Step.forward(plan) -> logits`, `Step.sample` (kelpie-models/kelpie_models/sdk/step.py:102-184),
+`to_device` (kelpie-models/kelpie_models/sdk/device.py:124-149).
+
+Decode-only batches (every entry one row) can run as a CUDA graph per batch-size bucket: the
+batch is copied into the graph's static buffer and the graph is replayed; forward pass and
+sampling are both inside it. The reference captures its decode buckets the same way and keeps
+prefill eager (kelpie-models/kelpie_models/sdk/captured.py:8-17,117-191).
 """
 
 from __future__ import annotations
@@ -15,17 +20,20 @@ import torch
 
 from ..cache.arena import KVArena, derive_groups
 from ..cache.manager import GroupSpec
+from ..kernels import ops
 from .batch import BatchLayout, StepBatch
 
 
 class StepContext:
     """What parts may read about the current step: the batch's arrays on the device (int32),
-    and the same batch on the host for decisions that shape launches."""
+    and the same batch on the host for decisions that shape launches. `counts` are the sizes
+    the kernels run at: the batch's own, or its capacities inside a CUDA graph."""
 
-    def __init__(self, host: StepBatch, dev: torch.Tensor):
+    def __init__(self, host: StepBatch, dev: torch.Tensor, counts: tuple[int, int, int] | None = None):
         self.host = host
-        self.n_tokens, self.n_entries, self.n_logit_rows = host.n_tokens, host.n_entries, host.n_logit_rows
-        t, r, w = host.n_tokens, host.n_entries, host.n_logit_rows
+        t, r, w = counts or (host.n_tokens, host.n_entries, host.n_logit_rows)
+        self.n_tokens, self.n_entries, self.n_logit_rows = t, r, w
+        self.captured = counts is not None
 
         def view(name: str, count: int) -> torch.Tensor:
             at, _ = host.section(name)
@@ -39,6 +47,11 @@ class StepContext:
         self.state_slot = view("state_slot", r)
         self.fresh = view("fresh", r)
         self.logit_rows = view("logit_rows", w)
+        self.temperature = view("temperature", w).view(torch.float32)
+        self.top_k = view("top_k", w)
+        self.key0 = view("key0", w)
+        self.key1 = view("key1", w)
+        self.sample_pos = view("sample_pos", w)
         at, _ = host.section("slot_mapping")
         self.slot_mapping = [dev[at + g * host.t_cap: at + g * host.t_cap + t] for g in range(len(host.block_tables))]
         at, _ = host.section("block_tables")
@@ -48,8 +61,50 @@ class StepContext:
             at += host.r_cap * width
 
 
+def _bucket(n: int) -> int:
+    """Powers of two up to 8, then multiples of 8."""
+    b = 1
+    while b < n and b < 8:
+        b *= 2
+    return b if n <= 8 else -(-n // 8) * 8
+
+
+class DecodeGraph:
+    """Forward pass + sampling of a decode-only batch of up to `cap` entries, as one CUDA graph."""
+
+    def __init__(self, step_fn: "StepFunction", cap: int):
+        self.cap = cap
+        self.host = StepBatch(BatchLayout(cap, cap, cap, step_fn.table_widths), pinned=True)
+        self.host.pad()
+        self.host.set_logit_rows([])
+        self.host.set_sampling([], [], [], [], [])
+        self.dev = torch.zeros(self.host.buf.shape[0], dtype=torch.int32, device=step_fn.device)
+        self.dev.copy_(self.host._pinned_tensor)
+        self.ctx = StepContext(self.host, self.dev, counts=(cap, cap, cap))
+        side = torch.cuda.Stream(device=step_fn.device)
+        side.wait_stream(torch.cuda.current_stream(step_fn.device))
+        with torch.cuda.stream(side):  # inert warm-up: every row is a pad row
+            for _ in range(2):
+                step_fn.sample(step_fn.forward(self.ctx), self.ctx)
+        torch.cuda.current_stream(step_fn.device).wait_stream(side)
+        torch.cuda.synchronize(step_fn.device)
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.logits = step_fn.forward(self.ctx)
+            self.tokens = step_fn.sample(self.logits, self.ctx)
+        self.kernels = ops.launch_count() - before
+
+    def replay(self) -> None:
+        self.dev.copy_(self.host._pinned_tensor, non_blocking=True)
+        self.host.copy_done = torch.cuda.Event()
+        self.host.copy_done.record()
+        self.graph.replay()
+        ops.count_launches(self.kernels)
+
+
 class StepFunction:
-    def __init__(self, model, page_size: int, num_pages: int, max_requests: int):
+    def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False):
         self.model = model
         self.device = model.rt.device
         self.groups, self.member_group = derive_groups(model.cache_members, page_size, num_pages)
@@ -60,20 +115,50 @@ class StepFunction:
         ]
         self.max_requests = max_requests
         self.table_widths = tuple(-(-model.max_seq_len // g.page_size) for g in self.groups)
-        self.launches = 0
+        # A mixer with state of its own folds an entry's rows on the host side of the launch, so
+        # only models whose mixers all say `capturable` may run inside a CUDA graph.
+        self.capture = capture and all(getattr(b.mixer, "capturable", False) for b in model.blocks)
+        self._graphs: dict[int, DecodeGraph] = {}
+        self._batches: dict[tuple[int, int, int], StepBatch] = {}
+        self.h2d_bytes = 0
 
     def cache_groups(self) -> list[GroupSpec]:
         return list(self.groups)
 
-    def new_batch(self, n_tokens: int, n_entries: int, n_logit_rows: int, widths=None) -> StepBatch:
-        layout = BatchLayout(n_tokens, n_entries, n_logit_rows, tuple(widths or self.table_widths))
-        return StepBatch(layout, pinned=True)
+    # ---- batches ---------------------------------------------------------------------------
+    def new_batch(self, n_tokens: int, n_entries: int, n_logit_rows: int, decode_only: bool = False) -> StepBatch:
+        """A pinned host batch with room for the given counts. Batches are kept and handed
+        out again; one is not reused before its last upload has finished."""
+        if decode_only and self.capture:
+            batch = self._graph(n_entries).host
+        else:
+            t_cap = _bucket(n_tokens) if n_tokens <= 64 else -(-n_tokens // 128) * 128
+            key = (t_cap, _bucket(max(n_entries, 1)), _bucket(max(n_logit_rows, 1)) if n_logit_rows <= 64 else t_cap)
+            batch = self._batches.get(key)
+            if batch is None:
+                batch = StepBatch(BatchLayout(key[0], key[1], max(key[2], n_logit_rows), self.table_widths), pinned=True)
+                self._batches[key] = batch
+        done = getattr(batch, "copy_done", None)
+        if done is not None:
+            done.synchronize()
+        return batch
+
+    def _graph(self, n_entries: int) -> DecodeGraph:
+        cap = _bucket(n_entries)
+        graph = self._graphs.get(cap)
+        if graph is None:
+            with torch.cuda.device(self.device):
+                graph = DecodeGraph(self, cap)
+            self._graphs[cap] = graph
+        return graph
 
     def upload(self, batch: StepBatch) -> StepContext:
         batch.pad()
         dev = torch.empty(batch.buf.shape[0], dtype=torch.int32, device=self.device)
-        src = batch._pinned_tensor if batch._pinned_tensor is not None else torch.from_numpy(batch.buf)
-        dev.copy_(src, non_blocking=True)
+        dev.copy_(batch._pinned_tensor, non_blocking=True)
+        batch.copy_done = torch.cuda.Event()
+        batch.copy_done.record()
+        self.h2d_bytes += batch.buf.nbytes
         return StepContext(batch, dev)
 
     def validate(self, batch: StepBatch) -> None:
@@ -92,15 +177,35 @@ class StepFunction:
         if t and batch.seq_lens[: batch.n_entries].max() > self.model.max_seq_len:
             raise ValueError("an entry reaches beyond max_seq_len")
 
+    # ---- running ---------------------------------------------------------------------------
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        return self.model.forward(ctx, self.arena.members, self.state_tensors)
+
+    def sample(self, logits: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return ops.sample(logits, ctx.temperature, ctx.top_k, ctx.key0, ctx.key1, ctx.sample_pos)
+
     @torch.no_grad()
     def __call__(self, batch: StepBatch) -> torch.Tensor:
+        """Logits [n_logit_rows, vocab] float32 on the device."""
         if batch.n_tokens == 0:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
         self.validate(batch)
         with torch.cuda.device(self.device):
+            return self.forward(self.upload(batch))
+
+    @torch.no_grad()
+    def step_and_sample(self, batch: StepBatch) -> torch.Tensor:
+        """One token per logit row (int32, on the device); `batch.set_sampling` has been called."""
+        self.validate(batch)
+        with torch.cuda.device(self.device):
+            graph = self._graphs.get(batch.r_cap) if self.capture else None
+            if graph is not None and batch is graph.host:
+                batch.pad()
+                graph.replay()
+                self.h2d_bytes += batch.buf.nbytes
+                return graph.tokens[: batch.n_logit_rows]
             ctx = self.upload(batch)
-            logits = self.model.forward(ctx, self.arena.members, self.state_tensors)
-        return logits[: batch.n_logit_rows]
+            return self.sample(self.forward(ctx), ctx)
 
 
 def logit_rows_of_last(batch: StepBatch) -> np.ndarray:

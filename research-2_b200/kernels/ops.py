@@ -33,8 +33,23 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this package have been launched (graph replays count their kernels)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
     if status == 0:
+        _launches += 1
         return
     if status < 0:
         raise KernelError(f"{what}: refused ({_STATUS.get(status, status)})")

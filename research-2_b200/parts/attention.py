@@ -48,6 +48,7 @@ class PagedAttention:
         return MemberSpec(self.n_kv_heads, self.head_dim, self.window)
 
     state_spec = None
+    capturable = True  # nothing here depends on the batch's contents, only on its shape
 
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
         qkv = ops.linear(h, self.w_qkv, self.b_qkv)
