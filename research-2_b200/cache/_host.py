@@ -73,7 +73,7 @@ def lib() -> C.CDLL:
         "r2_cache_can_reserve": (i32, [vp, i32, i32, i32, i32]),
         "r2_cache_slide": (i32, [vp, i32, i32]),
         "r2_cache_pages_held": (i32, [vp, i32, i32]),
-        "r2_cache_worst_pages": (i32, [vp, i32, i32, i32]),
+        "r2_cache_worst_pages": (i32, [vp, i32, i32, i32, i32]),
         "r2_cache_table": (i32, [vp, i32, i32, I32P, i32]),
         "r2_cache_fill_batch": (i32, [vp, i32, I32P, I32P, I32P, i32, i32] + [I32P] * 8),
         "r2_cache_check": (i32, [vp, C.c_char_p, i32]),

@@ -103,8 +103,8 @@ class CacheManager:
     def pages_held(self, req: int, group: int = 0) -> int:
         return self._lib.r2_cache_pages_held(self._h, req, group)
 
-    def worst_pages(self, group: int, n_total: int, max_chunk: int) -> int:
-        return self._lib.r2_cache_worst_pages(self._h, group, n_total, max_chunk)
+    def worst_pages(self, group: int, n_total: int, max_chunk: int, grain: int = 1) -> int:
+        return self._lib.r2_cache_worst_pages(self._h, group, n_total, max_chunk, grain)
 
     def table(self, req: int, group: int = 0) -> np.ndarray:
         out = np.zeros(self.table_widths[group], dtype=np.int32)

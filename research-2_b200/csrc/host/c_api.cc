@@ -82,9 +82,9 @@ int32_t r2_cache_pages_held(const void* cache, int32_t req, int32_t g) {
   if (!CCM(cache)->is_open(req) || g < 0 || g >= CCM(cache)->n_groups()) return r2::CACHE_BAD_REQUEST;
   return CCM(cache)->pages_held(req, g);
 }
-int32_t r2_cache_worst_pages(const void* cache, int32_t g, int32_t n_total, int32_t max_chunk) {
+int32_t r2_cache_worst_pages(const void* cache, int32_t g, int32_t n_total, int32_t max_chunk, int32_t grain) {
   if (g < 0 || g >= CCM(cache)->n_groups()) return r2::CACHE_BAD_ARG;
-  return CCM(cache)->worst_pages(g, n_total, max_chunk);
+  return CCM(cache)->worst_pages(g, n_total, max_chunk, grain);
 }
 int32_t r2_cache_table(const void* cache, int32_t req, int32_t g, int32_t* out, int32_t cap) {
   const CacheManager* c = CCM(cache);

@@ -117,14 +117,27 @@ int32_t CacheManager::slide(int32_t req, int32_t n_computed) {
   return CACHE_OK;
 }
 
-int32_t CacheManager::worst_pages(int32_t g, int32_t n_total, int32_t max_chunk) const {
+int32_t CacheManager::worst_pages(int32_t g, int32_t n_total, int32_t max_chunk, int32_t grain) const {
   const GroupSpec& spec = groups_[g];
   int32_t all = ceil_div(n_total, spec.page_size);
   if (spec.window <= 0) return all;
-  // Before a portion of c rows at s the group holds keys from s - window + 1; after it, up to
-  // s + c. That span touches at most ceil((window - 1 + c) / page) + 1 pages.
-  int32_t span = ceil_div(spec.window - 1 + std::max(1, max_chunk), spec.page_size) + 1;
-  return std::min(all, span);
+  // A portion of rows [s, e) needs the keys from s - window + 1 up to e - 1. Portions are
+  // either one decoded row at any s, or a piece of a history: it starts on a multiple of
+  // `grain` and ends on one unless it reaches the history's end. The most pages over all of them:
+  int32_t worst = 0;
+  max_chunk = std::max(1, max_chunk);
+  grain = std::max(1, grain);
+  for (int32_t s = 0; s < n_total; ++s) {
+    int32_t first_page = std::max(0, s - spec.window + 1) / spec.page_size;
+    int32_t e = s + 1;  // the single decoded row
+    if (s % grain == 0) {
+      e = std::min(n_total, s + max_chunk);
+      if (e < n_total) e = e / grain * grain;
+      if (e <= s) e = s + 1;
+    }
+    worst = std::max(worst, (e - 1) / spec.page_size - first_page + 1);
+  }
+  return std::min(all, worst);
 }
 
 int32_t CacheManager::fill_batch(int32_t n_entries, const int32_t* req, const int32_t* start,

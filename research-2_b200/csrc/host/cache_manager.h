@@ -76,8 +76,8 @@ class CacheManager {
   // Window groups give back the pages that no later row can read.
   int32_t slide(int32_t req, int32_t n_computed);
   // The most pages of group g that a lone request of n_total positions ever holds, when it is
-  // fed in portions of at most max_chunk rows.
-  int32_t worst_pages(int32_t g, int32_t n_total, int32_t max_chunk) const;
+  // fed in portions of at most max_chunk rows that end on multiples of `grain`.
+  int32_t worst_pages(int32_t g, int32_t n_total, int32_t max_chunk, int32_t grain) const;
 
   const int32_t* table(int32_t req, int32_t g) const { return &tables_[g][size_t(req) * widths_[g]]; }
   int32_t pages_held(int32_t req, int32_t g) const { return held_count_[g][req]; }

@@ -82,7 +82,7 @@ int32_t r2_cache_reserve(void* cache, int32_t req, int32_t n_computed, int32_t n
 int32_t r2_cache_can_reserve(const void* cache, int32_t req, int32_t n_computed, int32_t n_total, int32_t spare);
 int32_t r2_cache_slide(void* cache, int32_t req, int32_t n_computed);
 int32_t r2_cache_pages_held(const void* cache, int32_t req, int32_t group);
-int32_t r2_cache_worst_pages(const void* cache, int32_t group, int32_t n_total, int32_t max_chunk);
+int32_t r2_cache_worst_pages(const void* cache, int32_t group, int32_t n_total, int32_t max_chunk, int32_t grain);
 int32_t r2_cache_table(const void* cache, int32_t req, int32_t group, int32_t* out, int32_t cap);
 int32_t r2_cache_fill_batch(const void* cache, int32_t n_entries, const int32_t* req, const int32_t* start,
                             const int32_t* rows, int32_t t_stride, int32_t r_stride, int32_t* positions, int32_t* row_entry,

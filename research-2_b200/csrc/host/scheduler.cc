@@ -43,7 +43,7 @@ int32_t Scheduler::submit(const int32_t* prompt, int32_t n, int32_t max_new, flo
   const int32_t n_new = std::max(1, max_new);  // max_new_tokens 0 still yields one token
   if (int64_t(n) + n_new > cfg_.max_seq_len) return SCHED_TOO_LONG;
   for (int32_t g = 0; g < cache_.n_groups(); ++g) {
-    if (cache_.worst_pages(g, n + n_new - 1, cfg_.max_batch_tokens) > cache_.group(g).num_pages) {
+    if (cache_.worst_pages(g, n + n_new - 1, cfg_.max_batch_tokens, grain()) > cache_.group(g).num_pages) {
       return SCHED_EXCEEDS_KV_POOL;
     }
   }

@@ -206,7 +206,8 @@ def uniform_for(position: int, token: int, key: tuple[int, int]) -> float:
     kernels/ops/sample.py:26-30,51 (there the first counter word is the batch row; here it is
     the position of the token being drawn, so a request's draws do not depend on its batch)."""
     c0 = philox_4x32_10((position & MASK32, 0, token, 0), key)[0]
-    return ((c0 & 0xFFFFFF) + 0.5) * (1.0 / (1 << 24))
+    low = torch.tensor(float(c0 & 0xFFFFFF), dtype=torch.float32)  # float32 arithmetic, as the reference
+    return float((low + 0.5) * (1.0 / (1 << 24)))
 
 
 def sample_token(  # noqa: PLR0913

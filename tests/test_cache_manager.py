@@ -1,0 +1,157 @@
+"""The cache manager (no GPU): no page lost, held twice or freed twice, under random orders of
+requests; the null page is never handed out; freed pages are used again in the order of their
+release; window groups give pages back as the window passes them."""
+
+from __future__ import annotations
+
+import random
+
+import numpy as np
+import pytest
+
+from research_2_b200.cache import CacheError, CacheManager, GroupSpec, OutOfPages
+from research_2_b200.engine.batch import batch_for
+
+
+def test_pages_come_in_order_and_never_the_null_page():
+    cm = CacheManager([GroupSpec(4, 0, 6)], 3, 24)
+    cm.open(0)
+    cm.reserve(0, 0, 9)
+    assert list(cm.table(0)) == [1, 2, 3, 0, 0, 0]
+    assert cm.n_free() == 3 and cm.pages_held(0) == 3
+    cm.reserve(0, 9, 12)  # still inside page 3
+    assert cm.pages_held(0) == 3
+    cm.reserve(0, 12, 13)
+    assert list(cm.table(0))[:4] == [1, 2, 3, 4]
+    assert cm.check() == ""
+
+
+def test_freed_pages_are_reused_in_the_order_of_their_release():
+    cm = CacheManager([GroupSpec(2, 0, 6)], 3, 12)
+    cm.open(0); cm.open(1)
+    cm.reserve(0, 0, 4)   # pages 1 2
+    cm.reserve(1, 0, 4)   # pages 3 4
+    cm.close(0)           # free list: 5 6 1 2
+    cm.open(2)
+    cm.reserve(2, 0, 8)
+    assert list(cm.table(2))[:4] == [5, 6, 1, 2]
+    assert cm.check() == "" and cm.n_free() == 0
+
+
+def test_all_or_nothing_when_pages_run_out():
+    cm = CacheManager([GroupSpec(4, 0, 3), GroupSpec(4, 0, 2)], 2, 16)
+    cm.open(0)
+    assert not cm.can_reserve(0, 0, 12)  # the second group has only two pages
+    with pytest.raises(OutOfPages):
+        cm.reserve(0, 0, 12)
+    assert cm.n_free(0) == 3 and cm.n_free(1) == 2 and cm.pages_held(0, 0) == 0
+    cm.reserve(0, 0, 8)
+    assert cm.can_reserve(0, 8, 8, spare_pages=0) and not cm.can_reserve(0, 8, 8, spare_pages=1)
+
+
+def test_errors_are_reported_not_fatal():
+    cm = CacheManager([GroupSpec(4, 0, 3)], 2, 8)
+    with pytest.raises(CacheError):
+        cm.close(0)  # never opened
+    cm.open(0)
+    with pytest.raises(CacheError):
+        cm.open(0)  # opened twice
+    with pytest.raises(CacheError):
+        cm.reserve(0, 0, 9)  # beyond max_seq_len
+    with pytest.raises(CacheError):
+        cm.open(5)
+    cm.close(0)
+    with pytest.raises(CacheError):
+        cm.close(0)  # a second close frees nothing twice
+    assert cm.n_free() == 3 and cm.check() == ""
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(0, 0, 3)], 2, 8)
+
+
+def test_window_group_gives_pages_back_as_the_window_passes():
+    cm = CacheManager([GroupSpec(4, 0, 16), GroupSpec(4, 6, 5)], 1, 64)
+    cm.open(0)
+    held = []
+    for start in range(0, 40, 3):
+        cm.slide(0, start)
+        cm.reserve(0, start, start + 3)
+        table = cm.table(0, 1)
+        first_key = max(0, start - 6 + 1)
+        assert all(table[i] == 0 for i in range(first_key // 4)), "a page behind the window is still held"
+        assert all(table[i] != 0 for i in range(first_key // 4, -(-(start + 3) // 4))), "a page in the window is missing"
+        held.append(cm.pages_held(0, 1))
+        assert cm.pages_held(0, 0) == -(-(start + 3) // 4)
+        assert cm.check() == ""
+    assert max(held) <= cm.worst_pages(1, 64, 3) <= 5
+    cm.close(0)
+    assert cm.n_free(0) == 16 and cm.n_free(1) == 5
+
+
+def test_fill_batch_slots_tables_and_state():
+    cm = CacheManager([GroupSpec(4, 0, 8), GroupSpec(2, 0, 16)], 3, 16)
+    cm.open(2); cm.open(0)
+    cm.reserve(2, 0, 7)
+    cm.reserve(0, 0, 3)
+    b = batch_for(cm.table_widths, 6, 2, 2)
+    b.set_entries([2, 0], [4, 0], [[9, 9, 9], [5, 6, 7]])
+    cm.fill(b)
+    b.pad()
+    assert list(b.positions[:6]) == [4, 5, 6, 0, 1, 2]
+    assert list(b.row_entry[:6]) == [0, 0, 0, 1, 1, 1]
+    assert list(b.q_start[:3]) == [0, 3, 6] and list(b.seq_lens[:2]) == [7, 3]
+    assert list(b.fresh[:2]) == [0, 1] and list(b.state_slot[:2]) == [2, 0]
+    t2, t0 = cm.table(2, 0), cm.table(0, 0)
+    assert list(b.slot_mapping[0, :6]) == [t2[1] * 4 + 0, t2[1] * 4 + 1, t2[1] * 4 + 2, t0[0] * 4, t0[0] * 4 + 1, t0[0] * 4 + 2]
+    u2 = cm.table(2, 1)
+    assert list(b.slot_mapping[1, :3]) == [u2[2] * 2, u2[2] * 2 + 1, u2[3] * 2]
+    assert np.array_equal(b.block_tables[0][0], t2) and np.array_equal(b.block_tables[1][1], cm.table(0, 1))
+    b.check()
+    b2 = batch_for(cm.table_widths, 4, 1, 1)
+    b2.set_entries([0], [3], [[1, 2, 3, 4]])  # positions 3..6 were never reserved
+    with pytest.raises(OutOfPages):
+        cm.fill(b2)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_invariant(seed):
+    rng = random.Random(seed)
+    groups = [GroupSpec(rng.choice([2, 4, 8]), 0, rng.randint(6, 20)), GroupSpec(4, rng.choice([0, 5, 9]), rng.randint(4, 12))]
+    n_req, max_len = 5, 48
+    cm = CacheManager(groups, n_req, max_len)
+    fed = {}
+    for _ in range(600):
+        r = rng.randrange(n_req)
+        action = rng.random()
+        if r not in fed:
+            cm.open(r)
+            fed[r] = 0
+        elif action < 0.15:
+            cm.close(r)
+            del fed[r]
+        else:
+            n = rng.randint(1, 7)
+            total = min(max_len, fed[r] + n)
+            cm.slide(r, fed[r])
+            if cm.can_reserve(r, fed[r], total):
+                before = [cm.n_free(g) for g in range(2)]
+                cm.reserve(r, fed[r], total)
+                assert all(cm.n_free(g) <= before[g] for g in range(2))
+                fed[r] = total
+            else:
+                before = [cm.n_free(g) for g in range(2)]
+                with pytest.raises(OutOfPages):
+                    cm.reserve(r, fed[r], total)
+                assert [cm.n_free(g) for g in range(2)] == before, "a refused reservation took pages"
+        assert cm.check() == "", cm.check()
+        seen = [set(), set()]
+        for q in fed:  # no page in two live tables, and never the null page among the held ones
+            for g in range(2):
+                pages = [p for p in cm.table(q, g) if p != 0]
+                assert len(pages) == cm.pages_held(q, g)
+                assert not (seen[g] & set(pages))
+                seen[g] |= set(pages)
+        for g in range(2):
+            assert len(seen[g]) + cm.n_free(g) == groups[g].num_pages
+    for r in list(fed):
+        cm.close(r)
+    assert [cm.n_free(g) for g in range(2)] == [groups[0].num_pages, groups[1].num_pages]
