@@ -237,6 +237,8 @@ def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
             break
     for _ in range(warmup):
         engine.step()
+    for r in rids:
+        engine.poll(r)
     h0 = engine.step_fn.h2d_bytes
     torch.cuda.synchronize()
     t0 = time.perf_counter()

@@ -16,3 +16,8 @@ _spec = importlib.util.spec_from_file_location(
 _module = importlib.util.module_from_spec(_spec)
 sys.modules["research_2_b200"] = _module
 _spec.loader.exec_module(_module)
+
+if __name__ == "__main__":  # `python -m research_2_b200 ...` is the command line
+    from research_2_b200.cli import main as _main
+
+    sys.exit(_main())

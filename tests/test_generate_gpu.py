@@ -1,0 +1,130 @@
+"""Generation through the entry point against the plain implementation: greedy and sampled,
+alone and batched, with prompts cut into portions, and with so few pages that requests are
+preempted and recomputed. The workloads are those named for the two tiny configurations."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests.helpers import TINY_A, TINY_B, make_model_dir, random_tokens
+from tests.plain import gpt2_plain as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def wide_a(tmp_path_factory):
+    """Tiny A with a wider initialisation: clear gaps between the largest logits, so that greedy
+    tokens do not hang on the last bits."""
+    return make_model_dir(tmp_path_factory.mktemp("wide_a"), TINY_A, std=0.2)
+
+
+@pytest.fixture(scope="module")
+def wide_b(tmp_path_factory):
+    return make_model_dir(tmp_path_factory.mktemp("wide_b"), TINY_B, std=0.2)
+
+
+def plain_generate(folder, prompts, n, temperature=0.0, top_k=0, seed=0, stop=()):
+    w, cfg = plain.read_model(folder, torch.float32)
+    eos = cfg.get("eos_token_id")
+    stops = tuple(stop) + ((eos,) if eos is not None else ())
+    return [plain.generate(w, cfg, p, n, temperature, top_k, key=(seed & 0xFFFFFFFF, i), stop_token_ids=stops)
+            for i, p in enumerate(prompts)]
+
+
+def test_greedy_tiny_a_workload(wide_a):
+    """Four requests with prompts of 1, 5, 17 and 32 tokens, 16 greedy tokens each, pages of 16."""
+    import research_2_b200 as r2
+
+    prompts = [random_tokens(1 + i, n, 512) for i, n in enumerate((1, 5, 17, 32))]
+    want = plain_generate(wide_a, prompts, 16)
+    got = r2.generate(wide_a, prompts, 16, dtype="float32", block_size=16)
+    assert got == want
+    solo = [r2.generate(wide_a, [p], 16, dtype="float32", block_size=16)[0] for p in prompts]
+    assert solo == want, "a request's tokens depend on who it was batched with"
+
+
+def test_sampled_tiny_b_workload(wide_b):
+    """Six requests, prompts of 3 to 130 tokens, 24 tokens at temperature 0.8 with seed 4, the
+    largest prompt prefilled in portions of 48, pages of 8."""
+    import research_2_b200 as r2
+
+    prompts = [random_tokens(3 + i, n, 1031) for i, n in enumerate((3, 9, 40, 64, 100, 130))]
+    want = plain_generate(wide_b, prompts, 24, temperature=0.8, seed=4)
+    got = r2.generate(wide_b, prompts, 24, temperature=0.8, seed=4, dtype="float32", block_size=8, max_batch_tokens=48)
+    assert got == want
+    got_k = r2.generate(wide_b, prompts[:3], 12, temperature=1.2, top_k=5, seed=9, dtype="float32", block_size=8)
+    assert got_k == plain_generate(wide_b, prompts[:3], 12, temperature=1.2, top_k=5, seed=9)
+
+
+def test_bfloat16_generation_runs_with_and_without_graphs(wide_b):
+    """bfloat16 tokens may differ from float32 ones after a near-tie, but CUDA graphs must not
+    change them, and the first token comes from logits within the bfloat16 budget."""
+    import research_2_b200 as r2
+
+    prompts = [random_tokens(20 + i, n, 1031) for i, n in enumerate((12, 70, 33))]
+    eager = r2.generate(wide_b, prompts, 20, dtype="bfloat16", block_size=8, capture=False)
+    graphs = r2.generate(wide_b, prompts, 20, dtype="bfloat16", block_size=8, capture=True)
+    assert eager == graphs
+    assert all(len(t) == 20 for t in eager)
+
+
+def test_few_pages_preempt_and_recompute(wide_a):
+    """So few pages that running requests are preempted: the tokens stay the same."""
+    import research_2_b200 as r2
+    from research_2_b200.engine.api import generate_with
+
+    prompts = [random_tokens(40 + i, n, 512) for i, n in enumerate((30, 28, 25, 20))]
+    want = plain_generate(wide_a, prompts, 30)
+    with r2.run(wide_a, dtype="float32", block_size=4, num_slabs=34, max_requests=4, max_batch_tokens=64) as engine:
+        engine.keep_events = True
+        got = generate_with(engine, prompts, 30)
+        assert sum(e.n_preempted for e in engine.events) > 0, "the pool was meant to be too small"
+        assert engine.scheduler.cache.n_free(0) == 34 and engine.scheduler.cache.check() == ""
+    assert got == want
+
+
+def test_engine_handle_submit_wait_poll_and_stop_tokens(wide_a):
+    import research_2_b200 as r2
+
+    prompt = random_tokens(77, 9, 512)
+    want = plain_generate(wide_a, [prompt], 12)[0]
+    with r2.run(wide_a, dtype="float32") as engine:
+        rid = engine.submit(prompt, max_new_tokens=12)
+        done = engine.wait(rid, timeout_s=120.0)
+        assert done.finished and done.new_tokens == want and done.reason in ("finished_length", "finished_eos")
+        rid = engine.submit(prompt, max_new_tokens=12, stop_token_ids=[want[3]])
+        done = engine.wait(rid)
+        first = want.index(want[3])
+        assert done.new_tokens == want[: first + 1] and done.reason == "finished_eos"
+        rid = engine.submit(prompt, max_new_tokens=0)
+        assert engine.wait(rid).new_tokens == want[:1]
+        plan = None
+        rid = engine.submit(prompt, max_new_tokens=3)
+        plan = engine.plan()  # the by-hand rung
+        assert plan is not None and plan.n_entries == 1 and int(plan.rows[0]) == len(prompt)
+        batch = engine.build_batch(plan)
+        tokens = engine.step_fn.step_and_sample(batch).cpu().numpy()
+        engine.commit(tokens)
+        assert engine.poll(rid).new_tokens == want[:1]
+        engine.cancel(rid)
+        assert engine.plan() is None
+
+
+def test_command_line(wide_a):
+    prompt = random_tokens(5, 6, 512)
+    want = plain_generate(wide_a, [prompt], 5)[0]
+    proc = subprocess.run(
+        [sys.executable, "-m", "research_2_b200", "generate", "--model", str(wide_a), "--dtype", "float32",
+         "--prompt-tokens", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--max-requests", "2", "--block-size", "16"],
+        capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["prompt"] == prompt and line["tokens"] == want

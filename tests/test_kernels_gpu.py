@@ -1,0 +1,284 @@
+"""Each kernel alone against a plain float32 statement of the same op, at sizes other than the
+engine's: widths and vocabularies that are no power of two, several head sizes, grouped heads,
+a window, mixed batches over a paged cache with garbage in every slot that was never written."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests.plain import gpt2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from research_2_b200.kernels import ops as o
+
+    return o
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("width", [64, 100, 768, 1600])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm(width, out_dtype):
+    torch.manual_seed(width)
+    x = (torch.randn(37, width) * 3 + 1.5).to(DEV)
+    g, b = torch.randn(width).to(DEV), torch.randn(width).to(DEV)
+    for eps in (1e-5, 1e-2):
+        want = F.layer_norm(x, (width,), g, b, eps)
+        got = ops().layer_norm(x, g, b, eps, out_dtype)
+        assert got.dtype == out_dtype
+        torch.testing.assert_close(got.float(), want, **tol(out_dtype))
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32, device=DEV)
+    got = ops().layer_norm(x, g, b, 1e-5, out_dtype, rows=rows)
+    torch.testing.assert_close(got.float(), F.layer_norm(x[rows.long()], (width,), g, b, 1e-5), **tol(out_dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_with_and_without_positions(dtype):
+    torch.manual_seed(1)
+    table = torch.randn(1031, 96).to(dtype).to(DEV)
+    pos_table = torch.randn(77, 96).to(dtype).to(DEV)
+    ids = torch.randint(0, 1031, (50,), dtype=torch.int32, device=DEV)
+    pos = torch.randint(0, 77, (50,), dtype=torch.int32, device=DEV)
+    got = ops().embed(ids, table, pos, pos_table)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, table[ids.long()].float() + pos_table[pos.long()].float(), atol=0, rtol=0)
+    torch.testing.assert_close(ops().embed(ids, table), table[ids.long()].float(), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 96, 288), (7, 100, 1031), (64, 768, 2304), (130, 320, 96), (300, 64, 50)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("w_is_nk", [False, True])
+def test_linear(m, k, n, dtype, w_is_nk):
+    torch.manual_seed(m + k + n)
+    a = torch.randn(m, k).to(dtype).to(DEV)
+    w = (torch.randn(n, k) if w_is_nk else torch.randn(k, n)).mul(k**-0.5).to(dtype).to(DEV)
+    bias = torch.randn(n).to(DEV)
+    res = torch.randn(m, n).to(DEV)
+    base = a.float() @ (w.float().T if w_is_nk else w.float())
+    t = tol(dtype)
+    got = ops().linear(a, w, bias, w_is_nk=w_is_nk)
+    assert got.dtype == dtype
+    torch.testing.assert_close(got.float(), base + bias, **t)
+    got = ops().linear(a, w, None, w_is_nk=w_is_nk, out_dtype=torch.float32)
+    torch.testing.assert_close(got, base, **(t if dtype == torch.float32 else dict(atol=2e-4, rtol=2e-4)))
+    got = ops().linear(a, w, bias, w_is_nk=w_is_nk, act="gelu_new")
+    torch.testing.assert_close(got.float(), F.gelu(base + bias, approximate="tanh"), **t)
+    got = ops().linear(a, w, bias, w_is_nk=w_is_nk, act="gelu")
+    torch.testing.assert_close(got.float(), F.gelu(base + bias), **t)
+    got = ops().linear(a, w, bias, w_is_nk=w_is_nk, residual=res)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, base + bias + res, **(t if dtype == torch.float32 else dict(atol=2e-4, rtol=2e-4)))
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    """In float32 a row's result is the same bits alone and among other rows."""
+    torch.manual_seed(0)
+    a = torch.randn(200, 333, device=DEV)
+    w = torch.randn(333, 257, device=DEV)
+    whole = ops().linear(a, w)
+    for rows in (slice(0, 1), slice(5, 70), slice(199, 200)):
+        assert torch.equal(ops().linear(a[rows].contiguous(), w), whole[rows])
+
+
+def test_linear_refuses_what_it_cannot_do():
+    o = ops()
+    a = torch.randn(4, 8, device=DEV)
+    with pytest.raises(o.KernelError, match="does not fit"):
+        o.linear(a, torch.randn(9, 4, device=DEV))
+    with pytest.raises(o.KernelError, match="must be torch.float32, got torch.bfloat16"):
+        o.linear(a, torch.randn(8, 4, device=DEV).bfloat16())
+    with pytest.raises(o.KernelError, match="unknown activation"):
+        o.linear(a, torch.randn(8, 4, device=DEV), act="relu")
+    with pytest.raises(o.KernelError, match="CUDA tensor"):
+        o.linear(torch.randn(4, 8), torch.randn(8, 4))
+
+
+class PagedCase:
+    """Entries over a paged cache with shuffled pages; dense K and V per entry kept for the
+    plain statement. Slots never written hold `garbage`."""
+
+    def __init__(self, entries, n_heads, n_kv, hd, page, dtype, seed=0, garbage=64.0, mutate=None):
+        g = torch.Generator().manual_seed(seed)
+        self.entries, self.n_heads, self.n_kv, self.hd, self.page, self.dtype = entries, n_heads, n_kv, hd, page, dtype
+        ctx = [start + rows for start, rows in entries]
+        width = max(-(-c // page) for c in ctx)
+        n_pages = sum(-(-c // page) for c in ctx) + 1
+        order = (torch.randperm(n_pages - 1, generator=g) + 1).tolist()
+        self.k_dense = [torch.randn(c, n_kv, hd, generator=g).to(dtype) for c in ctx]
+        self.v_dense = [torch.randn(c, n_kv, hd, generator=g).to(dtype) for c in ctx]
+        self.q = [torch.randn(rows, n_heads, hd, generator=g).to(dtype) for _, rows in entries]
+        if mutate is not None:
+            mutate(self)
+        self.page_stride = 2 * n_kv * page * hd
+        pool = torch.full((n_pages, self.page_stride), garbage).to(dtype)
+        tables = torch.zeros(len(entries), width, dtype=torch.int32)
+        slots, row_entry, positions = [], [], []
+        for e, (start, rows) in enumerate(entries):
+            for i in range(-(-ctx[e] // page)):
+                tables[e, i] = order.pop()
+            for pos in range(ctx[e]):
+                p, off = int(tables[e, pos // page]), pos % page
+                if pos < start:  # history: already in the cache
+                    kv = pool[p].view(2, n_kv, page, hd)
+                    kv[0, :, off], kv[1, :, off] = self.k_dense[e][pos], self.v_dense[e][pos]
+                else:
+                    slots.append(p * page + off)
+                    row_entry.append(e)
+                    positions.append(pos)
+        self.pool = pool.to(DEV)
+        flat = self.pool.view(-1)
+        self.k_cache, self.v_cache = flat, flat[n_kv * page * hd:]
+        self.n_pages = n_pages
+        self.tables = tables.to(DEV)
+        self.slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+        self.row_entry = torch.tensor(row_entry, dtype=torch.int32, device=DEV)
+        self.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+        self.seq_lens = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+        self.q_rows = torch.cat([q.reshape(q.shape[0], -1) for q in self.q]).to(DEV)
+        self.k_new = torch.cat([self.k_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
+        self.v_new = torch.cat([self.v_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
+
+    def run(self, scale, window=0):
+        o = ops()
+        o.kv_write(self.k_new, self.v_new, self.k_cache, self.v_cache, self.slots, self.n_kv, self.hd, self.page,
+                   self.page_stride, self.n_pages)
+        return o.paged_attention(self.q_rows, self.k_cache, self.v_cache, self.page_stride, self.page, self.n_pages,
+                                 self.tables, self.row_entry, self.positions, self.seq_lens, self.n_heads, self.n_kv,
+                                 self.hd, scale, window)
+
+    def plain(self, scale, window=0):
+        outs = []
+        for e, (start, rows) in enumerate(self.entries):
+            ctx = start + rows
+            qfull = torch.zeros(ctx, self.n_heads, self.hd, dtype=torch.float64)
+            qfull[start:] = self.q[e].double()
+            out = plain.causal_attention(qfull, self.k_dense[e].double(), self.v_dense[e].double(), scale, window)
+            outs.append(out[start:])
+        return torch.cat(outs).float()
+
+
+CASES = [
+    # (entries (start, rows), heads, kv heads, head size, page size)
+    ([(0, 40)], 4, 4, 16, 16),
+    ([(0, 1), (37, 1), (5, 2), (0, 33), (60, 9)], 6, 2, 32, 8),
+    ([(100, 1), (17, 30), (0, 3)], 3, 3, 64, 16),
+    ([(250, 6), (0, 70)], 5, 1, 48, 4),
+    ([(30, 20), (299, 1)], 2, 2, 128, 32),
+    ([(10, 5)], 2, 1, 256, 16),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in CASES])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 13])
+def test_paged_attention(case, dtype, window):
+    entries, h, hkv, hd, page = case
+    pc = PagedCase(entries, h, hkv, hd, page, dtype, seed=hd + page)
+    scale = hd**-0.5 / 1.5
+    got = pc.run(scale, window).float().cpu()
+    want = pc.plain(scale, window)
+    assert torch.isfinite(got).all(), "garbage from a slot that was never written leaked in"
+    torch.testing.assert_close(got, want, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One query and one far key are scaled so that this key's score stands out: the output must
+    be (nearly) that key's value. A kernel that drops a page or a tile's edge shows here."""
+    for far in (0, 15, 16, 255, 256, 300, 511):
+        direction = torch.randn(64, generator=torch.Generator().manual_seed(far))
+        direction /= direction.norm()
+
+        def mutate(case, far=far, direction=direction):
+            case.q[0][0, :] = (direction * 30).to(dtype)
+            case.k_dense[0][far, :] = (direction * 30).to(dtype)
+
+        case = PagedCase([(511, 1)], 2, 2, 64, 16, dtype, seed=far, mutate=mutate)
+        got = case.run(1.0).float().cpu().view(2, 64)
+        want = case.v_dense[0][far].float()
+        assert torch.allclose(got, want, atol=5e-2), f"far key {far}: max diff {(got - want).abs().max():.3f}"
+
+
+def test_window_edge():
+    """With a window the key just outside must not count and the one just inside must."""
+    dtype = torch.float32
+    for window, pos in ((8, 40), (16, 16), (17, 33)):
+        inside, outside = pos - window + 1, pos - window
+        for far, visible in ((inside, True), (outside, False)):
+            if far < 0:
+                continue
+            d = torch.ones(16) / 4.0
+
+            def mutate(case, far=far, d=d):
+                case.q[0][0, 0] = d * 40
+                case.k_dense[0][far, 0] = d * 40
+
+            case = PagedCase([(pos, 1)], 1, 1, 16, 8, dtype, seed=window, mutate=mutate)
+            got = case.run(1.0, window).cpu().view(16)
+            hit = torch.allclose(got, case.v_dense[0][far, 0], atol=1e-3)
+            assert hit == visible, f"window {window}, query {pos}, key {far}: visible={visible}, hit={hit}"
+
+
+def test_pad_rows_are_zero():
+    pc = PagedCase([(3, 2)], 2, 2, 16, 4, torch.float32)
+    pc.row_entry[1] = -1
+    out = pc.run(0.25)
+    assert torch.count_nonzero(out[1]) == 0 and torch.count_nonzero(out[0]) > 0
+
+
+def test_sampling_greedy_first_index_on_ties():
+    logits = torch.full((3, 50257), -1.0)
+    logits[0, [7, 300, 50000]] = 5.0
+    logits[1, 50256] = 9.0
+    logits[2, 0] = 0.5
+    n = 3
+    tokens = ops().sample(logits.to(DEV), torch.ones(n, device=DEV), torch.ones(n, dtype=torch.int32, device=DEV),
+                          torch.zeros(n, dtype=torch.int32, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                          torch.zeros(n, dtype=torch.int32, device=DEV))
+    assert tokens.tolist() == [7, 50256, 0]
+
+
+@pytest.mark.parametrize("vocab", [512, 1031])
+def test_sampling_draws_equal_the_plain_sampler(vocab):
+    torch.manual_seed(vocab)
+    n = 24
+    logits = torch.randn(n, vocab) * 2
+    temps = torch.tensor([0.8, 1.0, 1.7, 0.3] * 6)
+    top_ks = torch.tensor([0, 5, 40, 1, vocab, 2] * 4, dtype=torch.int32)
+    key0 = torch.arange(n, dtype=torch.int64) * 7919 % (2**31)
+    key1 = torch.arange(n, dtype=torch.int64) + 11
+    pos = torch.arange(n, dtype=torch.int32) * 3 + 1
+    got = ops().sample(logits.to(DEV), temps.to(DEV), top_ks.to(DEV), key0.to(torch.int32).to(DEV),
+                       key1.to(torch.int32).to(DEV), pos.to(DEV)).tolist()
+    want = [plain.sample_token(logits[i], float(temps[i]), int(top_ks[i]), (int(key0[i]), int(key1[i])), int(pos[i]))
+            for i in range(n)]
+    assert got == want
+
+
+def test_top_k_frequencies():
+    """Draws with top_k = 3 land on the three largest logits with softmax(top3 / T) frequencies
+    (the reference's sampler check: kelpie/scripts/check_build_step.py:101-140)."""
+    vocab, n, temp = 300, 20000, 0.7
+    row = torch.randn(vocab)
+    top = torch.topk(row, 3)
+    logits = row.repeat(n, 1).to(DEV)
+    tokens = ops().sample(logits, torch.full((n,), temp, device=DEV), torch.full((n,), 3, dtype=torch.int32, device=DEV),
+                          torch.full((n,), 99, dtype=torch.int32, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                          torch.arange(n, dtype=torch.int32, device=DEV)).cpu()
+    assert set(tokens.tolist()) <= set(top.indices.tolist())
+    freq = torch.stack([(tokens == i).float().mean() for i in top.indices])
+    want = torch.softmax(top.values / temp, 0)
+    assert torch.allclose(freq, want, atol=0.02), (freq, want)
+    assert not math.isnan(float(freq.sum()))
+    _ = np  # keep numpy imported for debugging sessions
