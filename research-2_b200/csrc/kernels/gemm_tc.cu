@@ -1,0 +1,452 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) with the accumulator in
+// tensor memory, operands brought to shared memory by TMA, and a fused epilogue:
+//
+//   out[token, feature] = act(sum_k x[token, k] * w(k, feature) + bias[feature]) (+ residual)
+//
+// One CTA computes one 128 x BN tile (or one K-slice of it). Warp 0 issues the TMA loads, one
+// thread of warp 1 issues the MMAs, warps 2..5 read the accumulator back and write the result.
+// The 128-row side of the tile ("a side") is the tokens when there are many of them; for 64
+// tokens or fewer the operands swap and the 128-row side is the weight's output features, so
+// that a decode step streams the weights through full-height tiles (the tile is written back
+// transposed). With few tiles the K range is split over several CTAs; they leave float partial
+// sums in a workspace and the last one to arrive adds them in split order and runs the epilogue.
+//
+// Weights stored [K, N] (GPT-2's Conv1D layout) are the MN-major operand form, weights stored
+// [N, K] (a tied embedding as the head) the K-major form; both are loaded with 128-byte swizzle.
+// Every wait on an mbarrier is bounded: on time-out the thread records an error code in
+// `error_flag`, all roles leave their loops, tensor memory is freed and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows of the a side = UMMA M
+constexpr int BK = 64;           // one 128-byte swizzle span of bfloat16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+#define R2_ERR_TIMEOUT_FULL 1
+#define R2_ERR_TIMEOUT_EMPTY 2
+#define R2_ERR_TIMEOUT_ACC 3
+
+struct GemmParams {
+  int a_total, b_total, k_total;  // extents of the a side, the b side and K
+  int bn;                         // tile width on the b side = UMMA N (multiple of 16, <= 256)
+  int n_kb, kb_per_split, splits, stages;
+  const float* bias;
+  const float* residual;
+  int ldr;
+  void* out;
+  int ldo;
+  int out_is_bf16;
+  int act;
+  float* workspace;
+  int* counters;
+  int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Waits for the phase with the given parity to complete; false after SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (spin > 1024) __nanosleep(64);
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((addr >> 4) & 0x3FFF);
+  d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= uint64_t(1) << 46;   // descriptor version
+  d |= uint64_t(2) << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// A_MN / B_MN: the operand's tile in shared memory is MN-major (rows of 64 MN-elements, one row
+// per k) instead of K-major (rows of 64 k-elements, one row per MN index).
+// TRANSPOSED: the a side is the features and the b side the tokens.
+template <bool A_MN, bool B_MN, bool TRANSPOSED>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t a_bytes = BM * BK * 2;
+  const uint32_t b_bytes = uint32_t(p.bn) * BK * 2;
+  const uint32_t b_stride = (b_bytes + 1023u) & ~1023u;
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + size_t(p.stages) * a_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + size_t(p.stages) * b_stride);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_ready = empty + MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  int* is_last = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(p.n_kb, kb_begin + p.kb_per_split);
+  const int n_kb = kb_end - kb_begin;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < uint32_t(p.bn)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer: one thread feeds the ring of stages -------------------------------------
+    for (int i = 0; i < n_kb; ++i) {
+      int s = i % p.stages;
+      if (i >= p.stages && !mbar_wait(&empty[s], uint32_t((i / p.stages - 1) & 1))) {
+        atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
+        break;
+      }
+      int k0 = (kb_begin + i) * BK;
+      mbar_expect_tx(&full[s], a_bytes + b_bytes);
+      uint8_t* a_dst = a_tiles + size_t(s) * a_bytes;
+      uint8_t* b_dst = b_tiles + size_t(s) * b_stride;
+      if (A_MN) {  // [k rows][64 a-elements] boxes, one per 64 a-elements
+        tma_load_2d(a_dst, &map_a, a0, k0, &full[s]);
+        tma_load_2d(a_dst + BK * 128, &map_a, a0 + 64, k0, &full[s]);
+      } else {     // [a rows][64 k-elements]
+        tma_load_2d(a_dst, &map_a, k0, a0, &full[s]);
+      }
+      if (B_MN) {
+        for (int j = 0; j < p.bn; j += 64) tma_load_2d(b_dst + size_t(j / 64) * BK * 128, &map_b, b0 + j, k0, &full[s]);
+      } else {
+        tma_load_2d(b_dst, &map_b, k0, b0, &full[s]);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ------------------------------------------------------------------------
+    uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(A_MN) << 15) | (uint32_t(B_MN) << 16) |
+                     (uint32_t(p.bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; i < n_kb && ok; ++i) {
+      int s = i % p.stages;
+      if (!mbar_wait(&full[s], uint32_t((i / p.stages) & 1))) {
+        atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t a_addr = smem_u32(a_tiles + size_t(s) * a_bytes);
+      uint32_t b_addr = smem_u32(b_tiles + size_t(s) * b_stride);
+#pragma unroll
+      for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+        // K-major: 16 k-elements further along the swizzled row = 32 bytes.
+        // MN-major: 16 k-rows of 128 bytes further = 2048 bytes; 64-element chunks are 8192 bytes apart.
+        uint64_t da = A_MN ? smem_desc(a_addr + kk * (UMMA_K * 128), BK * 128, 1024) : smem_desc(a_addr + kk * 32, 16, 1024);
+        uint64_t db = B_MN ? smem_desc(b_addr + kk * (UMMA_K * 128), BK * 128, 1024) : smem_desc(b_addr + kk * 32, 16, 1024);
+        umma_bf16(tmem_base, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+    }
+    umma_commit(acc_ready);    // arrives when every MMA above has completed (also on the error path)
+  }
+
+  // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
+  if (warp >= 2) {
+    const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
+    const int a = a0 + q * 32 + lane;
+    bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
+    if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const int n_tiles = gridDim.x * gridDim.y;
+    bool finish = true;
+    if (p.splits > 1) {
+      // leave this slice's partial sums, then find out whether every other slice has left theirs
+      float* mine = p.workspace + (size_t(blockIdx.z) * n_tiles + tile) * size_t(p.bn) * BM;
+      if (ok && n_kb > 0) {
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          uint32_t r[16];
+          tmem_load16(lane_addr + uint32_t(c0), r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[size_t(c0 + j) * BM + q * 32 + lane] = __uint_as_float(r[j]);
+        }
+      } else {
+        for (int c = 0; c < p.bn; ++c) mine[size_t(c) * BM + q * 32 + lane] = 0.f;
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (threadIdx.x == 64) {
+        int arrived = atomicAdd(&p.counters[tile], 1);
+        *is_last = (arrived == p.splits - 1) ? 1 : 0;
+        if (arrived == p.splits - 1) p.counters[tile] = 0;  // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      finish = *is_last != 0;
+      if (finish) __threadfence();
+    }
+    if (finish && ok) {
+      const bool a_ok = a < p.a_total;
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        float v[16];
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int z = 0; z < p.splits; ++z) {  // split order: the sum does not depend on who came last
+            const float* part = p.workspace + (size_t(z) * n_tiles + tile) * size_t(p.bn) * BM;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&part[size_t(c0 + j) * BM + q * 32 + lane]);
+          }
+        } else {
+          uint32_t r[16];
+          tmem_load16(lane_addr + uint32_t(c0), r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        if (!a_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          int b = b0 + c0 + j;
+          if (b >= p.b_total) continue;
+          int token = TRANSPOSED ? b : a, feature = TRANSPOSED ? a : b;
+          float x = v[j];
+          if (p.bias != nullptr) x += p.bias[feature];
+          x = activate(x, p.act);
+          if (p.residual != nullptr) x += p.residual[size_t(token) * p.ldr + feature];
+          if (p.out_is_bf16) {
+            reinterpret_cast<bf16*>(p.out)[size_t(token) * p.ldo + feature] = __float2bfloat16_rn(x);
+          } else {
+            reinterpret_cast<float*>(p.out)[size_t(token) * p.ldo + feature] = x;
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// A 2-D bfloat16 tensor [outer, inner] with row stride `ld` elements; boxes of box_inner x box_outer.
+bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, bool TRANSPOSED>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  auto kernel = gemm_tc_kernel<A_MN, B_MN, TRANSPOSED>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  kernel<<<grid, THREADS, smem, stream>>>(ma, mb, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// Floats of workspace and number of counters that r2_gemm_tc may use for (m, n, k).
+extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, int* splits_out, long long* workspace_floats,
+                               int* n_counters) {
+  const bool swapped = m <= 64;
+  const int a_total = swapped ? n : m, b_total = swapped ? m : n;
+  int bn;
+  if (swapped) {
+    bn = ((b_total + 15) / 16) * 16;          // tokens, K-major: any multiple of 16
+  } else if (w_is_nk) {
+    bn = b_total >= 128 ? 128 : ((b_total + 15) / 16) * 16;
+  } else {
+    bn = b_total > 64 ? 128 : 64;             // MN-major boxes are 64 features wide
+  }
+  const int a_tiles = (a_total + BM - 1) / BM, b_tiles = (b_total + bn - 1) / bn;
+  const int n_kb = (k + BK - 1) / BK;
+  int splits = 1;
+  const int tiles = a_tiles * b_tiles;
+  if (swapped && tiles < 120 && n_kb > 1) {
+    splits = 148 / tiles;
+    if (splits > n_kb) splits = n_kb;
+    if (splits < 1) splits = 1;
+    int per = (n_kb + splits - 1) / splits;
+    splits = (n_kb + per - 1) / per;
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+  *workspace_floats = splits > 1 ? (long long)splits * tiles * bn * BM : 0;
+  *n_counters = splits > 1 ? tiles : 0;
+  return R2_OK;
+}
+
+// x [m, k] bfloat16 (row stride lda), w [k, n] or [n, k] bfloat16 (row stride ldw), bias [n] float or null,
+// residual [m, n] float or null, out [m, n] bfloat16 or float. Returns R2_UNSUPPORTED for shapes
+// whose rows are not 16-byte multiples; the caller then uses the CUDA-core kernel.
+extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_is_nk, const float* bias,
+                          const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
+                          int out_dtype, float* workspace, long long workspace_floats, int* counters, int n_counters,
+                          int* error_flag, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return R2_OK;
+  if (k < 1) return R2_BAD_SHAPE;
+  if (act < R2_ACT_NONE || act > R2_ACT_GELU_ERF) return R2_UNSUPPORTED;
+  if (out_dtype != R2_F32 && out_dtype != R2_BF16) return R2_BAD_DTYPE;
+  if (error_flag == nullptr) return R2_BAD_SHAPE;
+  if (lda % 8 != 0 || ldw % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return R2_UNSUPPORTED;
+  if (k % 8 != 0 || (!w_is_nk && n % 8 != 0)) return R2_UNSUPPORTED;
+  int bn, splits, need_counters;
+  long long need_ws;
+  r2_gemm_tc_plan(m, n, k, w_is_nk, &bn, &splits, &need_ws, &need_counters);
+  if (splits > 1 && (workspace == nullptr || counters == nullptr || workspace_floats < need_ws || n_counters < need_counters)) {
+    return R2_BAD_SHAPE;
+  }
+  const bool swapped = m <= 64;
+  GemmParams p;
+  p.a_total = swapped ? n : m;
+  p.b_total = swapped ? m : n;
+  p.k_total = k;
+  p.bn = bn;
+  p.n_kb = (k + BK - 1) / BK;
+  p.splits = splits;
+  p.kb_per_split = (p.n_kb + splits - 1) / splits;
+  p.bias = bias;
+  p.residual = residual;
+  p.ldr = ldr;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_is_bf16 = out_dtype == R2_BF16;
+  p.act = act;
+  p.workspace = workspace;
+  p.counters = counters;
+  p.error_flag = error_flag;
+  const size_t a_bytes = BM * BK * 2, b_stride = (size_t(bn) * BK * 2 + 1023) & ~size_t(1023);
+  int stages = int((227 * 1024 - 2048) / (a_bytes + b_stride));
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > p.kb_per_split) stages = p.kb_per_split;
+  if (stages < 1) stages = 1;
+  p.stages = stages;
+  const size_t smem = 1024 + size_t(stages) * (a_bytes + b_stride) + (2 * MAX_STAGES + 1) * 8 + 16;
+  dim3 grid((p.a_total + BM - 1) / BM, (p.b_total + bn - 1) / bn, splits);
+
+  CUtensorMap ma, mb;
+  bool ok;
+  if (!swapped) {
+    // a side: tokens [m, k] K-major; b side: the weight
+    ok = make_map(&ma, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, BM);
+    if (w_is_nk) {
+      ok = ok && make_map(&mb, w, uint64_t(k), uint64_t(n), uint64_t(ldw), BK, uint32_t(bn));
+      if (!ok) return R2_UNSUPPORTED;
+      return launch<false, false, false>(ma, mb, p, grid, smem, stream);
+    }
+    ok = ok && make_map(&mb, w, uint64_t(n), uint64_t(k), uint64_t(ldw), 64, BK);
+    if (!ok) return R2_UNSUPPORTED;
+    return launch<false, true, false>(ma, mb, p, grid, smem, stream);
+  }
+  // swapped: a side = the weight's features, b side = tokens [m, k] K-major
+  ok = make_map(&mb, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, uint32_t(bn));
+  if (w_is_nk) {
+    ok = ok && make_map(&ma, w, uint64_t(k), uint64_t(n), uint64_t(ldw), BK, BM);
+    if (!ok) return R2_UNSUPPORTED;
+    return launch<false, false, true>(ma, mb, p, grid, smem, stream);
+  }
+  ok = ok && make_map(&ma, w, uint64_t(n), uint64_t(k), uint64_t(ldw), 64, BK);
+  if (!ok) return R2_UNSUPPORTED;
+  return launch<true, false, true>(ma, mb, p, grid, smem, stream);
+}

@@ -9,6 +9,7 @@ are made here on the host: dtypes, contiguity, shapes, and that index tensors ar
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -93,8 +94,48 @@ def _lib(source: str) -> C.CDLL:
 
 def build_all() -> None:
     """Compile every kernel library (what `__graft_entry__.build()` calls)."""
-    for source in ("rowwise", "gemm_simt", "attention_simt", "sampling"):
+    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "sampling"):
         _lib(source)
+
+
+_tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
+
+
+def use_tensor_core_gemm(on: bool) -> bool:
+    """Switch the bfloat16 matrix products between the tcgen05 kernel and the CUDA-core one
+    (tests compare the two). Returns the previous setting."""
+    global _tensor_core_gemm
+    before, _tensor_core_gemm = _tensor_core_gemm, bool(on)
+    return before
+
+
+class _Workspace:
+    """Scratch of the split-K matrix product (partial sums, arrival counters) and the word in
+    which kernels record a bounded wait that ran out. One per device, sized once."""
+
+    FLOATS = 4 * 1024 * 1024
+    COUNTERS = 4096
+
+    def __init__(self, device):
+        self.floats = torch.empty(self.FLOATS, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
+        self.error = torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device) -> _Workspace:
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = _workspaces[device] = _Workspace(device)
+    return ws
+
+
+def device_errors(device="cuda:0") -> int:
+    """0, or the code that a kernel left when one of its bounded waits ran out (synchronises)."""
+    ws = _workspaces.get(torch.device(device))
+    return 0 if ws is None else int(ws.error[0].item())
 
 
 # ---------------------------------------------------------------------------------------------
@@ -173,6 +214,15 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         raise KernelError(f"linear: out {tuple(out.shape)} is not [{m}, {n}]")
     if act not in ACTIVATIONS:
         raise KernelError(f"linear: unknown activation {act!r}; known: {sorted(k for k in ACTIVATIONS if k)}")
+    if a.dtype == torch.bfloat16 and _tensor_core_gemm:
+        ws = _workspace(a.device)
+        status = _lib("gemm_tc").r2_gemm_tc(
+            _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
+            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.floats), C.c_longlong(ws.floats.numel()), _p(ws.counters),
+            ws.counters.numel(), _p(ws.error), _stream())
+        if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
+            _check(status, "linear (tensor cores)")
+            return out
     status = _lib("gemm_simt").r2_gemm_simt(
         _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[act], dtype_code(a.dtype), dtype_code(out.dtype), _stream())
