@@ -1,0 +1,283 @@
+// Decode attention over the paged cache, bfloat16 cache and queries, float arithmetic: rows
+// that are one new token each, the case whose time is the reading of the cache.
+//
+// A CTA takes one (row, kv head, slice of the keys). Its four warps walk the slice's 32-key
+// tiles in turn: lane = key for q.k (each lane reads its key's row in 16-byte pieces), lanes
+// over the head dimension for p.v; all query heads that share the kv head ride along on the
+// same loads. Every warp keeps an online-softmax state; the warps' states are merged in
+// shared memory. With one slice the CTA writes the output row; with several it leaves
+// (max, sum, unnormalised output) per slice in a scratch buffer and `merge` combines them.
+// The slicing depends on the row's own context length and on the number of slices only.
+//
+// Formulas: kelpie-models/kelpie_models/kernels/ops/paged_attention.py:160-240. HEAD_DIM is a
+// compile-time constant (-DHEAD_DIM=64): one library per head size, built on first use.
+#include <math.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+
+namespace {
+
+constexpr int HD = HEAD_DIM;
+constexpr int WARPS = 4;
+constexpr int VECS = HD / 8;                 // 16-byte pieces of a key row
+constexpr int DPL = (HD + 63) / 64;          // pairs of head-dimension elements per lane in p.v
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head sizes come in steps of 16 up to 256");
+
+struct DecodeParams {
+  const bf16* q; int q_row_stride;
+  bf16* out; int out_row_stride;
+  const bf16* k_cache; const bf16* v_cache;
+  long long page_stride; int page_size; int n_pages;
+  const int32_t* block_tables; int table_width;
+  const int32_t* row_entry; const int32_t* positions; const int32_t* seq_lens;
+  int n_heads, n_kv_heads;
+  float scale; int window;
+  int n_slices;
+  float* part_o;   // [rows, n_heads, n_slices, HD]
+  float* part_ml;  // [rows, n_heads, n_slices, 2]
+};
+
+template <int G>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_kernel(const DecodeParams p) {
+  __shared__ float q_s[G][HD];
+  __shared__ float red_o[WARPS][G][HD];
+  __shared__ float red_m[WARPS][G], red_l[WARPS][G];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slice = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+  const int h0 = kvh * G;
+  const int e = p.row_entry[t];
+  if (e < 0) {  // a pad row: zeros, and empty partials
+    for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+      int g = i / HD, d = i % HD;
+      if (p.n_slices == 1) {
+        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(0.f);
+      } else {
+        p.part_o[((size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice) * HD + d] = 0.f;
+      }
+    }
+    if (p.n_slices > 1 && threadIdx.x < G) {
+      float* ml = p.part_ml + ((size_t(t) * p.n_heads + h0 + threadIdx.x) * p.n_slices + slice) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+  const int pos = p.positions[t];
+  const int seq_len = p.seq_lens[e];
+  const int last = pos < seq_len - 1 ? pos : seq_len - 1;
+  const int first = p.window > 0 ? (pos - p.window + 1 > 0 ? pos - p.window + 1 : 0) : 0;
+  const int n_keys = last - first + 1;
+  // this slice's keys: equal runs of whole 32-key tiles
+  const int tiles = (n_keys + 31) / 32;
+  const int tiles_per = (tiles + p.n_slices - 1) / p.n_slices;
+  const int tile_begin = slice * tiles_per;
+  const int tile_end = min(tiles, tile_begin + tiles_per);
+  const int32_t* table = p.block_tables + size_t(e) * p.table_width;
+
+  for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+    int g = i / HD, d = i % HD;
+    q_s[g][d] = __bfloat162float(p.q[size_t(t) * p.q_row_stride + size_t(h0 + g) * HD + d]) * p.scale;
+  }
+  __syncthreads();
+
+  float m[G], l[G], acc[G][DPL][2];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i][0] = acc[g][i][1] = 0.f;
+  }
+  const size_t head_off = size_t(kvh) * p.page_size * HD;
+
+  for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS) {
+    const int j0 = first + tile * 32;
+    const int j = j0 + lane;
+    const bool valid = j <= last;
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    // the lane's own key: its page and the element offset of its row inside the layer's pages
+    long long row_off = 0;
+    if (valid) {
+      int page = table[j / p.page_size];
+      page = (page < 0 || page >= p.n_pages) ? 0 : page;
+      row_off = (long long)page * p.page_stride + (long long)head_off + (long long)(j % p.page_size) * HD;
+      const uint4* kr = reinterpret_cast<const uint4*>(p.k_cache + row_off);
+      constexpr int CH = VECS < 8 ? VECS : 8;  // 16-byte pieces in flight at a time
+#pragma unroll
+      for (int c0 = 0; c0 < VECS; c0 += CH) {
+        uint4 kv[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) kv[c] = (c0 + c < VECS) ? __ldg(kr + c0 + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          if (c0 + c >= VECS) continue;
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv[c]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float2 kf = __bfloat1622float2(k2[u]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              s[g] = fmaf(q_s[g][(c0 + c) * 8 + 2 * u], kf.x, s[g]);
+              s[g] = fmaf(q_s[g][(c0 + c) * 8 + 2 * u + 1], kf.y, s[g]);
+            }
+          }
+        }
+      }
+    }
+    float pr[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sv = valid ? s[g] : -INFINITY;
+      float m_new = fmaxf(m[g], warp_max(sv));
+      float corr = __expf(m[g] - m_new);
+      pr[g] = valid ? __expf(sv - m_new) : 0.f;
+      l[g] = l[g] * corr + warp_sum(pr[g]);
+      m[g] = m_new;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        acc[g][i][0] *= corr;
+        acc[g][i][1] *= corr;
+      }
+    }
+    const int n_valid = min(32, last - j0 + 1);
+    for (int jj = 0; jj < n_valid; ++jj) {
+      const long long off = __shfl_sync(0xffffffffu, row_off, jj);
+      const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(p.v_cache + off);
+      float2 vv[DPL];
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        int pair = lane + 32 * i;
+        vv[i] = (HD % 64 == 0 || 2 * pair < HD) ? __bfloat1622float2(vr[pair]) : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float pj = __shfl_sync(0xffffffffu, pr[g], jj);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+          acc[g][i][0] = fmaf(pj, vv[i].x, acc[g][i][0]);
+          acc[g][i][1] = fmaf(pj, vv[i].y, acc[g][i][1]);
+        }
+      }
+    }
+  }
+
+  // merge the four warps' states
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      red_m[warp][g] = m[g];
+      red_l[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      int d = 2 * (lane + 32 * i);
+      if (HD % 64 == 0 || d < HD) {
+        red_o[warp][g][d] = acc[g][i][0];
+        red_o[warp][g][d + 1] = acc[g][i][1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+    int g = i / HD, d = i % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, red_m[w][g]);
+    float o = 0.f, lsum = 0.f;
+    if (mx > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        float c = __expf(red_m[w][g] - mx);
+        o += c * red_o[w][g][d];
+        lsum += c * red_l[w][g];
+      }
+    }
+    if (p.n_slices == 1) {
+      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
+    } else {
+      size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
+      p.part_o[at * HD + d] = o;
+      if (d == 0) {
+        p.part_ml[at * 2] = mx;
+        p.part_ml[at * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+// out[t, h, :] = sum_s exp(m_s - m) o_s / sum_s exp(m_s - m) l_s, slices in order.
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                             int out_row_stride, int n_heads, int n_slices) {
+  const int t = blockIdx.y, h = blockIdx.x;
+  const size_t base = (size_t(t) * n_heads + h) * n_slices;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_slices; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float o = 0.f, l = 0.f;
+    if (mx > -INFINITY) {
+      for (int s = 0; s < n_slices; ++s) {
+        float c = __expf(part_ml[(base + s) * 2] - mx);
+        o += c * part_o[(base + s) * HD + d];
+        l += c * part_ml[(base + s) * 2 + 1];
+      }
+    }
+    out[size_t(t) * out_row_stride + size_t(h) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+}
+
+template <int G>
+int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
+  dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
+  decode_kernel<G><<<grid, WARPS * 32, 0, stream>>>(p);
+  return launch_status();
+}
+
+}  // namespace
+
+extern "C" int r2_attention_decode_head_dim(void) { return HD; }
+
+// Floats of scratch that n_slices > 1 needs: the unnormalised outputs, then (max, sum) pairs.
+extern "C" long long r2_attention_decode_scratch_floats(int n_rows, int n_heads, int n_slices) {
+  return n_slices > 1 ? (long long)n_rows * n_heads * n_slices * (HD + 2) : 0;
+}
+
+extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                                   const void* v_cache, long long page_stride, int page_size, int n_pages,
+                                   const int32_t* block_tables, int table_width, const int32_t* row_entry,
+                                   const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
+                                   int n_kv_heads, float scale, int window, int n_slices, float* scratch,
+                                   long long scratch_floats, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || n_slices < 1) return R2_BAD_SHAPE;
+  if (page_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15)) return R2_BAD_ALIGN;
+  if (n_slices > 1 && (scratch == nullptr || scratch_floats < r2_attention_decode_scratch_floats(n_rows, n_heads, n_slices))) return R2_BAD_SHAPE;
+  DecodeParams p;
+  p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
+  p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.page_stride = page_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.block_tables = block_tables; p.table_width = table_width;
+  p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
+  p.scale = scale; p.window = window; p.n_slices = n_slices;
+  p.part_o = scratch;
+  p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
+  int status;
+  switch (n_heads / n_kv_heads) {
+    case 1: status = launch<1>(p, n_rows, stream); break;
+    case 2: status = launch<2>(p, n_rows, stream); break;
+    case 4: status = launch<4>(p, n_rows, stream); break;
+    case 8: status = launch<8>(p, n_rows, stream); break;
+    default: return R2_UNSUPPORTED;
+  }
+  if (status != R2_OK || n_slices == 1) return status;
+  merge_kernel<<<dim3(n_heads, n_rows), HD >= 128 ? 128 : 64, 0, stream>>>(p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
+  return launch_status();
+}

@@ -34,6 +34,14 @@ class StepContext:
         t, r, w = counts or (host.n_tokens, host.n_entries, host.n_logit_rows)
         self.n_tokens, self.n_entries, self.n_logit_rows = t, r, w
         self.captured = counts is not None
+        # shape facts that choose kernels: inside a graph every row is an entry of its own and
+        # contexts may reach the whole table; outside, the host batch says what is there
+        if self.captured:
+            self.decode_only = True
+            self.max_context = host.max_context_bound
+        else:
+            self.decode_only = bool(r == t and r > 0)
+            self.max_context = int(host.seq_lens[:r].max()) if r else 0
 
         def view(name: str, count: int) -> torch.Tensor:
             at, _ = host.section(name)
@@ -75,6 +83,7 @@ class DecodeGraph:
     def __init__(self, step_fn: "StepFunction", cap: int):
         self.cap = cap
         self.host = StepBatch(BatchLayout(cap, cap, cap, step_fn.table_widths), pinned=True)
+        self.host.max_context_bound = step_fn.model.max_seq_len
         self.host.pad()
         self.host.set_logit_rows([])
         self.host.set_sampling([], [], [], [], [])

@@ -96,9 +96,39 @@ def build_all() -> None:
     """Compile every kernel library (what `__graft_entry__.build()` calls)."""
     for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "sampling"):
         _lib(source)
+    for head_dim in (16, 32, 64):  # the head sizes of the tiny test models and of GPT-2
+        _lib_for_head_dim("attention_decode", head_dim)
 
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
+_fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
+N_SMS = 148
+
+
+def use_fast_attention(on: bool) -> bool:
+    """Switch bfloat16 attention between the fast kernels and the general CUDA-core one."""
+    global _fast_attention
+    before, _fast_attention = _fast_attention, bool(on)
+    return before
+
+
+def decode_slices(n_rows: int, n_kv_heads: int, max_context: int) -> int:
+    """Slices of the keys per (row, kv head) in decode attention: enough CTAs for two per SM,
+    never less than 128 keys a slice."""
+    ctas = max(1, n_rows * n_kv_heads)
+    want = -(-2 * N_SMS // ctas)
+    most = max(1, max_context // 128)
+    return max(1, min(want, most, 32))
+
+
+def _lib_for_head_dim(source: str, head_dim: int) -> C.CDLL:
+    key = f"{source}:{head_dim}"
+    lib = _libs.get(key)
+    if lib is None:
+        lib = kernel_library(source, {"HEAD_DIM": head_dim})
+        lib.r2_attention_decode_scratch_floats.restype = C.c_longlong
+        _libs[key] = lib
+    return lib
 
 
 def use_tensor_core_gemm(on: bool) -> bool:
@@ -254,8 +284,11 @@ def kv_write(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int,
                     n_pages: int, block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                     seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                    window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * head_dim]."""
+                    window: int = 0, out: torch.Tensor | None = None, *, decode_only: bool = False,
+                    max_context: int = 0) -> torch.Tensor:
+    """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * head_dim].
+    `decode_only` says that every row is an entry of its own (one new token each) and
+    `max_context` bounds the rows' context lengths; both only choose the kernel and its slicing."""
     _need(q, "q", dim=2)
     for name, t in (("row_entry", row_entry), ("positions", positions), ("seq_lens", seq_lens)):
         _need(t, name, torch.int32, 1)
@@ -271,6 +304,23 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError(f"attention: head sizes come in steps of 16, got {head_dim}")
     if out is None:
         out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
+    group = n_heads // max(n_kv_heads, 1)
+    if q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
+        lib = _lib_for_head_dim("attention_decode", head_dim)
+        n_slices = decode_slices(n, n_kv_heads, max_context)
+        ws = _workspace(q.device)
+        need = lib.r2_attention_decode_scratch_floats(n, n_heads, n_slices)
+        if need > ws.floats.numel():
+            n_slices, need = 1, 0
+        status = lib.r2_attention_decode(
+            _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
+            page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens),
+            n, n_heads, n_kv_heads, C.c_float(scale), window, n_slices, _p(ws.floats), C.c_longlong(ws.floats.numel()),
+            _stream())
+        _check(status, "paged_attention (decode)")
+        if n_slices > 1:
+            count_launches(1)  # the merge kernel
+        return out
     status = _lib("attention_simt").r2_attention_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
         page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,

@@ -149,13 +149,13 @@ class PagedCase:
         self.k_new = torch.cat([self.k_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
         self.v_new = torch.cat([self.v_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
 
-    def run(self, scale, window=0):
+    def run(self, scale, window=0, **kernel_choice):
         o = ops()
         o.kv_write(self.k_new, self.v_new, self.k_cache, self.v_cache, self.slots, self.n_kv, self.hd, self.page,
                    self.page_stride, self.n_pages)
         return o.paged_attention(self.q_rows, self.k_cache, self.v_cache, self.page_stride, self.page, self.n_pages,
                                  self.tables, self.row_entry, self.positions, self.seq_lens, self.n_heads, self.n_kv,
-                                 self.hd, scale, window)
+                                 self.hd, scale, window, **kernel_choice)
 
     def plain(self, scale, window=0):
         outs = []
@@ -192,6 +192,41 @@ def test_paged_attention(case, dtype, window):
     torch.testing.assert_close(got, want, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)))
 
 
+DECODE_CASES = [
+    # (contexts before the new token, heads, kv heads, head size, page size)
+    ([0, 1, 31, 32, 33, 500], 4, 4, 64, 16),
+    ([700, 5], 8, 1, 32, 8),
+    ([129, 64, 1000, 3], 6, 3, 16, 4),
+    ([260], 4, 2, 128, 32),
+    ([90, 91], 2, 2, 48, 16),
+    ([300, 17], 8, 2, 80, 8),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in DECODE_CASES])
+@pytest.mark.parametrize("window", [0, 40])
+@pytest.mark.parametrize("sliced", [False, True])
+def test_decode_attention(case, window, sliced):
+    """The decode kernel (one new token per entry), with one slice of the keys and with several."""
+    contexts, h, hkv, hd, page = case
+    pc = PagedCase([(c, 1) for c in contexts], h, hkv, hd, page, torch.bfloat16, seed=hd + page + window)
+    scale = hd**-0.5
+    got = pc.run(scale, window, decode_only=True, max_context=4096 if sliced else 64).float().cpu()
+    want = pc.plain(scale, window)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, atol=3e-2, rtol=3e-2)
+    general = pc.run(scale, window).float().cpu()
+    torch.testing.assert_close(got, general, atol=2e-2, rtol=2e-2)
+
+
+def test_decode_slices_choice():
+    o = ops()
+    assert o.decode_slices(64, 12, 1024) == 1
+    assert o.decode_slices(8, 12, 1024) == 4
+    assert o.decode_slices(1, 12, 1024) == 8
+    assert o.decode_slices(1, 12, 100) == 1
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_among_hundreds(dtype):
     """One query and one far key are scaled so that this key's score stands out: the output must
@@ -205,9 +240,11 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
             case.k_dense[0][far, :] = (direction * 30).to(dtype)
 
         case = PagedCase([(511, 1)], 2, 2, 64, 16, dtype, seed=far, mutate=mutate)
-        got = case.run(1.0).float().cpu().view(2, 64)
         want = case.v_dense[0][far].float()
-        assert torch.allclose(got, want, atol=5e-2), f"far key {far}: max diff {(got - want).abs().max():.3f}"
+        choices = [{}] if dtype == torch.float32 else [{}, dict(decode_only=True, max_context=64), dict(decode_only=True, max_context=4096)]
+        for choice in choices:
+            got = case.run(1.0, **choice).float().cpu().view(2, 64)
+            assert torch.allclose(got, want, atol=5e-2), f"far key {far} {choice}: max diff {(got - want).abs().max():.3f}"
 
 
 def test_window_edge():
