@@ -281,3 +281,81 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   merge_kernel<<<dim3(n_heads, n_rows), HD >= 128 ? 128 : 64, 0, stream>>>(p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same computation for callers that cannot allocate device memory: the slices' partial
+// results go to a file-scope device array instead of a buffer that the caller passes in.
+// Declaration, limits and rules for the caller: attention_decode_static.h.
+#include <stdio.h>
+
+#include <mutex>
+
+#include "attention_decode_static.h"
+
+// In host code this name is only a stand-in for the device array, not its address: it must not
+// be handed to a kernel. The address comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float r2_static_scratch[R2_STATIC_SCRATCH_FLOATS];
+
+namespace {
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch[MAX_DEVICES] = {};  // the array's device address, by device ordinal
+std::mutex g_static_setup;
+thread_local char g_static_error[320] = "";
+
+// The device address of the static scratch array on the current device; looked up on the first
+// call for that device (which is why that call should come before any stream capture).
+float* static_scratch_for_current_device() {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+    snprintf(g_static_error, sizeof g_static_error, "r2_attention_decode_static: no usable current device (%s, ordinal %d)",
+             cudaGetErrorString(e), device);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_setup);
+  if (g_static_scratch[device] == nullptr) {
+    float* address = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), r2_static_scratch);
+    if (e != cudaSuccess || address == nullptr) {
+      snprintf(g_static_error, sizeof g_static_error,
+               "r2_attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_static_scratch[device] = address;
+  }
+  return g_static_scratch[device];
+}
+
+}  // namespace
+
+extern "C" const char* r2_attention_decode_static_error(void) { return g_static_error; }
+
+extern "C" int r2_attention_decode_static(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                          const void* k_cache, const void* v_cache, long long page_stride, int page_size,
+                                          int n_pages, const int32_t* block_tables, int table_width,
+                                          const int32_t* row_entry, const int32_t* positions, const int32_t* seq_lens,
+                                          int n_rows, int n_heads, int n_kv_heads, float scale, int window, int n_slices,
+                                          cudaStream_t stream) {
+  g_static_error[0] = 0;
+  if (n_rows <= 0) return R2_OK;
+  if (n_heads < 1 || n_slices < 1) return R2_BAD_SHAPE;
+  const long long need = r2_attention_decode_scratch_floats(n_rows, n_heads, n_slices);
+  if (need > (long long)R2_STATIC_SCRATCH_FLOATS) {
+    snprintf(g_static_error, sizeof g_static_error,
+             "r2_attention_decode_static: %d rows x %d heads x %d slices of head size %d need %lld floats of scratch, "
+             "the built-in array holds %d; use fewer slices or rows, or r2_attention_decode with a buffer of your own",
+             n_rows, n_heads, n_slices, HD, need, int(R2_STATIC_SCRATCH_FLOATS));
+    return R2_STATIC_SCRATCH_TOO_SMALL;
+  }
+  float* scratch = nullptr;
+  if (n_slices > 1) {
+    scratch = static_scratch_for_current_device();
+    if (scratch == nullptr) return R2_STATIC_SETUP_FAILED;
+  }
+  // Every (row, head, slice) word of the scratch that the merge reads is written by this call's
+  // own slices first (empty slices write zeros and a -inf maximum), so nothing needs clearing.
+  return r2_attention_decode(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, n_pages,
+                             block_tables, table_width, row_entry, positions, seq_lens, n_rows, n_heads, n_kv_heads,
+                             scale, window, n_slices, scratch, (long long)R2_STATIC_SCRATCH_FLOATS, stream);
+}
