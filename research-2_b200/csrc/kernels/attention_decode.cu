@@ -146,23 +146,34 @@ decode_kernel(const DecodeParams p) {
         acc[g][i][1] *= corr;
       }
     }
+    // p.v: keys in groups of eight, all eight rows' loads issued before the first is used.
+    // Lanes beyond the last key hold p = 0 and borrow lane 0's row, so every load is in bounds.
+    const long long safe_off = __shfl_sync(0xffffffffu, row_off, 0);
+    const long long my_off = valid ? row_off : safe_off;
     const int n_valid = min(32, last - j0 + 1);
-    for (int jj = 0; jj < n_valid; ++jj) {
-      const long long off = __shfl_sync(0xffffffffu, row_off, jj);
-      const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(p.v_cache + off);
-      float2 vv[DPL];
+#pragma unroll 1
+    for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
+      float2 vv[8][DPL];
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) {
-        int pair = lane + 32 * i;
-        vv[i] = (HD % 64 == 0 || 2 * pair < HD) ? __bfloat1622float2(vr[pair]) : make_float2(0.f, 0.f);
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float pj = __shfl_sync(0xffffffffu, pr[g], jj);
+      for (int u = 0; u < 8; ++u) {
+        const long long off = __shfl_sync(0xffffffffu, my_off, jj0 + u);
+        const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(p.v_cache + off);
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
-          acc[g][i][0] = fmaf(pj, vv[i].x, acc[g][i][0]);
-          acc[g][i][1] = fmaf(pj, vv[i].y, acc[g][i][1]);
+          int pair = lane + 32 * i;
+          vv[u][i] = (HD % 64 == 0 || 2 * pair < HD) ? __bfloat1622float2(vr[pair]) : make_float2(0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float pj = __shfl_sync(0xffffffffu, pr[g], jj0 + u);
+#pragma unroll
+          for (int i = 0; i < DPL; ++i) {
+            acc[g][i][0] = fmaf(pj, vv[u][i].x, acc[g][i][0]);
+            acc[g][i][1] = fmaf(pj, vv[u][i].y, acc[g][i][1]);
+          }
         }
       }
     }

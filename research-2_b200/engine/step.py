@@ -39,9 +39,12 @@ class StepContext:
         if self.captured:
             self.decode_only = True
             self.max_context = host.max_context_bound
+            self.n_attention_tiles = 0
         else:
             self.decode_only = bool(r == t and r > 0)
             self.max_context = int(host.seq_lens[:r].max()) if r else 0
+            rows = host.q_start[1: r + 1] - host.q_start[:r]
+            self.n_attention_tiles = int(((rows + 63) // 64).sum())  # 64-row tiles, entry by entry
 
         def view(name: str, count: int) -> torch.Tensor:
             at, _ = host.section(name)

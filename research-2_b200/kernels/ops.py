@@ -98,6 +98,7 @@ def build_all() -> None:
         _lib(source)
     for head_dim in (16, 32, 64):  # the head sizes of the tiny test models and of GPT-2
         _lib_for_head_dim("attention_decode", head_dim)
+        _lib_for_head_dim("attention_prefill", head_dim)
 
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
@@ -126,7 +127,8 @@ def _lib_for_head_dim(source: str, head_dim: int) -> C.CDLL:
     lib = _libs.get(key)
     if lib is None:
         lib = kernel_library(source, {"HEAD_DIM": head_dim})
-        lib.r2_attention_decode_scratch_floats.restype = C.c_longlong
+        if source == "attention_decode":
+            lib.r2_attention_decode_scratch_floats.restype = C.c_longlong
         _libs[key] = lib
     return lib
 
@@ -285,10 +287,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     n_pages: int, block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                     seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                     window: int = 0, out: torch.Tensor | None = None, *, decode_only: bool = False,
-                    max_context: int = 0) -> torch.Tensor:
+                    max_context: int = 0, q_start: torch.Tensor | None = None, n_tiles: int = 0) -> torch.Tensor:
     """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * head_dim].
     `decode_only` says that every row is an entry of its own (one new token each) and
-    `max_context` bounds the rows' context lengths; both only choose the kernel and its slicing."""
+    `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
+    sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
+    only choose the kernel and its slicing."""
     _need(q, "q", dim=2)
     for name, t in (("row_entry", row_entry), ("positions", positions), ("seq_lens", seq_lens)):
         _need(t, name, torch.int32, 1)
@@ -320,6 +324,16 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _check(status, "paged_attention (decode)")
         if n_slices > 1:
             count_launches(1)  # the merge kernel
+        return out
+    if (q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
+            and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0):
+        _need(q_start, "q_start", torch.int32, 1)
+        lib = _lib_for_head_dim("attention_prefill", head_dim)
+        status = lib.r2_attention_prefill(
+            _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
+            page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens),
+            q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _stream())
+        _check(status, "paged_attention (prefill)")
         return out
     status = _lib("attention_simt").r2_attention_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),

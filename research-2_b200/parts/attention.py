@@ -63,5 +63,6 @@ class PagedAttention:
         mixed = ops.paged_attention(
             q, cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group],
             ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-            self.window, decode_only=ctx.decode_only, max_context=ctx.max_context)
+            self.window, decode_only=ctx.decode_only, max_context=ctx.max_context, q_start=ctx.q_start,
+            n_tiles=ctx.n_attention_tiles)
         return ops.linear(mixed, self.w_out, self.b_out, residual=residual)

@@ -145,6 +145,11 @@ class PagedCase:
         self.row_entry = torch.tensor(row_entry, dtype=torch.int32, device=DEV)
         self.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
         self.seq_lens = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+        starts = [0]
+        for _, rows in entries:
+            starts.append(starts[-1] + rows)
+        self.q_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        self.n_tiles = sum(-(-rows // 64) for _, rows in entries)
         self.q_rows = torch.cat([q.reshape(q.shape[0], -1) for q in self.q]).to(DEV)
         self.k_new = torch.cat([self.k_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
         self.v_new = torch.cat([self.v_dense[e][s:].reshape(r, -1) for e, (s, r) in enumerate(entries)]).to(DEV)
@@ -190,6 +195,28 @@ def test_paged_attention(case, dtype, window):
     want = pc.plain(scale, window)
     assert torch.isfinite(got).all(), "garbage from a slot that was never written leaked in"
     torch.testing.assert_close(got, want, **(dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)))
+
+
+PREFILL_CASES = CASES + [
+    ([(0, 200), (100, 130), (511, 1), (0, 64), (64, 65)], 4, 4, 64, 16),
+    ([(3, 129), (0, 2)], 6, 2, 32, 8),
+    ([(40, 100)], 2, 1, 96, 16),
+    ([(0, 70), (70, 70)], 2, 2, 112, 4),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}_{len(c[0])}e" for c in PREFILL_CASES])
+@pytest.mark.parametrize("window", [0, 13, 70])
+def test_prefill_attention(case, window):
+    """The tensor-core prefill kernel on mixed batches (head sizes up to 128; larger ones fall
+    back to the general kernel inside the same call)."""
+    entries, h, hkv, hd, page = case
+    pc = PagedCase(entries, h, hkv, hd, page, torch.bfloat16, seed=hd + page + window)
+    scale = hd**-0.5 / 1.5
+    got = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles).float().cpu()
+    want = pc.plain(scale, window)
+    assert torch.isfinite(got).all(), "garbage from a slot that was never written leaked in"
+    torch.testing.assert_close(got, want, atol=3e-2, rtol=3e-2)
 
 
 DECODE_CASES = [
@@ -241,7 +268,8 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
 
         case = PagedCase([(511, 1)], 2, 2, 64, 16, dtype, seed=far, mutate=mutate)
         want = case.v_dense[0][far].float()
-        choices = [{}] if dtype == torch.float32 else [{}, dict(decode_only=True, max_context=64), dict(decode_only=True, max_context=4096)]
+        choices = [{}] if dtype == torch.float32 else [{}, dict(decode_only=True, max_context=64), dict(decode_only=True, max_context=4096),
+                                                       dict(q_start=case.q_start, n_tiles=case.n_tiles)]
         for choice in choices:
             got = case.run(1.0, **choice).float().cpu().view(2, 64)
             assert torch.allclose(got, want, atol=5e-2), f"far key {far} {choice}: max diff {(got - want).abs().max():.3f}"
