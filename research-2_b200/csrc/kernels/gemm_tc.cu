@@ -110,6 +110,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -254,15 +259,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     if (finish && ok) {
       const bool a_ok = a < p.a_total;
+      // In the transposed form the thread's feature is fixed: one bias value serves every column.
+      const float bias_a = (TRANSPOSED && a_ok && p.bias != nullptr) ? p.bias[a] : 0.f;
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
         float v[16];
         if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int z = 0; z < p.splits; ++z) {  // split order: the sum does not depend on who came last
-            const float* part = p.workspace + (size_t(z) * n_tiles + tile) * size_t(p.bn) * BM;
+          for (int z0 = 0; z0 < p.splits; z0 += 4) {  // split order: the sum does not depend on who came last
+            float part[4][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&part[size_t(c0 + j) * BM + q * 32 + lane]);
+            for (int u = 0; u < 4; ++u) {
+              const float* src = p.workspace + (size_t(min(z0 + u, p.splits - 1)) * n_tiles + tile) * size_t(p.bn) * BM;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) part[u][j] = __ldcg(&src[size_t(c0 + j) * BM + q * 32 + lane]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (z0 + u < p.splits) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += part[u][j];
+              }
+            }
           }
         } else {
           uint32_t r[16];
@@ -270,20 +288,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
         }
-        if (!a_ok) continue;
+        const int nb = min(16, p.b_total - (b0 + c0));  // columns of this chunk that exist
+        if (!a_ok || nb <= 0) continue;
+        if (TRANSPOSED) {
+          // lanes hold consecutive features: every column is one coalesced row segment
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          int b = b0 + c0 + j;
-          if (b >= p.b_total) continue;
-          int token = TRANSPOSED ? b : a, feature = TRANSPOSED ? a : b;
-          float x = v[j];
-          if (p.bias != nullptr) x += p.bias[feature];
-          x = activate(x, p.act);
-          if (p.residual != nullptr) x += p.residual[size_t(token) * p.ldr + feature];
+          for (int j = 0; j < 16; ++j) v[j] += bias_a;
+          if (p.act == R2_ACT_GELU_TANH) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+          } else if (p.act == R2_ACT_GELU_ERF) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
+          }
+          if (p.residual != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < nb) v[j] += p.residual[size_t(b0 + c0 + j) * p.ldr + a];
+            }
+          }
           if (p.out_is_bf16) {
-            reinterpret_cast<bf16*>(p.out)[size_t(token) * p.ldo + feature] = __float2bfloat16_rn(x);
+            bf16* dst = reinterpret_cast<bf16*>(p.out) + size_t(b0 + c0) * p.ldo + a;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < nb) dst[size_t(j) * p.ldo] = __float2bfloat16_rn(v[j]);
+            }
           } else {
-            reinterpret_cast<float*>(p.out)[size_t(token) * p.ldo + feature] = x;
+            float* dst = reinterpret_cast<float*>(p.out) + size_t(b0 + c0) * p.ldo + a;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < nb) dst[size_t(j) * p.ldo] = v[j];
+            }
+          }
+        } else {
+          // the thread holds 16 consecutive features of its token's row
+          const int f0 = b0 + c0;
+          if (p.bias != nullptr) {
+            if (nb == 16 && (reinterpret_cast<uintptr_t>(p.bias + f0) & 15) == 0) {
+              const float4* b4 = reinterpret_cast<const float4*>(p.bias + f0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float4 t = __ldg(b4 + j);
+                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < nb) v[j] += p.bias[f0 + j];
+              }
+            }
+          }
+          if (p.act == R2_ACT_GELU_TANH) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+          } else if (p.act == R2_ACT_GELU_ERF) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
+          }
+          if (p.residual != nullptr) {
+            const float* rrow = p.residual + size_t(a) * p.ldr + f0;
+            if (nb == 16 && (reinterpret_cast<uintptr_t>(rrow) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float4 t = *reinterpret_cast<const float4*>(rrow + 4 * j);
+                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < nb) v[j] += rrow[j];
+              }
+            }
+          }
+          if (p.out_is_bf16) {
+            bf16* dst = reinterpret_cast<bf16*>(p.out) + size_t(a) * p.ldo + f0;
+            if (nb == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+              uint4 w0, w1;
+              w0.x = pack2(v[0], v[1]); w0.y = pack2(v[2], v[3]); w0.z = pack2(v[4], v[5]); w0.w = pack2(v[6], v[7]);
+              w1.x = pack2(v[8], v[9]); w1.y = pack2(v[10], v[11]); w1.z = pack2(v[12], v[13]); w1.w = pack2(v[14], v[15]);
+              reinterpret_cast<uint4*>(dst)[0] = w0;
+              reinterpret_cast<uint4*>(dst)[1] = w1;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < nb) dst[j] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(p.out) + size_t(a) * p.ldo + f0;
+            if (nb == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < nb) dst[j] = v[j];
+              }
+            }
           }
         }
       }
@@ -363,10 +464,10 @@ extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, in
   const int n_kb = (k + BK - 1) / BK;
   int splits = 1;
   const int tiles = a_tiles * b_tiles;
-  if (swapped && tiles < 120 && n_kb > 1) {
-    splits = 148 / tiles;
-    if (splits > n_kb) splits = n_kb;
-    if (splits < 1) splits = 1;
+  // A CTA streams its K range at a few hundred GB/s, so splitting K pays only when there are
+  // very few tiles and K is long; the last CTA's sum over the partials costs latency per slice.
+  if (swapped && tiles <= 8 && n_kb >= 32) {
+    splits = 4;
     int per = (n_kb + splits - 1) / splits;
     splits = (n_kb + per - 1) / per;
   }
