@@ -8,8 +8,10 @@
 // The 128-row side of the tile ("a side") is the tokens when there are many of them; for 64
 // tokens or fewer the operands swap and the 128-row side is the weight's output features, so
 // that a decode step streams the weights through full-height tiles (the tile is written back
-// transposed). With few tiles the K range is split over several CTAs; they leave float partial
-// sums in a workspace and the last one to arrive adds them in split order and runs the epilogue.
+// transposed). With few tiles the K range is split over the CTAs of a thread-block cluster: each
+// streams its share of the weights, the others send their float partial sums into the leader's
+// shared memory (distributed shared memory), and after a cluster barrier the leader adds them in
+// rank order and runs the epilogue. The order is fixed, so the result is the same bits every run.
 //
 // Weights stored [K, N] (GPT-2's Conv1D layout) are the MN-major operand form, weights stored
 // [N, K] (a tied embedding as the head) the K-major form; both are loaded with 128-byte swizzle.
@@ -29,6 +31,7 @@ constexpr int BK = 64;           // one 128-byte swizzle span of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr int MAX_STAGES = 8;
+constexpr int N_SMS = 148;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 #define R2_ERR_TIMEOUT_FULL 1
@@ -46,8 +49,6 @@ struct GemmParams {
   int ldo;
   int out_is_bf16;
   int act;
-  float* workspace;
-  int* counters;
   int* error_flag;
 };
 
@@ -110,6 +111,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -141,11 +147,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* acc_ready = empty + MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
-  int* is_last = reinterpret_cast<int*>(tmem_slot + 1);
+  // partial sums of the other CTAs of the cluster, [rank - 1][column][row], used in the leader only
+  float* reduce = reinterpret_cast<float*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
+  uint32_t rank = 0;  // this CTA's place in its cluster = its slice of K
+  if (p.splits > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int kb_begin = int(rank) * p.kb_per_split;
   const int kb_end = min(p.n_kb, kb_begin + p.kb_per_split);
   const int n_kb = kb_end - kb_begin;
   uint32_t tmem_cols = 32;
@@ -169,6 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  if (p.splits > 1) cluster_sync();  // every CTA of the cluster is running before anyone writes into another
 
   if (warp == 0 && lane == 0) {
     // ---- producer: one thread feeds the ring of stages -------------------------------------
@@ -223,70 +233,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
+  bool acc_ok = true;
   if (warp >= 2) {
     const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
-    const int a = a0 + q * 32 + lane;
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const int n_tiles = gridDim.x * gridDim.y;
-    bool finish = true;
-    if (p.splits > 1) {
-      // leave this slice's partial sums, then find out whether every other slice has left theirs
-      float* mine = p.workspace + (size_t(blockIdx.z) * n_tiles + tile) * size_t(p.bn) * BM;
-      if (ok && n_kb > 0) {
-        for (int c0 = 0; c0 < p.bn; c0 += 16) {
-          uint32_t r[16];
+    acc_ok = ok;
+    if (p.splits > 1 && rank != 0) {
+      // send this slice's partial sums to the leader's shared memory
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(reduce)), "r"(0u));
+      remote += (uint32_t(rank - 1) * uint32_t(p.bn) * BM + uint32_t(q * 32 + lane)) * 4u;
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        uint32_t r[16];
+        if (ok && n_kb > 0) {
           tmem_load16(lane_addr + uint32_t(c0), r);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[size_t(c0 + j) * BM + q * 32 + lane] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
-      } else {
-        for (int c = 0; c < p.bn; ++c) mine[size_t(c) * BM + q * 32 + lane] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + uint32_t(c0 + j) * BM * 4u), "r"(r[j]) : "memory");
+        }
       }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-      if (threadIdx.x == 64) {
-        int arrived = atomicAdd(&p.counters[tile], 1);
-        *is_last = (arrived == p.splits - 1) ? 1 : 0;
-        if (arrived == p.splits - 1) p.counters[tile] = 0;  // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      finish = *is_last != 0;
-      if (finish) __threadfence();
     }
+  }
+  if (p.splits > 1) cluster_sync();  // partial sums have landed in the leader (release / acquire)
+  if (warp >= 2 && rank == 0) {
+    const int q = warp & 3;
+    const int a = a0 + q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    const bool ok = acc_ok;
+    const bool finish = true;
     if (finish && ok) {
       const bool a_ok = a < p.a_total;
       // In the transposed form the thread's feature is fixed: one bias value serves every column.
       const float bias_a = (TRANSPOSED && a_ok && p.bias != nullptr) ? p.bias[a] : 0.f;
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
         float v[16];
-        if (p.splits > 1) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int z0 = 0; z0 < p.splits; z0 += 4) {  // split order: the sum does not depend on who came last
-            float part[4][16];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float* src = p.workspace + (size_t(min(z0 + u, p.splits - 1)) * n_tiles + tile) * size_t(p.bn) * BM;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) part[u][j] = __ldcg(&src[size_t(c0 + j) * BM + q * 32 + lane]);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              if (z0 + u < p.splits) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] += part[u][j];
-              }
-            }
-          }
-        } else {
+        {
           uint32_t r[16];
-          tmem_load16(lane_addr + uint32_t(c0), r);
+          if (n_kb > 0) {
+            tmem_load16(lane_addr + uint32_t(c0), r);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        for (int z = 1; z < p.splits; ++z) {  // rank order: the sum is the same bits every run
+          const float* part = reduce + (size_t(z - 1) * p.bn + c0) * BM + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += part[size_t(j) * BM];
         }
         const int nb = min(16, p.b_total - (b0 + c0));  // columns of this chunk that exist
         if (!a_ok || nb <= 0) continue;
@@ -441,40 +443,78 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  kernel<<<grid, THREADS, smem, stream>>>(ma, mb, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = unsigned(p.splits);
+  config.attrs = attr;
+  config.numAttrs = p.splits > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, ma, mb, p);
+  if (e != cudaSuccess) return int(e);
   return launch_status();
+}
+
+struct Plan {
+  bool swapped;
+  int a_total, b_total, bn, n_kb, splits, kb_per_split, stages;
+  size_t smem;
+};
+
+Plan make_plan(int m, int n, int k, int w_is_nk) {
+  Plan pl;
+  pl.swapped = m <= 64;
+  pl.a_total = pl.swapped ? n : m;
+  pl.b_total = pl.swapped ? m : n;
+  if (pl.swapped) {
+    pl.bn = ((pl.b_total + 15) / 16) * 16;               // tokens, K-major: any multiple of 16
+  } else if (w_is_nk) {
+    pl.bn = pl.b_total >= 128 ? 128 : ((pl.b_total + 15) / 16) * 16;
+  } else {
+    pl.bn = pl.b_total > 64 ? 128 : 64;                   // MN-major boxes are 64 features wide
+  }
+  const int tiles = ((pl.a_total + BM - 1) / BM) * ((pl.b_total + pl.bn - 1) / pl.bn);
+  pl.n_kb = (k + BK - 1) / BK;
+  // A CTA streams its K range at well under 100 GB/s, so a product with few tiles uses the CTAs
+  // of a cluster (at most 8) on one tile, each with a share of K; the leader's shared memory
+  // must hold the others' partial tiles.
+  pl.splits = 1;
+  if (pl.swapped && tiles * 2 <= N_SMS) {
+    int s = N_SMS / tiles;
+    if (s > 8) s = 8;
+    if (s > pl.n_kb) s = pl.n_kb;
+    while (s > 1 && size_t(s - 1) * pl.bn * BM * 4 > 100 * 1024) --s;
+    if (s < 1) s = 1;
+    int per = (pl.n_kb + s - 1) / s;
+    pl.splits = (pl.n_kb + per - 1) / per;
+  }
+  pl.kb_per_split = (pl.n_kb + pl.splits - 1) / pl.splits;
+  const size_t a_bytes = BM * BK * 2, b_stride = (size_t(pl.bn) * BK * 2 + 1023) & ~size_t(1023);
+  const size_t fixed = 1024 + (2 * MAX_STAGES + 1) * 8 + 32 + size_t(pl.splits - 1) * pl.bn * BM * 4;
+  // with more tiles than SMs, leave room for two CTAs on an SM: one's epilogue under the other's loads
+  const size_t budget = (tiles * pl.splits > N_SMS ? 113 * 1024 : 227 * 1024) - fixed;
+  int stages = int(budget / (a_bytes + b_stride));
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > pl.kb_per_split) stages = pl.kb_per_split;
+  if (stages < 1) stages = 1;
+  pl.stages = stages;
+  pl.smem = fixed + size_t(stages) * (a_bytes + b_stride);
+  return pl;
 }
 
 }  // namespace
 
-// Floats of workspace and number of counters that r2_gemm_tc may use for (m, n, k).
-extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, int* splits_out, long long* workspace_floats,
-                               int* n_counters) {
-  const bool swapped = m <= 64;
-  const int a_total = swapped ? n : m, b_total = swapped ? m : n;
-  int bn;
-  if (swapped) {
-    bn = ((b_total + 15) / 16) * 16;          // tokens, K-major: any multiple of 16
-  } else if (w_is_nk) {
-    bn = b_total >= 128 ? 128 : ((b_total + 15) / 16) * 16;
-  } else {
-    bn = b_total > 64 ? 128 : 64;             // MN-major boxes are 64 features wide
-  }
-  const int a_tiles = (a_total + BM - 1) / BM, b_tiles = (b_total + bn - 1) / bn;
-  const int n_kb = (k + BK - 1) / BK;
-  int splits = 1;
-  const int tiles = a_tiles * b_tiles;
-  // A CTA streams its K range at a few hundred GB/s, so splitting K pays only when there are
-  // very few tiles and K is long; the last CTA's sum over the partials costs latency per slice.
-  if (swapped && tiles <= 8 && n_kb >= 32) {
-    splits = 4;
-    int per = (n_kb + splits - 1) / splits;
-    splits = (n_kb + per - 1) / per;
-  }
-  *bn_out = bn;
-  *splits_out = splits;
-  *workspace_floats = splits > 1 ? (long long)splits * tiles * bn * BM : 0;
-  *n_counters = splits > 1 ? tiles : 0;
+// How r2_gemm_tc would run (m, n, k): tile width on the b side, CTAs per cluster (slices of K), stages.
+extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, int* splits_out, int* stages_out) {
+  Plan pl = make_plan(m, n, k, w_is_nk);
+  *bn_out = pl.bn;
+  *splits_out = pl.splits;
+  *stages_out = pl.stages;
   return R2_OK;
 }
 
@@ -483,8 +523,7 @@ extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, in
 // whose rows are not 16-byte multiples; the caller then uses the CUDA-core kernel.
 extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_is_nk, const float* bias,
                           const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
-                          int out_dtype, float* workspace, long long workspace_floats, int* counters, int n_counters,
-                          int* error_flag, cudaStream_t stream) {
+                          int out_dtype, int* error_flag, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return R2_OK;
   if (k < 1) return R2_BAD_SHAPE;
   if (act < R2_ACT_NONE || act > R2_ACT_GELU_ERF) return R2_UNSUPPORTED;
@@ -492,21 +531,16 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   if (error_flag == nullptr) return R2_BAD_SHAPE;
   if (lda % 8 != 0 || ldw % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return R2_UNSUPPORTED;
   if (k % 8 != 0 || (!w_is_nk && n % 8 != 0)) return R2_UNSUPPORTED;
-  int bn, splits, need_counters;
-  long long need_ws;
-  r2_gemm_tc_plan(m, n, k, w_is_nk, &bn, &splits, &need_ws, &need_counters);
-  if (splits > 1 && (workspace == nullptr || counters == nullptr || workspace_floats < need_ws || n_counters < need_counters)) {
-    return R2_BAD_SHAPE;
-  }
-  const bool swapped = m <= 64;
+  const Plan pl = make_plan(m, n, k, w_is_nk);
   GemmParams p;
-  p.a_total = swapped ? n : m;
-  p.b_total = swapped ? m : n;
+  p.a_total = pl.a_total;
+  p.b_total = pl.b_total;
   p.k_total = k;
-  p.bn = bn;
-  p.n_kb = (k + BK - 1) / BK;
-  p.splits = splits;
-  p.kb_per_split = (p.n_kb + splits - 1) / splits;
+  p.bn = pl.bn;
+  p.n_kb = pl.n_kb;
+  p.splits = pl.splits;
+  p.kb_per_split = pl.kb_per_split;
+  p.stages = pl.stages;
   p.bias = bias;
   p.residual = residual;
   p.ldr = ldr;
@@ -514,21 +548,14 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   p.ldo = ldo;
   p.out_is_bf16 = out_dtype == R2_BF16;
   p.act = act;
-  p.workspace = workspace;
-  p.counters = counters;
   p.error_flag = error_flag;
-  const size_t a_bytes = BM * BK * 2, b_stride = (size_t(bn) * BK * 2 + 1023) & ~size_t(1023);
-  int stages = int((227 * 1024 - 2048) / (a_bytes + b_stride));
-  if (stages > MAX_STAGES) stages = MAX_STAGES;
-  if (stages > p.kb_per_split) stages = p.kb_per_split;
-  if (stages < 1) stages = 1;
-  p.stages = stages;
-  const size_t smem = 1024 + size_t(stages) * (a_bytes + b_stride) + (2 * MAX_STAGES + 1) * 8 + 16;
-  dim3 grid((p.a_total + BM - 1) / BM, (p.b_total + bn - 1) / bn, splits);
+  const int bn = pl.bn;
+  const size_t smem = pl.smem;
+  dim3 grid((p.a_total + BM - 1) / BM, (p.b_total + bn - 1) / bn, pl.splits);
 
   CUtensorMap ma, mb;
   bool ok;
-  if (!swapped) {
+  if (!pl.swapped) {
     // a side: tokens [m, k] K-major; b side: the weight
     ok = make_map(&ma, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, BM);
     if (w_is_nk) {

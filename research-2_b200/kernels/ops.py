@@ -142,8 +142,8 @@ def use_tensor_core_gemm(on: bool) -> bool:
 
 
 class _Workspace:
-    """Scratch of the split-K matrix product (partial sums, arrival counters) and the word in
-    which kernels record a bounded wait that ran out. One per device, sized once."""
+    """Scratch of sliced decode attention (the slices' partial results) and the word in which
+    kernels record a bounded wait that ran out. One per device, sized once."""
 
     FLOATS = 4 * 1024 * 1024
     COUNTERS = 4096
@@ -250,8 +250,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         ws = _workspace(a.device)
         status = _lib("gemm_tc").r2_gemm_tc(
             _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
-            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.floats), C.c_longlong(ws.floats.numel()), _p(ws.counters),
-            ws.counters.numel(), _p(ws.error), _stream())
+            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _stream())
         if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
             _check(status, "linear (tensor cores)")
             return out
