@@ -44,6 +44,8 @@ struct DecodeParams {
 template <int G>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_kernel(const DecodeParams p) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ float q_s[G][HD];
   __shared__ float red_o[WARPS][G][HD];
   __shared__ float red_m[WARPS][G], red_l[WARPS][G];
@@ -226,6 +228,8 @@ decode_kernel(const DecodeParams p) {
 // out[t, h, :] = sum_s exp(m_s - m) o_s / sum_s exp(m_s - m) l_s, slices in order.
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                              int out_row_stride, int n_heads, int n_slices) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   const int t = blockIdx.y, h = blockIdx.x;
   const size_t base = (size_t(t) * n_heads + h) * n_slices;
   float mx = -INFINITY;
@@ -246,7 +250,7 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
 template <int G>
 int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
-  decode_kernel<G><<<grid, WARPS * 32, 0, stream>>>(p);
+  r2_launch(decode_kernel<G>, dim3(grid), dim3(WARPS * 32), size_t(0), stream, p);
   return launch_status();
 }
 
@@ -289,7 +293,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
     default: return R2_UNSUPPORTED;
   }
   if (status != R2_OK || n_slices == 1) return status;
-  merge_kernel<<<dim3(n_heads, n_rows), HD >= 128 ? 128 : 64, 0, stream>>>(p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
+  r2_launch(merge_kernel, dim3(dim3(n_heads, n_rows)), dim3(HD >= 128 ? 128 : 64), size_t(0), stream, p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
   return launch_status();
 }
 

@@ -70,6 +70,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __global__ void __launch_bounds__(WARPS * 32)
 prefill_kernel(const PrefillParams p) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_s = smem;                         // [BM] rows
   uint8_t* k_s = smem + TILE_BYTES;            // 2 stages
@@ -300,6 +302,6 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  prefill_kernel<<<dim3(n_tiles, n_heads), WARPS * 32, smem, stream>>>(p);
+  r2_launch(prefill_kernel, dim3(dim3(n_tiles, n_heads)), dim3(WARPS * 32), size_t(smem), stream, p);
   return launch_status();
 }

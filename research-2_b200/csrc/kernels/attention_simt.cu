@@ -26,6 +26,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
                       const int32_t* __restrict__ row_entry, const int32_t* __restrict__ positions,
                       const int32_t* __restrict__ seq_lens, int n_heads, int n_kv_heads, int head_dim,
                       float scale, int window, int n_pages) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -109,12 +111,12 @@ extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
   dim3 grid(n_rows, (n_heads + WARPS - 1) / WARPS);
   if (dtype == R2_F32) {
-    attention_simt_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+    r2_launch(attention_simt_kernel<float>, dim3(grid), dim3(WARPS * 32), size_t(0), stream, 
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache, (const float*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
         head_dim, scale, window, n_pages);
   } else if (dtype == R2_BF16) {
-    attention_simt_kernel<bf16><<<grid, WARPS * 32, 0, stream>>>(
+    r2_launch(attention_simt_kernel<bf16>, dim3(grid), dim3(WARPS * 32), size_t(0), stream, 
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
         head_dim, scale, window, n_pages);

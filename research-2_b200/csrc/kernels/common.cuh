@@ -74,6 +74,33 @@ __device__ __forceinline__ float activate(float x, int act) {
   return x;
 }
 
+// Programmatic dependent launch: a kernel may start while its predecessor in the stream is still
+// running. Everything it does before `pdl_wait()` must neither read what the predecessor writes
+// nor write anything; `pdl_wait()` returns once the predecessor has completed and its writes are
+// visible. `pdl_launch_dependents()` lets the successor start its own prologue. Both are no-ops
+// for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static int g_r2_pdl = 1;
+// Every kernel library exports this switch (1 = launch with programmatic stream serialization).
+extern "C" void r2_set_pdl(int on) { g_r2_pdl = on ? 1 : 0; }
+
+template <typename... KArgs, typename... Args>
+static inline void r2_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = g_r2_pdl ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);  // a failure shows in launch_status()
+}
+
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? R2_OK : int(e);

@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, int ldw,
                  const float* __restrict__ bias, const float* __restrict__ residual, int ldr,
                  TO* __restrict__ out, int ldo, int m_total, int n_total, int k_total, int act) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ float as[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -87,10 +89,10 @@ int launch(const void* a, int lda, const void* w, int ldw, int w_is_nk, const fl
            int ldr, void* out, int ldo, int m, int n, int k, int act, cudaStream_t stream) {
   dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
   if (w_is_nk) {
-    gemm_simt_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((const TA*)a, lda, (const TW*)w, ldw, bias, residual,
+    r2_launch(gemm_simt_kernel<TA, TW, TO, true>, dim3(grid), dim3(256), size_t(0), stream, (const TA*)a, lda, (const TW*)w, ldw, bias, residual,
                                                                  ldr, (TO*)out, ldo, m, n, k, act);
   } else {
-    gemm_simt_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((const TA*)a, lda, (const TW*)w, ldw, bias, residual,
+    r2_launch(gemm_simt_kernel<TA, TW, TO, false>, dim3(grid), dim3(256), size_t(0), stream, (const TA*)a, lda, (const TW*)w, ldw, bias, residual,
                                                                   ldr, (TO*)out, ldo, m, n, k, act);
   }
   return launch_status();

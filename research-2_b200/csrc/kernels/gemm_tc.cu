@@ -150,6 +150,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // partial sums of the other CTAs of the cluster, [rank - 1][column][row], used in the leader only
   float* reduce = reinterpret_cast<float*>(tmem_slot + 4);
 
+  pdl_launch_dependents();  // the next kernel may set up and prefetch its weights meanwhile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
   uint32_t rank = 0;  // this CTA's place in its cluster = its slice of K
@@ -178,31 +179,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  if (p.splits > 1) cluster_sync();  // every CTA of the cluster is running before anyone writes into another
-
-  if (warp == 0 && lane == 0) {
-    // ---- producer: one thread feeds the ring of stages -------------------------------------
-    for (int i = 0; i < n_kb; ++i) {
-      int s = i % p.stages;
-      if (i >= p.stages && !mbar_wait(&empty[s], uint32_t((i / p.stages - 1) & 1))) {
-        atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
-        break;
-      }
-      int k0 = (kb_begin + i) * BK;
-      mbar_expect_tx(&full[s], a_bytes + b_bytes);
+  // The weight is never written by a kernel, so its first tiles are requested before the wait
+  // on the previous kernel; the activations, which that kernel may have written, after it.
+  auto load_weight = [&](int i, int s) {
+    int k0 = (kb_begin + i) * BK;
+    if (TRANSPOSED) {
       uint8_t* a_dst = a_tiles + size_t(s) * a_bytes;
-      uint8_t* b_dst = b_tiles + size_t(s) * b_stride;
       if (A_MN) {  // [k rows][64 a-elements] boxes, one per 64 a-elements
         tma_load_2d(a_dst, &map_a, a0, k0, &full[s]);
         tma_load_2d(a_dst + BK * 128, &map_a, a0 + 64, k0, &full[s]);
       } else {     // [a rows][64 k-elements]
         tma_load_2d(a_dst, &map_a, k0, a0, &full[s]);
       }
+    } else {
+      uint8_t* b_dst = b_tiles + size_t(s) * b_stride;
       if (B_MN) {
         for (int j = 0; j < p.bn; j += 64) tma_load_2d(b_dst + size_t(j / 64) * BK * 128, &map_b, b0 + j, k0, &full[s]);
       } else {
         tma_load_2d(b_dst, &map_b, k0, b0, &full[s]);
       }
+    }
+  };
+  auto load_tokens = [&](int i, int s) {
+    int k0 = (kb_begin + i) * BK;
+    if (TRANSPOSED) {
+      tma_load_2d(b_tiles + size_t(s) * b_stride, &map_b, k0, b0, &full[s]);  // tokens are K-major
+    } else {
+      tma_load_2d(a_tiles + size_t(s) * a_bytes, &map_a, k0, a0, &full[s]);
+    }
+  };
+  const int first = min(n_kb, p.stages);
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full[i], a_bytes + b_bytes);
+      load_weight(i, i);
+    }
+  }
+  __syncwarp();
+  if (p.splits > 1) cluster_sync();  // every CTA of the cluster is running before anyone writes into another
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer: one thread feeds the ring of stages -------------------------------------
+    pdl_wait();
+    for (int i = 0; i < first; ++i) load_tokens(i, i);
+    for (int i = first; i < n_kb; ++i) {
+      int s = i % p.stages;
+      if (!mbar_wait(&empty[s], uint32_t((i / p.stages - 1) & 1))) {
+        atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
+        break;
+      }
+      mbar_expect_tx(&full[s], a_bytes + b_bytes);
+      load_weight(i, s);
+      load_tokens(i, s);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ------------------------------------------------------------------------
@@ -235,6 +263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
   bool acc_ok = true;
   if (warp >= 2) {
+    pdl_wait();  // the epilogue reads the residual stream and writes the output
     const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
@@ -448,13 +477,22 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
   config.blockDim = dim3(THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = unsigned(p.splits);
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (p.splits > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = unsigned(p.splits);
+    ++n_attr;
+  }
+  if (g_r2_pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   config.attrs = attr;
-  config.numAttrs = p.splits > 1 ? 1 : 0;
+  config.numAttrs = n_attr;
   cudaError_t e = cudaLaunchKernelEx(&config, kernel, ma, mb, p);
   if (e != cudaSuccess) return int(e);
   return launch_status();

@@ -9,6 +9,8 @@ template <typename W>
 __global__ void embed_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
                              const W* __restrict__ table, const W* __restrict__ pos_table,
                              float* __restrict__ out, int width, int n_vocab, int n_positions) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= n_vocab ? n_vocab - 1 : id);  // ids are validated on the host
@@ -34,10 +36,10 @@ extern "C" int r2_embed(const int32_t* ids, const int32_t* positions, const void
   if (width < 1 || n_vocab < 1) return R2_BAD_SHAPE;
   int threads = width >= 256 ? 256 : (width >= 128 ? 128 : 64);
   if (wdtype == R2_F32) {
-    embed_kernel<float><<<n_rows, threads, 0, stream>>>(ids, positions, (const float*)table, (const float*)pos_table,
+    r2_launch(embed_kernel<float>, dim3(n_rows), dim3(threads), size_t(0), stream, ids, positions, (const float*)table, (const float*)pos_table,
                                                         out, width, n_vocab, n_positions);
   } else if (wdtype == R2_BF16) {
-    embed_kernel<bf16><<<n_rows, threads, 0, stream>>>(ids, positions, (const bf16*)table, (const bf16*)pos_table,
+    r2_launch(embed_kernel<bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, ids, positions, (const bf16*)table, (const bf16*)pos_table,
                                                        out, width, n_vocab, n_positions);
   } else {
     return R2_BAD_DTYPE;
@@ -53,6 +55,8 @@ template <typename O>
 __global__ void layer_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
                                   const float* __restrict__ gamma, const float* __restrict__ beta,
                                   O* __restrict__ out, int width, float eps) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   extern __shared__ float row_s[];
   __shared__ float scratch[33];
   int r = blockIdx.x;
@@ -86,10 +90,10 @@ extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* g
   size_t smem = size_t(width) * sizeof(float);
   if (odtype == R2_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    layer_norm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (float*)out, width, eps);
+    r2_launch(layer_norm_kernel<float>, dim3(n_rows), dim3(threads), size_t(smem), stream, x, rows, gamma, beta, (float*)out, width, eps);
   } else if (odtype == R2_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    layer_norm_kernel<bf16><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (bf16*)out, width, eps);
+    r2_launch(layer_norm_kernel<bf16>, dim3(n_rows), dim3(threads), size_t(smem), stream, x, rows, gamma, beta, (bf16*)out, width, eps);
   } else {
     return R2_BAD_DTYPE;
   }
@@ -106,6 +110,8 @@ __global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict
                                 C* __restrict__ k_cache, C* __restrict__ v_cache,
                                 const int32_t* __restrict__ slot_mapping, int n_kv_heads, int head_dim,
                                 int page_size, long long page_stride, int n_pages) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   int t = blockIdx.x;
   int slot = slot_mapping[t];
   int page = slot / page_size, off = slot % page_size;
@@ -129,11 +135,11 @@ extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_str
   int width = n_kv_heads * head_dim;
   int threads = width >= 256 ? 256 : 128;
   if (dtype == R2_F32) {
-    kv_write_kernel<float, float><<<n_rows, threads, 0, stream>>>((const float*)k_src, (const float*)v_src, src_row_stride,
+    r2_launch(kv_write_kernel<float, float>, dim3(n_rows), dim3(threads), size_t(0), stream, (const float*)k_src, (const float*)v_src, src_row_stride,
                                                                   (float*)k_cache, (float*)v_cache, slot_mapping,
                                                                   n_kv_heads, head_dim, page_size, page_stride, n_pages_total);
   } else if (dtype == R2_BF16) {
-    kv_write_kernel<bf16, bf16><<<n_rows, threads, 0, stream>>>((const bf16*)k_src, (const bf16*)v_src, src_row_stride,
+    r2_launch(kv_write_kernel<bf16, bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, (const bf16*)k_src, (const bf16*)v_src, src_row_stride,
                                                                 (bf16*)k_cache, (bf16*)v_cache, slot_mapping,
                                                                 n_kv_heads, head_dim, page_size, page_stride, n_pages_total);
   } else {

@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const uint32_t* __restrict__ key0, const uint32_t* __restrict__ key1,
               const int32_t* __restrict__ sample_pos, int32_t* __restrict__ tokens) {
+  pdl_launch_dependents();  // the next kernel may begin its prologue
+  pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ Best best_s[THREADS / 32];
   __shared__ uint32_t hist[256];
   __shared__ uint32_t sel_prefix, sel_remaining;
@@ -165,6 +167,6 @@ extern "C" int r2_sample(const float* logits, int ld, int n_rows, int vocab, con
                          int32_t* tokens, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (vocab < 1 || ld < vocab) return R2_BAD_SHAPE;
-  sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, key0, key1, sample_pos, tokens);
+  r2_launch(sample_kernel, dim3(n_rows), dim3(THREADS), size_t(0), stream, logits, ld, vocab, temperature, top_k, key0, key1, sample_pos, tokens);
   return launch_status();
 }

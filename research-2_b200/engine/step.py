@@ -100,6 +100,16 @@ class DecodeGraph:
                 step_fn.sample(step_fn.forward(self.ctx), self.ctx)
         torch.cuda.current_stream(step_fn.device).wait_stream(side)
         torch.cuda.synchronize(step_fn.device)
+        try:
+            self._capture(step_fn)
+        except RuntimeError:
+            # a driver that cannot record programmatic launch edges in a graph: plain edges then
+            if not ops.use_programmatic_dependent_launch(False):
+                raise
+            torch.cuda.synchronize(step_fn.device)
+            self._capture(step_fn)
+
+    def _capture(self, step_fn: "StepFunction") -> None:
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(self.graph):

@@ -84,10 +84,25 @@ def _rows(t: torch.Tensor, name: str) -> int:
 _libs: dict[str, C.CDLL] = {}
 
 
+_pdl = os.environ.get("R2_PDL", "1") != "0"
+
+
+def use_programmatic_dependent_launch(on: bool) -> bool:
+    """Kernels are launched so that each may start its prologue (set-up, weight prefetch) while
+    its predecessor still runs; every kernel waits for the predecessor before it reads or writes
+    anything the predecessor touches. Returns the previous setting."""
+    global _pdl
+    before, _pdl = _pdl, bool(on)
+    for lib in _libs.values():
+        lib.r2_set_pdl(int(_pdl))
+    return before
+
+
 def _lib(source: str) -> C.CDLL:
     lib = _libs.get(source)
     if lib is None:
         lib = kernel_library(source)
+        lib.r2_set_pdl(int(_pdl))
         _libs[source] = lib
     return lib
 
@@ -127,6 +142,7 @@ def _lib_for_head_dim(source: str, head_dim: int) -> C.CDLL:
     lib = _libs.get(key)
     if lib is None:
         lib = kernel_library(source, {"HEAD_DIM": head_dim})
+        lib.r2_set_pdl(int(_pdl))
         if source == "attention_decode":
             lib.r2_attention_decode_scratch_floats.restype = C.c_longlong
         _libs[key] = lib
