@@ -37,6 +37,7 @@ constexpr uint32_t SPIN_LIMIT = 1u << 22;
 #define R2_ERR_TIMEOUT_FULL 1
 #define R2_ERR_TIMEOUT_EMPTY 2
 #define R2_ERR_TIMEOUT_ACC 3
+#define R2_ERR_TIMEOUT_TOKENS 4
 
 struct GemmParams {
   int a_total, b_total, k_total;  // extents of the a side, the b side and K
@@ -50,6 +51,14 @@ struct GemmParams {
   int out_is_bf16;
   int act;
   int* error_flag;
+  // LayerNorm of the tokens fused in front of the product (swapped form only): the token operand
+  // is built in shared memory from float rows instead of being loaded by TMA.
+  const float* ln_x;       // [*, k] float rows, or null: no fused norm
+  int ln_ldx;
+  const int32_t* ln_rows;  // token i reads row ln_rows[i] (null: row i)
+  const float* ln_gamma;
+  const float* ln_beta;
+  float ln_eps;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -130,6 +139,61 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// LayerNorm of the token rows, written as the K-major, 128-byte-swizzled bfloat16 tiles that the
+// tensor core reads: warp `w` of the four takes rows w, w + 4, ...; a lane holds every 32nd group
+// of four elements of its row; mean and variance are two passes over registers, in float
+// (kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23). Rows past the last token are zeros.
+constexpr int LN_MAX_K = 2048;
+
+__device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t* b_tiles, uint32_t b_stride, int kb_begin,
+                                                    int n_kb, int w, int lane) {
+  const int k_total = p.k_total;
+  const int k_lo = kb_begin * BK, k_hi = min(k_total, (kb_begin + n_kb) * BK);
+  for (int r = w; r < p.bn; r += 4) {
+    float4 v[LN_MAX_K / 128];
+    float mean = 0.f, rstd = 0.f;
+    const bool live = r < p.b_total;
+    if (live) {
+      const int src = p.ln_rows != nullptr ? p.ln_rows[r] : r;
+      const float4* row = reinterpret_cast<const float4*>(p.ln_x + size_t(src) * p.ln_ldx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        int k = (lane + 32 * i) * 4;
+        v[i] = k < k_total ? row[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += v[i].x + v[i].y + v[i].z + v[i].w;
+      }
+      mean = warp_sum(sum) / float(k_total);
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        int k = (lane + 32 * i) * 4;
+        if (k < k_total) {
+          float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+          sq += a * a + b * b + c * c + d * d;
+        }
+      }
+      rstd = 1.f / sqrtf(warp_sum(sq) / float(k_total) + p.ln_eps);
+    }
+#pragma unroll
+    for (int i = 0; i < LN_MAX_K / 128; ++i) {
+      int k = (lane + 32 * i) * 4;
+      if (k < k_lo || k >= (kb_begin + n_kb) * BK) continue;  // another CTA's share of K, or past the tiles
+      uint32_t lo = 0u, hi = 0u;
+      if (live && k < k_hi) {
+        float4 g = *reinterpret_cast<const float4*>(p.ln_gamma + k);
+        float4 b = *reinterpret_cast<const float4*>(p.ln_beta + k);
+        lo = pack2((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y);
+        hi = pack2((v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+      }
+      const int kb = k / BK - kb_begin, kin = k % BK;
+      uint8_t* tile = b_tiles + size_t(kb) * b_stride;
+      uint32_t off = uint32_t(r / 8) * 1024u + uint32_t(r % 8) * 128u + (uint32_t((kin / 8) ^ (r % 8)) * 16u) + uint32_t(kin % 8) * 2u;
+      *reinterpret_cast<uint2*>(tile + off) = make_uint2(lo, hi);
+    }
+  }
+}
+
 // A_MN / B_MN: the operand's tile in shared memory is MN-major (rows of 64 MN-elements, one row
 // per k) instead of K-major (rows of 64 k-elements, one row per MN index).
 // TRANSPOSED: the a side is the features and the b side the tokens.
@@ -141,12 +205,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t a_bytes = BM * BK * 2;
   const uint32_t b_bytes = uint32_t(p.bn) * BK * 2;
   const uint32_t b_stride = (b_bytes + 1023u) & ~1023u;
+  const bool fused_ln = TRANSPOSED && p.ln_x != nullptr;
+  const int b_slots = fused_ln ? p.kb_per_split : p.stages;  // with a fused norm every token tile stays resident
   uint8_t* a_tiles = smem;
   uint8_t* b_tiles = smem + size_t(p.stages) * a_bytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + size_t(p.stages) * b_stride);
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + size_t(b_slots) * b_stride);
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* acc_ready = empty + MAX_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  uint64_t* tokens_ready = acc_ready + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tokens_ready + 1);
   // partial sums of the other CTAs of the cluster, [rank - 1][column][row], used in the leader only
   float* reduce = reinterpret_cast<float*>(tmem_slot + 4);
 
@@ -167,6 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_ready, 1);
+    mbar_init(tokens_ready, 4);  // one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -209,9 +277,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   };
   const int first = min(n_kb, p.stages);
+  const uint32_t stage_bytes = a_bytes + (fused_ln ? 0u : b_bytes);
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < first; ++i) {
-      mbar_expect_tx(&full[i], a_bytes + b_bytes);
+      mbar_expect_tx(&full[i], stage_bytes);
       load_weight(i, i);
     }
   }
@@ -221,22 +290,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0 && lane == 0) {
     // ---- producer: one thread feeds the ring of stages -------------------------------------
     pdl_wait();
-    for (int i = 0; i < first; ++i) load_tokens(i, i);
+    if (!fused_ln) {
+      for (int i = 0; i < first; ++i) load_tokens(i, i);
+    }
     for (int i = first; i < n_kb; ++i) {
       int s = i % p.stages;
       if (!mbar_wait(&empty[s], uint32_t((i / p.stages - 1) & 1))) {
         atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
         break;
       }
-      mbar_expect_tx(&full[s], a_bytes + b_bytes);
+      mbar_expect_tx(&full[s], stage_bytes);
       load_weight(i, s);
-      load_tokens(i, s);
+      if (!fused_ln) load_tokens(i, s);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ------------------------------------------------------------------------
     uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(A_MN) << 15) | (uint32_t(B_MN) << 16) |
                      (uint32_t(p.bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
     bool ok = true;
+    if (fused_ln && !mbar_wait(tokens_ready, 0)) {
+      atomicMax(p.error_flag, R2_ERR_TIMEOUT_TOKENS);
+      ok = false;
+    }
     for (int i = 0; i < n_kb && ok; ++i) {
       int s = i % p.stages;
       if (!mbar_wait(&full[s], uint32_t((i / p.stages) & 1))) {
@@ -246,7 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t a_addr = smem_u32(a_tiles + size_t(s) * a_bytes);
-      uint32_t b_addr = smem_u32(b_tiles + size_t(s) * b_stride);
+      uint32_t b_addr = smem_u32(b_tiles + size_t(fused_ln ? i : s) * b_stride);
 #pragma unroll
       for (int kk = 0; kk < BK / UMMA_K; ++kk) {
         // K-major: 16 k-elements further along the swizzled row = 32 bytes.
@@ -264,6 +339,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   bool acc_ok = true;
   if (warp >= 2) {
     pdl_wait();  // the epilogue reads the residual stream and writes the output
+    if (TRANSPOSED && fused_ln) {
+      build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor core
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tokens_ready)) : "memory");
+    }
     const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
@@ -504,7 +585,7 @@ struct Plan {
   size_t smem;
 };
 
-Plan make_plan(int m, int n, int k, int w_is_nk) {
+Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   Plan pl;
   pl.swapped = m <= 64;
   pl.a_total = pl.swapped ? n : m;
@@ -533,9 +614,19 @@ Plan make_plan(int m, int n, int k, int w_is_nk) {
   }
   pl.kb_per_split = (pl.n_kb + pl.splits - 1) / pl.splits;
   const size_t a_bytes = BM * BK * 2, b_stride = (size_t(pl.bn) * BK * 2 + 1023) & ~size_t(1023);
-  const size_t fixed = 1024 + (2 * MAX_STAGES + 1) * 8 + 32 + size_t(pl.splits - 1) * pl.bn * BM * 4;
+  const size_t fixed = 1024 + (2 * MAX_STAGES + 2) * 8 + 32 + size_t(pl.splits - 1) * pl.bn * BM * 4;
   // with more tiles than SMs, leave room for two CTAs on an SM: one's epilogue under the other's loads
   const size_t budget = (tiles * pl.splits > N_SMS ? 113 * 1024 : 227 * 1024) - fixed;
+  if (fused_ln) {
+    // the normalised token tiles of the CTA's whole K share stay resident; the ring holds weights only
+    const size_t tokens = size_t(pl.kb_per_split) * b_stride;
+    int stages = tokens + a_bytes <= budget ? int((budget - tokens) / a_bytes) : 0;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > pl.kb_per_split) stages = pl.kb_per_split;
+    pl.stages = stages;  // 0: does not fit
+    pl.smem = fixed + tokens + size_t(stages) * a_bytes;
+    return pl;
+  }
   int stages = int(budget / (a_bytes + b_stride));
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > pl.kb_per_split) stages = pl.kb_per_split;
@@ -559,18 +650,36 @@ extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, in
 // x [m, k] bfloat16 (row stride lda), w [k, n] or [n, k] bfloat16 (row stride ldw), bias [n] float or null,
 // residual [m, n] float or null, out [m, n] bfloat16 or float. Returns R2_UNSUPPORTED for shapes
 // whose rows are not 16-byte multiples; the caller then uses the CUDA-core kernel.
+//
+// With ln_x != null the tokens are LayerNorm(ln_x[ln_rows[i]] or ln_x[i]) computed inside the kernel
+// (`x` is then ignored); this form takes at most 64 tokens and k <= 2048, else R2_UNSUPPORTED.
 extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_is_nk, const float* bias,
                           const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
-                          int out_dtype, int* error_flag, cudaStream_t stream) {
+                          int out_dtype, int* error_flag, const float* ln_x, int ln_ldx, const int32_t* ln_rows,
+                          const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return R2_OK;
+  const bool fused_ln = ln_x != nullptr;
+  if (fused_ln) {
+    if (m > 64 || k > LN_MAX_K || k % 8 != 0 || ln_ldx % 4 != 0 || ln_gamma == nullptr || ln_beta == nullptr) return R2_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(ln_x) & 15) || (reinterpret_cast<uintptr_t>(ln_gamma) & 15) || (reinterpret_cast<uintptr_t>(ln_beta) & 15)) return R2_UNSUPPORTED;
+    x = w;  // only its alignment is looked at below
+    lda = 8;
+  }
   if (k < 1) return R2_BAD_SHAPE;
   if (act < R2_ACT_NONE || act > R2_ACT_GELU_ERF) return R2_UNSUPPORTED;
   if (out_dtype != R2_F32 && out_dtype != R2_BF16) return R2_BAD_DTYPE;
   if (error_flag == nullptr) return R2_BAD_SHAPE;
   if (lda % 8 != 0 || ldw % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return R2_UNSUPPORTED;
   if (k % 8 != 0 || (!w_is_nk && n % 8 != 0)) return R2_UNSUPPORTED;
-  const Plan pl = make_plan(m, n, k, w_is_nk);
+  const Plan pl = make_plan(m, n, k, w_is_nk, fused_ln);
+  if (pl.stages < 1) return R2_UNSUPPORTED;
   GemmParams p;
+  p.ln_x = ln_x;
+  p.ln_ldx = ln_ldx;
+  p.ln_rows = ln_rows;
+  p.ln_gamma = ln_gamma;
+  p.ln_beta = ln_beta;
+  p.ln_eps = ln_eps;
   p.a_total = pl.a_total;
   p.b_total = pl.b_total;
   p.k_total = k;
@@ -606,7 +715,8 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
     return launch<false, true, false>(ma, mb, p, grid, smem, stream);
   }
   // swapped: a side = the weight's features, b side = tokens [m, k] K-major
-  ok = make_map(&mb, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, uint32_t(bn));
+  ok = fused_ln ? make_map(&mb, w, 64, 64, 64, BK, 16)  // a placeholder map: the kernel never uses it
+                : make_map(&mb, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, uint32_t(bn));
   if (w_is_nk) {
     ok = ok && make_map(&ma, w, uint64_t(k), uint64_t(n), uint64_t(ldw), BK, BM);
     if (!ok) return R2_UNSUPPORTED;

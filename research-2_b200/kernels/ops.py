@@ -118,6 +118,14 @@ def build_all() -> None:
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
+_fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
+
+
+def use_fused_norm(on: bool) -> bool:
+    """Switch the LayerNorm inside the matrix product's kernel (few rows, bfloat16) on or off."""
+    global _fused_norm
+    before, _fused_norm = _fused_norm, bool(on)
+    return before
 N_SMS = 148
 
 
@@ -232,11 +240,60 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: fl
     return out
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: bool = False,
+class NormedRows:
+    """LayerNorm of float32 rows that has not been computed yet: `linear` may compute it inside
+    its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel."""
+
+    def __init__(self, x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, dtype: torch.dtype,
+                 rows: torch.Tensor | None = None):
+        self.x, self.gamma, self.beta, self.eps, self.dtype, self.rows = x, gamma, beta, eps, dtype, rows
+        self.shape = (x.shape[0] if rows is None else rows.shape[0], x.shape[1])
+        self.device = x.device
+
+    def materialize(self) -> torch.Tensor:
+        return layer_norm(self.x, self.gamma, self.beta, self.eps, self.dtype, rows=self.rows)
+
+
+def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype, out):
+    """The fused form, or None when the kernel does not take the shape."""
+    m, k = a.shape
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    if not (_tensor_core_gemm and _fused_norm and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and m <= 64):
+        return None
+    if (w.shape[1] if w_is_nk else w.shape[0]) != k:
+        raise KernelError(f"linear: normed rows {a.shape} do not fit w {tuple(w.shape)} (w_is_nk={w_is_nk})")
+    _need(a.x, "x", torch.float32, 2)
+    if not a.x.is_contiguous():
+        return None
+    if out_dtype is None:
+        out_dtype = torch.float32 if residual is not None else a.dtype
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    ldr = _rows(residual, "residual") if residual is not None else 0
+    ws = _workspace(a.device)
+    status = _lib("gemm_tc").r2_gemm_tc(
+        None, 0, _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
+        ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _p(a.x), a.x.stride(0), _p(a.rows), _p(a.gamma),
+        _p(a.beta), C.c_float(a.eps), _stream())
+    if status == -4:
+        return None
+    _check(status, "linear (tensor cores, fused norm)")
+    return out
+
+
+def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: bool = False,
            act: str | None = None, residual: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None) -> torch.Tensor:
     """act(a @ w + bias) (+ residual). `w` is [K, N], or [N, K] with w_is_nk. `a` and `w`
-    share a dtype; bias and residual are float32; a float32 residual makes a float32 result."""
+    share a dtype; bias and residual are float32; a float32 residual makes a float32 result.
+    `a` may be NormedRows: the LayerNorm then runs inside the product's kernel where it can."""
+    if isinstance(a, NormedRows):
+        if act not in ACTIVATIONS:
+            raise KernelError(f"linear: unknown activation {act!r}; known: {sorted(k for k in ACTIVATIONS if k)}")
+        fused = _linear_of_normed(a, w, bias, w_is_nk, act, residual, out_dtype, out)
+        if fused is not None:
+            return fused
+        a = a.materialize()
     _need(a, "a", dim=2)
     _need(w, "w", a.dtype, 2)
     m, k = a.shape
@@ -266,7 +323,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *
         ws = _workspace(a.device)
         status = _lib("gemm_tc").r2_gemm_tc(
             _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
-            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _stream())
+            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0), _stream())
         if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
             _check(status, "linear (tensor cores)")
             return out

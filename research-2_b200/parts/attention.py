@@ -49,6 +49,7 @@ class PagedAttention:
 
     state_spec = None
     capturable = True  # nothing here depends on the batch's contents, only on its shape
+    takes_lazy_norm = True  # the input goes straight into ops.linear
 
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
         qkv = ops.linear(h, self.w_qkv, self.b_qkv)

@@ -16,7 +16,14 @@ class PreNormBlock:
         self.compute_dtype = compute_dtype
 
     def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
-        h = self.norm_1.forward(x, self.compute_dtype)
+        h = self._normed(self.norm_1, x, self.mixer)
         x = self.mixer.forward(h, x, ctx, cache, state, writes_cache)
-        h = self.norm_2.forward(x, self.compute_dtype)
+        h = self._normed(self.norm_2, x, self.feed_forward)
         return self.feed_forward.forward(h, x, ctx)
+
+    def _normed(self, norm, x, consumer):
+        """A part that says `takes_lazy_norm` gets the norm unevaluated and may fuse it into its
+        first matrix product; any other part gets a tensor."""
+        if getattr(consumer, "takes_lazy_norm", False) and getattr(norm, "can_be_lazy", False):
+            return norm.forward(x, self.compute_dtype, lazy=True)
+        return norm.forward(x, self.compute_dtype)

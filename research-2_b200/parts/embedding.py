@@ -30,5 +30,6 @@ class Head:
         self.norm, self.table, self.compute_dtype = norm, table, compute_dtype
 
     def forward(self, x, rows):
-        last = self.norm.forward(x, self.compute_dtype, rows=rows)
+        lazy = getattr(self.norm, "can_be_lazy", False)
+        last = self.norm.forward(x, self.compute_dtype, rows=rows, lazy=True) if lazy else self.norm.forward(x, self.compute_dtype, rows=rows)
         return ops.linear(last, self.table, None, w_is_nk=True, out_dtype=torch.float32)

@@ -24,6 +24,8 @@ class DenseMLP:
         if self.w_in.shape[1] != self.w_out.shape[0] or self.w_in.shape[0] != self.w_out.shape[1]:
             raise ValueError(f"mlp: w_in {tuple(self.w_in.shape)} and w_out {tuple(self.w_out.shape)} do not fit")
 
+    takes_lazy_norm = True  # the input goes straight into ops.linear
+
     def forward(self, h, residual, ctx):
         inner = ops.linear(h, self.w_in, self.b_in, act=self.activation)
         return ops.linear(inner, self.w_out, self.b_out, residual=residual)

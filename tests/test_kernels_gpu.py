@@ -81,6 +81,34 @@ def test_linear(m, k, n, dtype, w_is_nk):
     torch.testing.assert_close(got, base + bias + res, **(t if dtype == torch.float32 else dict(atol=2e-4, rtol=2e-4)))
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 768, 2304), (8, 768, 3072), (64, 768, 2304), (5, 96, 288), (33, 1600, 4800), (17, 320, 96)])
+@pytest.mark.parametrize("w_is_nk", [False, True])
+def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
+    """LayerNorm of a few float32 rows computed inside the tensor-core product's kernel: same
+    result as the LayerNorm kernel followed by the product, and as a plain float32 statement."""
+    o = ops()
+    torch.manual_seed(m + k)
+    x = (torch.randn(m + 3, k) * 2 + 0.5).to(DEV)
+    g, b = (1 + 0.1 * torch.randn(k)).to(DEV), (0.1 * torch.randn(k)).to(DEV)
+    w = ((torch.randn(n, k) if w_is_nk else torch.randn(k, n)) * k**-0.5).bfloat16().to(DEV)
+    bias = torch.randn(n).to(DEV)
+    rows = torch.randperm(m + 3)[:m].to(torch.int32).to(DEV)
+    for pick in (None, rows):
+        lazy = o.NormedRows(x, g, b, 1e-5, torch.bfloat16, rows=pick)
+        fused = o.linear(lazy, w, bias, w_is_nk=w_is_nk, act="gelu_new", out_dtype=torch.float32)
+        before = o.use_fused_norm(False)
+        try:
+            apart = o.linear(lazy, w, bias, w_is_nk=w_is_nk, act="gelu_new", out_dtype=torch.float32)
+        finally:
+            o.use_fused_norm(before)
+        src = x if pick is None else x[pick.long()]
+        h = F.layer_norm(src, (k,), g, b, 1e-5).bfloat16().float()
+        want = F.gelu(h @ (w.float().T if w_is_nk else w.float()) + bias, approximate="tanh")
+        torch.testing.assert_close(fused, want, atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(fused, apart, atol=2e-2, rtol=2e-2)
+    assert o.device_errors() == 0
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     """In float32 a row's result is the same bits alone and among other rows."""
     torch.manual_seed(0)
