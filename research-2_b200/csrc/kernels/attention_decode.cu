@@ -39,7 +39,30 @@ struct DecodeParams {
   int n_slices;
   float* part_o;   // [rows, n_heads, n_slices, HD]
   float* part_ml;  // [rows, n_heads, n_slices, 2]
+  // The fused form: the kernel itself puts the new token's key and value into the cache (the
+  // warp that owns the tile of the newest key does), and the slices of a (row, kv head) are
+  // the CTAs of a cluster whose leader merges them through distributed shared memory.
+  const bf16* k_new; const bf16* v_new; int new_row_stride;  // [rows, n_kv_heads * HD], or null
+  const int32_t* slot_mapping;
+  bf16* k_cache_w; bf16* v_cache_w;
+  int cluster_merge;
 };
+
+constexpr int CLUSTER_MAX_SLICES = 8;
+constexpr int CLUSTER_MAX_GHD = 512;  // query heads per kv head x head size that the leader's buffers hold
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void store_to_leader(const void* local, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(0u));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 
 template <int G>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -49,6 +72,10 @@ decode_kernel(const DecodeParams p) {
   __shared__ float q_s[G][HD];
   __shared__ float red_o[WARPS][G][HD];
   __shared__ float red_m[WARPS][G], red_l[WARPS][G];
+  // the leader's copy of every slice's state (cluster merge only)
+  constexpr int GHD = G * HD <= CLUSTER_MAX_GHD ? G * HD : 1;
+  __shared__ float cl_o[CLUSTER_MAX_SLICES][GHD];
+  __shared__ float cl_m[CLUSTER_MAX_SLICES][G], cl_l[CLUSTER_MAX_SLICES][G];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int h0 = kvh * G;
@@ -56,19 +83,20 @@ decode_kernel(const DecodeParams p) {
   if (e < 0) {  // a pad row: zeros, and empty partials
     for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
       int g = i / HD, d = i % HD;
-      if (p.n_slices == 1) {
-        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(0.f);
+      if (p.n_slices == 1 || p.cluster_merge) {
+        if (slice == 0) p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(0.f);
       } else {
         p.part_o[((size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice) * HD + d] = 0.f;
       }
     }
-    if (p.n_slices > 1 && threadIdx.x < G) {
+    if (p.n_slices > 1 && !p.cluster_merge && threadIdx.x < G) {
       float* ml = p.part_ml + ((size_t(t) * p.n_heads + h0 + threadIdx.x) * p.n_slices + slice) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
     return;
   }
+  if (p.n_slices > 1 && p.cluster_merge) cluster_sync_all();  // every CTA of the cluster runs before any writes into the leader
   const int pos = p.positions[t];
   const int seq_len = p.seq_lens[e];
   const int last = pos < seq_len - 1 ? pos : seq_len - 1;
@@ -97,8 +125,27 @@ decode_kernel(const DecodeParams p) {
   }
   const size_t head_off = size_t(kvh) * p.page_size * HD;
 
+  const int tile_of_new = (p.k_new != nullptr && pos == last) ? (pos - first) / 32 : -1;
   for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS) {
     const int j0 = first + tile * 32;
+    if (tile == tile_of_new) {
+      // the newest key lies in this tile: its key and value go from the projection's output to
+      // their cache slot first; this warp alone reads that slot in this kernel
+      const int slot = p.slot_mapping[t];
+      const int page = slot / p.page_size;
+      if (slot >= 0 && page < p.n_pages) {
+        const size_t dst = size_t(page) * p.page_stride + size_t(kvh) * p.page_size * HD + size_t(slot % p.page_size) * HD;
+        const __nv_bfloat162* ks = reinterpret_cast<const __nv_bfloat162*>(p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD);
+        const __nv_bfloat162* vs = reinterpret_cast<const __nv_bfloat162*>(p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD);
+        __nv_bfloat162* kd = reinterpret_cast<__nv_bfloat162*>(p.k_cache_w + dst);
+        __nv_bfloat162* vd = reinterpret_cast<__nv_bfloat162*>(p.v_cache_w + dst);
+        for (int i = lane; i < HD / 2; i += 32) {
+          kd[i] = ks[i];
+          vd[i] = vs[i];
+        }
+      }
+      __syncwarp();
+    }
     const int j = j0 + lane;
     const bool valid = j <= last;
     float s[G];
@@ -116,7 +163,7 @@ decode_kernel(const DecodeParams p) {
       for (int c0 = 0; c0 < VECS; c0 += CH) {
         uint4 kv[CH];
 #pragma unroll
-        for (int c = 0; c < CH; ++c) kv[c] = (c0 + c < VECS) ? __ldg(kr + c0 + c) : make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < CH; ++c) kv[c] = (c0 + c < VECS) ? kr[c0 + c] : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
           if (c0 + c >= VECS) continue;
@@ -214,12 +261,37 @@ decode_kernel(const DecodeParams p) {
     }
     if (p.n_slices == 1) {
       p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
+    } else if (p.cluster_merge) {
+      store_to_leader(&cl_o[slice][i % GHD], o);
+      if (d == 0) {
+        store_to_leader(&cl_m[slice][g], mx);
+        store_to_leader(&cl_l[slice][g], lsum);
+      }
     } else {
       size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
       p.part_o[at * HD + d] = o;
       if (d == 0) {
         p.part_ml[at * 2] = mx;
         p.part_ml[at * 2 + 1] = lsum;
+      }
+    }
+  }
+  if (p.n_slices > 1 && p.cluster_merge) {
+    cluster_sync_all();  // every slice's state has landed in the leader
+    if (slice == 0) {
+      for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+        int g = i / HD, d = i % HD;
+        float mx = -INFINITY;
+        for (int s = 0; s < p.n_slices; ++s) mx = fmaxf(mx, cl_m[s][g]);
+        float o = 0.f, lsum = 0.f;
+        if (mx > -INFINITY) {
+          for (int s = 0; s < p.n_slices; ++s) {  // slices in order: the same bits every run
+            float c = __expf(cl_m[s][g] - mx);
+            o += c * cl_o[s][i % GHD];
+            lsum += c * cl_l[s][g];
+          }
+        }
+        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
       }
     }
   }
@@ -284,6 +356,8 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   p.scale = scale; p.window = window; p.n_slices = n_slices;
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
+  p.k_new = nullptr; p.v_new = nullptr; p.new_row_stride = 0; p.slot_mapping = nullptr;
+  p.k_cache_w = nullptr; p.v_cache_w = nullptr; p.cluster_merge = 0;
   int status;
   switch (n_heads / n_kv_heads) {
     case 1: status = launch<1>(p, n_rows, stream); break;
@@ -295,6 +369,80 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   if (status != R2_OK || n_slices == 1) return status;
   r2_launch(merge_kernel, dim3(dim3(n_heads, n_rows)), dim3(HD >= 128 ? 128 : 64), size_t(0), stream, p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
   return launch_status();
+}
+
+namespace {
+
+template <int G>
+int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(p.n_slices, p.n_kv_heads, n_rows);
+  config.blockDim = dim3(WARPS * 32);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (p.n_slices > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = unsigned(p.n_slices);
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (g_r2_pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  config.attrs = attr;
+  config.numAttrs = n_attr;
+  cudaLaunchKernelEx(&config, decode_kernel<G>, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// One launch for a decode-only batch: the new tokens' keys and values (k_new, v_new:
+// [rows, n_kv_heads * HD] with row stride new_row_stride) are written to their cache slots by
+// the kernel itself, and the 1, 2, 4 or 8 slices of a (row, kv head) are merged by the leader of
+// a thread-block cluster, so there is neither a separate cache-write kernel nor a merge kernel
+// nor scratch memory. Needs (n_heads / n_kv_heads) * HD <= 512 when n_slices > 1.
+extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
+                                         void* v_cache, long long page_stride, int page_size, int n_pages,
+                                         const int32_t* block_tables, int table_width, const int32_t* row_entry,
+                                         const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
+                                         int n_kv_heads, float scale, int window, int n_slices, const void* k_new,
+                                         const void* v_new, int new_row_stride, const int32_t* slot_mapping,
+                                         cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
+  if (n_slices != 1 && n_slices != 2 && n_slices != 4 && n_slices != 8) return R2_UNSUPPORTED;
+  const int group = n_heads / n_kv_heads;
+  if (n_slices > 1 && group * HD > CLUSTER_MAX_GHD) return R2_UNSUPPORTED;
+  if (page_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)) return R2_BAD_ALIGN;
+  if (k_new != nullptr && (v_new == nullptr || slot_mapping == nullptr || new_row_stride % 2 != 0 ||
+                           (reinterpret_cast<uintptr_t>(k_new) & 3) || (reinterpret_cast<uintptr_t>(v_new) & 3))) return R2_BAD_ALIGN;
+  DecodeParams p;
+  p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
+  p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.page_stride = page_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.block_tables = block_tables; p.table_width = table_width;
+  p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
+  p.scale = scale; p.window = window; p.n_slices = n_slices;
+  p.part_o = nullptr; p.part_ml = nullptr;
+  p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.new_row_stride = new_row_stride;
+  p.slot_mapping = slot_mapping;
+  p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
+  p.cluster_merge = 1;
+  switch (group) {
+    case 1: return launch_fused<1>(p, n_rows, stream);
+    case 2: return launch_fused<2>(p, n_rows, stream);
+    case 4: return launch_fused<4>(p, n_rows, stream);
+    case 8: return launch_fused<8>(p, n_rows, stream);
+    default: return R2_UNSUPPORTED;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -141,55 +141,73 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
 
 // LayerNorm of the token rows, written as the K-major, 128-byte-swizzled bfloat16 tiles that the
 // tensor core reads: warp `w` of the four takes rows w, w + 4, ...; a lane holds every 32nd group
-// of four elements of its row; mean and variance are two passes over registers, in float
+// of four elements of its row (rows of at most 1,024 elements, at most 16 tokens); mean and
+// variance are two passes over registers, in float
 // (kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23). Rows past the last token are zeros.
-constexpr int LN_MAX_K = 2048;
+constexpr int LN_MAX_K = 1024;
+constexpr int LN_MAX_TOKENS = 16;
+constexpr int LN_CHUNKS = LN_MAX_K / 128;
 
 __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t* b_tiles, uint32_t b_stride, int kb_begin,
                                                     int n_kb, int w, int lane) {
   const int k_total = p.k_total;
-  const int k_lo = kb_begin * BK, k_hi = min(k_total, (kb_begin + n_kb) * BK);
-  for (int r = w; r < p.bn; r += 4) {
-    float4 v[LN_MAX_K / 128];
-    float mean = 0.f, rstd = 0.f;
-    const bool live = r < p.b_total;
-    if (live) {
-      const int src = p.ln_rows != nullptr ? p.ln_rows[r] : r;
+  const int k_lo = kb_begin * BK, k_end = (kb_begin + n_kb) * BK, k_hi = min(k_total, k_end);
+  // gain and shift for the lane's elements inside this CTA's share of K, fetched once
+  float4 gam[LN_CHUNKS], bet[LN_CHUNKS];
+#pragma unroll
+  for (int i = 0; i < LN_CHUNKS; ++i) {
+    int k = (lane + 32 * i) * 4;
+    bool mine = k >= k_lo && k < k_hi;
+    gam[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_gamma + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bet[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_beta + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int r0 = w; r0 < p.bn; r0 += 8) {  // two rows at a time: both rows' loads are in flight together
+    float4 v[2][LN_CHUNKS];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int r = r0 + 4 * u;
+      live[u] = r < p.b_total;
+      const int src = live[u] ? (p.ln_rows != nullptr ? p.ln_rows[r] : r) : 0;
       const float4* row = reinterpret_cast<const float4*>(p.ln_x + size_t(src) * p.ln_ldx);
+#pragma unroll
+      for (int i = 0; i < LN_CHUNKS; ++i) {
+        int k = (lane + 32 * i) * 4;
+        v[u][i] = (live[u] && k < k_total) ? row[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int r = r0 + 4 * u;
+      if (r >= p.bn) continue;
       float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
-        int k = (lane + 32 * i) * 4;
-        v[i] = k < k_total ? row[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        sum += v[i].x + v[i].y + v[i].z + v[i].w;
-      }
-      mean = warp_sum(sum) / float(k_total);
+      for (int i = 0; i < LN_CHUNKS; ++i) sum += v[u][i].x + v[u][i].y + v[u][i].z + v[u][i].w;
+      const float mean = warp_sum(sum) / float(k_total);
       float sq = 0.f;
 #pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+      for (int i = 0; i < LN_CHUNKS; ++i) {
         int k = (lane + 32 * i) * 4;
         if (k < k_total) {
-          float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+          float a = v[u][i].x - mean, b = v[u][i].y - mean, c = v[u][i].z - mean, d = v[u][i].w - mean;
           sq += a * a + b * b + c * c + d * d;
         }
       }
-      rstd = 1.f / sqrtf(warp_sum(sq) / float(k_total) + p.ln_eps);
-    }
+      const float rstd = 1.f / sqrtf(warp_sum(sq) / float(k_total) + p.ln_eps);
 #pragma unroll
-    for (int i = 0; i < LN_MAX_K / 128; ++i) {
-      int k = (lane + 32 * i) * 4;
-      if (k < k_lo || k >= (kb_begin + n_kb) * BK) continue;  // another CTA's share of K, or past the tiles
-      uint32_t lo = 0u, hi = 0u;
-      if (live && k < k_hi) {
-        float4 g = *reinterpret_cast<const float4*>(p.ln_gamma + k);
-        float4 b = *reinterpret_cast<const float4*>(p.ln_beta + k);
-        lo = pack2((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y);
-        hi = pack2((v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+      for (int i = 0; i < LN_CHUNKS; ++i) {
+        int k = (lane + 32 * i) * 4;
+        if (k < k_lo || k >= k_end) continue;  // another CTA's share of K, or past the tiles
+        uint32_t lo = 0u, hi = 0u;
+        if (live[u] && k < k_hi) {
+          lo = pack2((v[u][i].x - mean) * rstd * gam[i].x + bet[i].x, (v[u][i].y - mean) * rstd * gam[i].y + bet[i].y);
+          hi = pack2((v[u][i].z - mean) * rstd * gam[i].z + bet[i].z, (v[u][i].w - mean) * rstd * gam[i].w + bet[i].w);
+        }
+        const int kb = k / BK - kb_begin, kin = k % BK;
+        uint8_t* tile = b_tiles + size_t(kb) * b_stride;
+        uint32_t off = uint32_t(r / 8) * 1024u + uint32_t(r % 8) * 128u + (uint32_t((kin / 8) ^ (r % 8)) * 16u) + uint32_t(kin % 8) * 2u;
+        *reinterpret_cast<uint2*>(tile + off) = make_uint2(lo, hi);
       }
-      const int kb = k / BK - kb_begin, kin = k % BK;
-      uint8_t* tile = b_tiles + size_t(kb) * b_stride;
-      uint32_t off = uint32_t(r / 8) * 1024u + uint32_t(r % 8) * 128u + (uint32_t((kin / 8) ^ (r % 8)) * 16u) + uint32_t(kin % 8) * 2u;
-      *reinterpret_cast<uint2*>(tile + off) = make_uint2(lo, hi);
     }
   }
 }
@@ -652,7 +670,7 @@ extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, in
 // whose rows are not 16-byte multiples; the caller then uses the CUDA-core kernel.
 //
 // With ln_x != null the tokens are LayerNorm(ln_x[ln_rows[i]] or ln_x[i]) computed inside the kernel
-// (`x` is then ignored); this form takes at most 64 tokens and k <= 2048, else R2_UNSUPPORTED.
+// (`x` is then ignored); this form takes at most 16 tokens and k <= 1024, else R2_UNSUPPORTED.
 extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_is_nk, const float* bias,
                           const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
                           int out_dtype, int* error_flag, const float* ln_x, int ln_ldx, const int32_t* ln_rows,
@@ -660,7 +678,7 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   if (m <= 0 || n <= 0) return R2_OK;
   const bool fused_ln = ln_x != nullptr;
   if (fused_ln) {
-    if (m > 64 || k > LN_MAX_K || k % 8 != 0 || ln_ldx % 4 != 0 || ln_gamma == nullptr || ln_beta == nullptr) return R2_UNSUPPORTED;
+    if (m > LN_MAX_TOKENS || k > LN_MAX_K || k % 8 != 0 || ln_ldx % 4 != 0 || ln_gamma == nullptr || ln_beta == nullptr) return R2_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(ln_x) & 15) || (reinterpret_cast<uintptr_t>(ln_gamma) & 15) || (reinterpret_cast<uintptr_t>(ln_beta) & 15)) return R2_UNSUPPORTED;
     x = w;  // only its alignment is looked at below
     lda = 8;

@@ -119,6 +119,14 @@ def build_all() -> None:
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
 _fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
+_fused_decode = os.environ.get("R2_FUSED_DECODE", "1") != "0"
+
+
+def use_fused_decode_attention(on: bool) -> bool:
+    """Switch the one-launch decode attention (cache write and slice merge inside) on or off."""
+    global _fused_decode
+    before, _fused_decode = _fused_decode, bool(on)
+    return before
 
 
 def use_fused_norm(on: bool) -> bool:
@@ -258,7 +266,7 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
     """The fused form, or None when the kernel does not take the shape."""
     m, k = a.shape
     n = w.shape[0] if w_is_nk else w.shape[1]
-    if not (_tensor_core_gemm and _fused_norm and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and m <= 64):
+    if not (_tensor_core_gemm and _fused_norm and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and m <= 16 and k <= 1024):
         return None
     if (w.shape[1] if w_is_nk else w.shape[0]) != k:
         raise KernelError(f"linear: normed rows {a.shape} do not fit w {tuple(w.shape)} (w_is_nk={w_is_nk})")
@@ -412,6 +420,44 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
         n_kv_heads, head_dim, C.c_float(scale), window, n_pages, dtype_code(q.dtype), _stream())
     _check(status, "paged_attention")
+    return out
+
+
+def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, slot_mapping: torch.Tensor,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int, n_pages: int,
+                           block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
+                           seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                           window: int, max_context: int) -> torch.Tensor | None:
+    """Decode attention in ONE launch for a batch in which every row is an entry of its own: the
+    kernel writes the new keys and values to their cache slots and merges its slices inside a
+    thread-block cluster. Returns None when it does not take the case (the caller then writes
+    the cache and calls `paged_attention`)."""
+    group = n_heads // max(n_kv_heads, 1)
+    if not (_fast_attention and _fused_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and group in (1, 2, 4, 8) and head_dim % 16 == 0):
+        return None
+    _need(q, "q", dim=2)
+    _need(k_new, "k_new", torch.bfloat16, 2)
+    _need(v_new, "v_new", torch.bfloat16, 2)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    _need(block_tables, "block_tables", torch.int32, 2)
+    n = q.shape[0]
+    stride = _rows(k_new, "k_new")
+    if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
+        raise KernelError("decode attention: the new keys and values do not fit the rows")
+    slices = decode_slices(n, n_kv_heads, max_context)
+    slices = 8 if slices >= 8 else 4 if slices >= 4 else 2 if slices >= 2 else 1
+    if slices > 1 and group * head_dim > 512:
+        slices = 1
+    out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
+    lib = _lib_for_head_dim("attention_decode", head_dim)
+    status = lib.r2_attention_decode_fused(
+        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride), page_size,
+        n_pages, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
+        n_kv_heads, C.c_float(scale), window, slices, _p(k_new), _p(v_new), stride, _p(slot_mapping), _stream())
+    if status == -4:
+        return None
+    _check(status, "decode attention (fused)")
     return out
 
 

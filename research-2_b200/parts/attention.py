@@ -58,6 +58,13 @@ class PagedAttention:
         v = qkv[:, self.q_width + self.kv_width:]
         if self.rotary is not None:
             self.rotary.rotate(q, k, ctx)
+        if writes_cache and ctx.decode_only:
+            mixed = ops.decode_attention_fused(
+                q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
+                cache.n_pages, ctx.block_tables[cache.group], ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads,
+                self.n_kv_heads, self.head_dim, self.scale, self.window, ctx.max_context)
+            if mixed is not None:
+                return ops.linear(mixed, self.w_out, self.b_out, residual=residual)
         if writes_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages)

@@ -274,6 +274,27 @@ def test_decode_attention(case, window, sliced):
     torch.testing.assert_close(got, general, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in DECODE_CASES])
+@pytest.mark.parametrize("window", [0, 40])
+@pytest.mark.parametrize("max_context", [64, 300, 4096])
+def test_decode_attention_in_one_launch(case, window, max_context):
+    """The fused form: the kernel writes the new keys and values itself and merges 1, 2, 4 or 8
+    slices inside a cluster. The cache must afterwards hold the new token."""
+    contexts, h, hkv, hd, page = case
+    pc = PagedCase([(c, 1) for c in contexts], h, hkv, hd, page, torch.bfloat16, seed=hd + page + window + 1)
+    scale = hd**-0.5
+    o = ops()
+    got = o.decode_attention_fused(pc.q_rows, pc.k_new, pc.v_new, pc.slots, pc.k_cache, pc.v_cache, pc.page_stride,
+                                   pc.page, pc.n_pages, pc.tables, pc.row_entry, pc.positions, pc.seq_lens, h, hkv, hd,
+                                   scale, window, max_context)
+    assert got is not None
+    torch.testing.assert_close(got.float().cpu(), pc.plain(scale, window), atol=3e-2, rtol=3e-2)
+    # the cache now holds the new keys and values: the general kernel reads them back
+    again = o.paged_attention(pc.q_rows, pc.k_cache, pc.v_cache, pc.page_stride, pc.page, pc.n_pages, pc.tables,
+                              pc.row_entry, pc.positions, pc.seq_lens, h, hkv, hd, scale, window)
+    torch.testing.assert_close(again.float(), got.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_decode_slices_choice():
     o = ops()
     assert o.decode_slices(64, 12, 1024) == 1
