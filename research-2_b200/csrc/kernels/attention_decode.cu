@@ -25,6 +25,9 @@ constexpr int HD = HEAD_DIM;
 constexpr int WARPS = 4;
 constexpr int VECS = HD / 8;                 // 16-byte pieces of a key row
 constexpr int DPL = (HD + 63) / 64;          // pairs of head-dimension elements per lane in p.v
+constexpr int ROW_BYTES = HD * 2 + 16;       // a key's row in shared memory, padded against bank conflicts
+constexpr int NBUF = HD <= 128 ? 2 : 1;      // tiles in flight per warp
+constexpr int TILE_SMEM = WARPS * NBUF * 2 * 32 * ROW_BYTES;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head sizes come in steps of 16 up to 256");
 
 struct DecodeParams {
@@ -125,12 +128,49 @@ decode_kernel(const DecodeParams p) {
   }
   const size_t head_off = size_t(kvh) * p.page_size * HD;
 
+  // Tiles of 32 keys go through shared memory: every lane copies its own key's K row and V row
+  // with 16-byte asynchronous copies, so a tile's 2 x 32 rows are all in flight at once, and
+  // (for head sizes up to 128) the next tile is on its way while this one is used. The newest
+  // key's row comes from the projection's output (k_new, v_new), not from the cache.
+  extern __shared__ __align__(16) uint8_t tile_smem[];
+  uint8_t* my_smem = tile_smem + size_t(warp) * NBUF * 2 * 32 * ROW_BYTES;
   const int tile_of_new = (p.k_new != nullptr && pos == last) ? (pos - first) / 32 : -1;
-  for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS) {
+
+  auto issue = [&](int tile, int buf) {
+    const int j = first + tile * 32 + lane;
+    const bool valid = j <= last;
+    const bf16* ksrc = p.k_cache;
+    const bf16* vsrc = p.v_cache;
+    if (valid) {
+      if (tile == tile_of_new && j == pos) {
+        ksrc = p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD;
+        vsrc = p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD;
+      } else {
+        int page = table[j / p.page_size];
+        page = (page < 0 || page >= p.n_pages) ? 0 : page;
+        size_t off = size_t(page) * p.page_stride + head_off + size_t(j % p.page_size) * HD;
+        ksrc += off;
+        vsrc += off;
+      }
+    }
+    const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES + lane * ROW_BYTES);
+    const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES + lane * ROW_BYTES);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: zeros
+#pragma unroll
+    for (int c = 0; c < VECS; ++c) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd + c * 16), "l"(ksrc + c * 8), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd + c * 16), "l"(vsrc + c * 8), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  if (tile_begin + warp < tile_end) issue(tile_begin + warp, 0);
+  int it = 0;
+  for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS, ++it) {
     const int j0 = first + tile * 32;
+    const int buf = NBUF == 2 ? (it & 1) : 0;
     if (tile == tile_of_new) {
-      // the newest key lies in this tile: its key and value go from the projection's output to
-      // their cache slot first; this warp alone reads that slot in this kernel
+      // the newest key lies in this tile: this warp also puts its key and value into the cache
       const int slot = p.slot_mapping[t];
       const int page = slot / p.page_size;
       if (slot >= 0 && page < p.n_pages) {
@@ -144,38 +184,38 @@ decode_kernel(const DecodeParams p) {
           vd[i] = vs[i];
         }
       }
-      __syncwarp();
     }
+    if (NBUF == 2) {
+      if (tile + WARPS < tile_end) {
+        issue(tile + WARPS, buf ^ 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncwarp();
+    const uint8_t* k_tile = my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES;
+    const uint8_t* v_tile = my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES;
     const int j = j0 + lane;
     const bool valid = j <= last;
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) s[g] = 0.f;
-    // the lane's own key: its page and the element offset of its row inside the layer's pages
-    long long row_off = 0;
-    if (valid) {
-      int page = table[j / p.page_size];
-      page = (page < 0 || page >= p.n_pages) ? 0 : page;
-      row_off = (long long)page * p.page_stride + (long long)head_off + (long long)(j % p.page_size) * HD;
-      const uint4* kr = reinterpret_cast<const uint4*>(p.k_cache + row_off);
-      constexpr int CH = VECS < 8 ? VECS : 8;  // 16-byte pieces in flight at a time
+    {
+      const uint4* kr = reinterpret_cast<const uint4*>(k_tile + lane * ROW_BYTES);
 #pragma unroll
-      for (int c0 = 0; c0 < VECS; c0 += CH) {
-        uint4 kv[CH];
+      for (int c = 0; c < VECS; ++c) {
+        uint4 kv = kr[c];
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) kv[c] = (c0 + c < VECS) ? kr[c0 + c] : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < 4; ++u) {
+          float2 kf = __bfloat1622float2(k2[u]);
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          if (c0 + c >= VECS) continue;
-          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv[c]);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float2 kf = __bfloat1622float2(k2[u]);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              s[g] = fmaf(q_s[g][(c0 + c) * 8 + 2 * u], kf.x, s[g]);
-              s[g] = fmaf(q_s[g][(c0 + c) * 8 + 2 * u + 1], kf.y, s[g]);
-            }
+          for (int g = 0; g < G; ++g) {
+            s[g] = fmaf(q_s[g][c * 8 + 2 * u], kf.x, s[g]);
+            s[g] = fmaf(q_s[g][c * 8 + 2 * u + 1], kf.y, s[g]);
           }
         }
       }
@@ -195,38 +235,34 @@ decode_kernel(const DecodeParams p) {
         acc[g][i][1] *= corr;
       }
     }
-    // p.v: keys in groups of eight, all eight rows' loads issued before the first is used.
-    // Lanes beyond the last key hold p = 0 and borrow lane 0's row, so every load is in bounds.
-    const long long safe_off = __shfl_sync(0xffffffffu, row_off, 0);
-    const long long my_off = valid ? row_off : safe_off;
-    const int n_valid = min(32, last - j0 + 1);
-#pragma unroll 1
-    for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
-      float2 vv[8][DPL];
+    // p.v from shared memory: lanes over the head dimension, keys in turn (rows past the last key are zeros)
+#pragma unroll 8
+    for (int jj = 0; jj < 32; ++jj) {
+      const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(v_tile + jj * ROW_BYTES);
+      float2 vv[DPL];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const long long off = __shfl_sync(0xffffffffu, my_off, jj0 + u);
-        const __nv_bfloat162* vr = reinterpret_cast<const __nv_bfloat162*>(p.v_cache + off);
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-          int pair = lane + 32 * i;
-          vv[u][i] = (HD % 64 == 0 || 2 * pair < HD) ? __bfloat1622float2(vr[pair]) : make_float2(0.f, 0.f);
-        }
+      for (int i = 0; i < DPL; ++i) {
+        int pair = lane + 32 * i;
+        vv[i] = (HD % 64 == 0 || 2 * pair < HD) ? __bfloat1622float2(vr[pair]) : make_float2(0.f, 0.f);
       }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int g = 0; g < G; ++g) {
+        float pj = __shfl_sync(0xffffffffu, pr[g], jj);
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float pj = __shfl_sync(0xffffffffu, pr[g], jj0 + u);
-#pragma unroll
-          for (int i = 0; i < DPL; ++i) {
-            acc[g][i][0] = fmaf(pj, vv[u][i].x, acc[g][i][0]);
-            acc[g][i][1] = fmaf(pj, vv[u][i].y, acc[g][i][1]);
-          }
+        for (int i = 0; i < DPL; ++i) {
+          acc[g][i][0] = fmaf(pj, vv[i].x, acc[g][i][0]);
+          acc[g][i][1] = fmaf(pj, vv[i].y, acc[g][i][1]);
         }
       }
     }
+    if (NBUF == 1) {
+      __syncwarp();
+      if (tile + WARPS < tile_end) issue(tile + WARPS, 0);
+    } else {
+      __syncwarp();  // the buffer may be overwritten by the copy after next
+    }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // merge the four warps' states
 #pragma unroll
@@ -319,10 +355,22 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   }
 }
 
+template <typename K>
+bool configure_smem(K kernel) {
+  // once per kernel instance: room for the tiles beyond the default 48 KB
+  static bool done = false;
+  if (!done) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
+    done = true;
+  }
+  return true;
+}
+
 template <int G>
 int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
-  r2_launch(decode_kernel<G>, dim3(grid), dim3(WARPS * 32), size_t(0), stream, p);
+  if (!configure_smem(decode_kernel<G>)) return R2_UNSUPPORTED;
+  r2_launch(decode_kernel<G>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
   return launch_status();
 }
 
@@ -378,7 +426,8 @@ int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(p.n_slices, p.n_kv_heads, n_rows);
   config.blockDim = dim3(WARPS * 32);
-  config.dynamicSmemBytes = 0;
+  if (!configure_smem(decode_kernel<G>)) return R2_UNSUPPORTED;
+  config.dynamicSmemBytes = TILE_SMEM;
   config.stream = stream;
   cudaLaunchAttribute attr[2];
   int n_attr = 0;

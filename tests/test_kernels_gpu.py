@@ -95,9 +95,10 @@ def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
     rows = torch.randperm(m + 3)[:m].to(torch.int32).to(DEV)
     for pick in (None, rows):
         lazy = o.NormedRows(x, g, b, 1e-5, torch.bfloat16, rows=pick)
-        fused = o.linear(lazy, w, bias, w_is_nk=w_is_nk, act="gelu_new", out_dtype=torch.float32)
-        before = o.use_fused_norm(False)
+        before = o.use_fused_norm(True)
         try:
+            fused = o.linear(lazy, w, bias, w_is_nk=w_is_nk, act="gelu_new", out_dtype=torch.float32)
+            o.use_fused_norm(False)
             apart = o.linear(lazy, w, bias, w_is_nk=w_is_nk, act="gelu_new", out_dtype=torch.float32)
         finally:
             o.use_fused_norm(before)
