@@ -26,7 +26,7 @@ constexpr int WARPS = 4;
 constexpr int VECS = HD / 8;                 // 16-byte pieces of a key row
 constexpr int DPL = (HD + 63) / 64;          // pairs of head-dimension elements per lane in p.v
 constexpr int ROW_BYTES = HD * 2 + 16;       // a key's row in shared memory, padded against bank conflicts
-constexpr int NBUF = HD <= 128 ? 2 : 1;      // tiles in flight per warp
+constexpr int NBUF = 1;                      // tiles in flight per warp; other warps' work hides the wait
 constexpr int TILE_SMEM = WARPS * NBUF * 2 * 32 * ROW_BYTES;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head sizes come in steps of 16 up to 256");
 
@@ -43,29 +43,15 @@ struct DecodeParams {
   float* part_o;   // [rows, n_heads, n_slices, HD]
   float* part_ml;  // [rows, n_heads, n_slices, 2]
   // The fused form: the kernel itself puts the new token's key and value into the cache (the
-  // warp that owns the tile of the newest key does), and the slices of a (row, kv head) are
-  // the CTAs of a cluster whose leader merges them through distributed shared memory.
+  // warp that owns the tile of the newest key does), and the CTA that finishes last among the
+  // slices of a (row, kv head) merges them (arrival counters in global memory, reset after use).
   const bf16* k_new; const bf16* v_new; int new_row_stride;  // [rows, n_kv_heads * HD], or null
   const int32_t* slot_mapping;
   bf16* k_cache_w; bf16* v_cache_w;
-  int cluster_merge;
+  int* counters;  // [rows, n_kv_heads], zero between launches; null: a separate merge kernel follows
 };
 
-constexpr int CLUSTER_MAX_SLICES = 8;
-constexpr int CLUSTER_MAX_GHD = 512;  // query heads per kv head x head size that the leader's buffers hold
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void store_to_leader(const void* local, float v) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(0u));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
 
 template <int G>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -75,10 +61,7 @@ decode_kernel(const DecodeParams p) {
   __shared__ float q_s[G][HD];
   __shared__ float red_o[WARPS][G][HD];
   __shared__ float red_m[WARPS][G], red_l[WARPS][G];
-  // the leader's copy of every slice's state (cluster merge only)
-  constexpr int GHD = G * HD <= CLUSTER_MAX_GHD ? G * HD : 1;
-  __shared__ float cl_o[CLUSTER_MAX_SLICES][GHD];
-  __shared__ float cl_m[CLUSTER_MAX_SLICES][G], cl_l[CLUSTER_MAX_SLICES][G];
+  __shared__ int is_last_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int h0 = kvh * G;
@@ -86,20 +69,19 @@ decode_kernel(const DecodeParams p) {
   if (e < 0) {  // a pad row: zeros, and empty partials
     for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
       int g = i / HD, d = i % HD;
-      if (p.n_slices == 1 || p.cluster_merge) {
+      if (p.n_slices == 1 || p.counters != nullptr) {
         if (slice == 0) p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(0.f);
       } else {
         p.part_o[((size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice) * HD + d] = 0.f;
       }
     }
-    if (p.n_slices > 1 && !p.cluster_merge && threadIdx.x < G) {
+    if (p.n_slices > 1 && p.counters == nullptr && threadIdx.x < G) {
       float* ml = p.part_ml + ((size_t(t) * p.n_heads + h0 + threadIdx.x) * p.n_slices + slice) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
     return;
   }
-  if (p.n_slices > 1 && p.cluster_merge) cluster_sync_all();  // every CTA of the cluster runs before any writes into the leader
   const int pos = p.positions[t];
   const int seq_len = p.seq_lens[e];
   const int last = pos < seq_len - 1 ? pos : seq_len - 1;
@@ -137,29 +119,37 @@ decode_kernel(const DecodeParams p) {
   const int tile_of_new = (p.k_new != nullptr && pos == last) ? (pos - first) / 32 : -1;
 
   auto issue = [&](int tile, int buf) {
-    const int j = first + tile * 32 + lane;
-    const bool valid = j <= last;
-    const bf16* ksrc = p.k_cache;
-    const bf16* vsrc = p.v_cache;
-    if (valid) {
-      if (tile == tile_of_new && j == pos) {
-        ksrc = p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD;
-        vsrc = p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD;
+    // lane r finds row r's place once; then consecutive lanes copy consecutive 16-byte pieces of
+    // a row, then the next row: whole lines per request
+    const int j0 = first + tile * 32;
+    long long my_k, my_v;  // element offsets from k_cache / v_cache; -1 for a row past the last key
+    {
+      const int j = j0 + lane;
+      if (j > last) {
+        my_k = my_v = -1;
+      } else if (tile == tile_of_new && j == pos) {
+        my_k = (p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.k_cache;
+        my_v = (p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.v_cache;
       } else {
         int page = table[j / p.page_size];
         page = (page < 0 || page >= p.n_pages) ? 0 : page;
-        size_t off = size_t(page) * p.page_stride + head_off + size_t(j % p.page_size) * HD;
-        ksrc += off;
-        vsrc += off;
+        my_k = my_v = (long long)(size_t(page) * p.page_stride + head_off + size_t(j % p.page_size) * HD);
       }
     }
-    const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES + lane * ROW_BYTES);
-    const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES + lane * ROW_BYTES);
-    const int bytes = valid ? 16 : 0;  // 0 source bytes: zeros
+    const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
+    const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES);
 #pragma unroll
-    for (int c = 0; c < VECS; ++c) {
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd + c * 16), "l"(ksrc + c * 8), "r"(bytes) : "memory");
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd + c * 16), "l"(vsrc + c * 8), "r"(bytes) : "memory");
+    for (int i = 0; i < VECS; ++i) {
+      const int f = lane + 32 * i;
+      const int row = f / VECS, c = f % VECS;
+      const long long ko = __shfl_sync(0xffffffffu, my_k, row);
+      const long long vo = __shfl_sync(0xffffffffu, my_v, row);
+      const bool valid = ko >= 0 || (tile == tile_of_new && j0 + row == pos);
+      const int bytes = valid ? 16 : 0;  // 0 source bytes: zeros
+      const bf16* ksrc = valid ? p.k_cache + ko + c * 8 : p.k_cache;
+      const bf16* vsrc = valid ? p.v_cache + vo + c * 8 : p.v_cache;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd + row * ROW_BYTES + c * 16), "l"(ksrc), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd + row * ROW_BYTES + c * 16), "l"(vsrc), "r"(bytes) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -297,12 +287,6 @@ decode_kernel(const DecodeParams p) {
     }
     if (p.n_slices == 1) {
       p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
-    } else if (p.cluster_merge) {
-      store_to_leader(&cl_o[slice][i % GHD], o);
-      if (d == 0) {
-        store_to_leader(&cl_m[slice][g], mx);
-        store_to_leader(&cl_l[slice][g], lsum);
-      }
     } else {
       size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
       p.part_o[at * HD + d] = o;
@@ -312,19 +296,30 @@ decode_kernel(const DecodeParams p) {
       }
     }
   }
-  if (p.n_slices > 1 && p.cluster_merge) {
-    cluster_sync_all();  // every slice's state has landed in the leader
-    if (slice == 0) {
+  if (p.n_slices > 1 && p.counters != nullptr) {
+    // the slice that arrives last merges all of them, in slice order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* counter = p.counters + size_t(t) * p.n_kv_heads + kvh;
+      int arrived = atomicAdd(counter, 1);
+      is_last_s = arrived == p.n_slices - 1;
+      if (is_last_s) *counter = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (is_last_s) {
+      __threadfence();
       for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
         int g = i / HD, d = i % HD;
+        const size_t base = (size_t(t) * p.n_heads + h0 + g) * p.n_slices;
         float mx = -INFINITY;
-        for (int s = 0; s < p.n_slices; ++s) mx = fmaxf(mx, cl_m[s][g]);
+        for (int s = 0; s < p.n_slices; ++s) mx = fmaxf(mx, __ldcg(&p.part_ml[(base + s) * 2]));
         float o = 0.f, lsum = 0.f;
         if (mx > -INFINITY) {
-          for (int s = 0; s < p.n_slices; ++s) {  // slices in order: the same bits every run
-            float c = __expf(cl_m[s][g] - mx);
-            o += c * cl_o[s][i % GHD];
-            lsum += c * cl_l[s][g];
+          for (int s = 0; s < p.n_slices; ++s) {
+            float c = __expf(__ldcg(&p.part_ml[(base + s) * 2]) - mx);
+            o += c * __ldcg(&p.part_o[(base + s) * HD + d]);
+            lsum += c * __ldcg(&p.part_ml[(base + s) * 2 + 1]);
           }
         }
         p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
@@ -355,12 +350,12 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   }
 }
 
-template <typename K>
-bool configure_smem(K kernel) {
+template <int G>
+bool configure_smem() {
   // once per kernel instance: room for the tiles beyond the default 48 KB
   static bool done = false;
   if (!done) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
     done = true;
   }
   return true;
@@ -369,7 +364,7 @@ bool configure_smem(K kernel) {
 template <int G>
 int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
-  if (!configure_smem(decode_kernel<G>)) return R2_UNSUPPORTED;
+  if (!configure_smem<G>()) return R2_UNSUPPORTED;
   r2_launch(decode_kernel<G>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
   return launch_status();
 }
@@ -405,7 +400,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = nullptr; p.v_new = nullptr; p.new_row_stride = 0; p.slot_mapping = nullptr;
-  p.k_cache_w = nullptr; p.v_cache_w = nullptr; p.cluster_merge = 0;
+  p.k_cache_w = nullptr; p.v_cache_w = nullptr; p.counters = nullptr;
   int status;
   switch (n_heads / n_kv_heads) {
     case 1: status = launch<1>(p, n_rows, stream); break;
@@ -423,29 +418,8 @@ namespace {
 
 template <int G>
 int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(p.n_slices, p.n_kv_heads, n_rows);
-  config.blockDim = dim3(WARPS * 32);
-  if (!configure_smem(decode_kernel<G>)) return R2_UNSUPPORTED;
-  config.dynamicSmemBytes = TILE_SMEM;
-  config.stream = stream;
-  cudaLaunchAttribute attr[2];
-  int n_attr = 0;
-  if (p.n_slices > 1) {
-    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-    attr[n_attr].val.clusterDim.x = unsigned(p.n_slices);
-    attr[n_attr].val.clusterDim.y = 1;
-    attr[n_attr].val.clusterDim.z = 1;
-    ++n_attr;
-  }
-  if (g_r2_pdl) {
-    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
-    ++n_attr;
-  }
-  config.attrs = attr;
-  config.numAttrs = n_attr;
-  cudaLaunchKernelEx(&config, decode_kernel<G>, p);
+  if (!configure_smem<G>()) return R2_UNSUPPORTED;
+  r2_launch(decode_kernel<G>, dim3(p.n_slices, p.n_kv_heads, n_rows), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
   return launch_status();
 }
 
@@ -453,24 +427,25 @@ int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
 
 // One launch for a decode-only batch: the new tokens' keys and values (k_new, v_new:
 // [rows, n_kv_heads * HD] with row stride new_row_stride) are written to their cache slots by
-// the kernel itself, and the 1, 2, 4 or 8 slices of a (row, kv head) are merged by the leader of
-// a thread-block cluster, so there is neither a separate cache-write kernel nor a merge kernel
-// nor scratch memory. Needs (n_heads / n_kv_heads) * HD <= 512 when n_slices > 1.
+// the kernel itself, and the slices of a (row, kv head) are merged by whichever of their CTAs
+// finishes last, so there is neither a separate cache-write kernel nor a merge kernel.
+// `scratch` as for r2_attention_decode; `counters` holds n_rows * n_kv_heads ints that are
+// zero before the call and zero again after it.
 extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
                                          void* v_cache, long long page_stride, int page_size, int n_pages,
                                          const int32_t* block_tables, int table_width, const int32_t* row_entry,
                                          const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
                                          int n_kv_heads, float scale, int window, int n_slices, const void* k_new,
                                          const void* v_new, int new_row_stride, const int32_t* slot_mapping,
+                                         float* scratch, long long scratch_floats, int* counters, int n_counters,
                                          cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
-  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
-  if (n_slices != 1 && n_slices != 2 && n_slices != 4 && n_slices != 8) return R2_UNSUPPORTED;
-  const int group = n_heads / n_kv_heads;
-  if (n_slices > 1 && group * HD > CLUSTER_MAX_GHD) return R2_UNSUPPORTED;
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || n_slices < 1) return R2_BAD_SHAPE;
+  if (n_slices > 1 && (scratch == nullptr || counters == nullptr || n_counters < n_rows * n_kv_heads ||
+                       scratch_floats < r2_attention_decode_scratch_floats(n_rows, n_heads, n_slices))) return R2_BAD_SHAPE;
   if (page_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)) return R2_BAD_ALIGN;
-  if (k_new != nullptr && (v_new == nullptr || slot_mapping == nullptr || new_row_stride % 2 != 0 ||
-                           (reinterpret_cast<uintptr_t>(k_new) & 3) || (reinterpret_cast<uintptr_t>(v_new) & 3))) return R2_BAD_ALIGN;
+  if (k_new != nullptr && (v_new == nullptr || slot_mapping == nullptr || new_row_stride % 8 != 0 ||
+                           (reinterpret_cast<uintptr_t>(k_new) & 15) || (reinterpret_cast<uintptr_t>(v_new) & 15))) return R2_UNSUPPORTED;
   DecodeParams p;
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
@@ -480,12 +455,13 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window; p.n_slices = n_slices;
-  p.part_o = nullptr; p.part_ml = nullptr;
+  p.part_o = scratch;
+  p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.new_row_stride = new_row_stride;
   p.slot_mapping = slot_mapping;
   p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
-  p.cluster_merge = 1;
-  switch (group) {
+  p.counters = n_slices > 1 ? counters : nullptr;
+  switch (n_heads / n_kv_heads) {
     case 1: return launch_fused<1>(p, n_rows, stream);
     case 2: return launch_fused<2>(p, n_rows, stream);
     case 4: return launch_fused<4>(p, n_rows, stream);

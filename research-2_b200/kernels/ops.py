@@ -148,7 +148,7 @@ def decode_slices(n_rows: int, n_kv_heads: int, max_context: int) -> int:
     """Slices of the keys per (row, kv head) in decode attention: enough CTAs for two per SM,
     never less than 128 keys a slice."""
     ctas = max(1, n_rows * n_kv_heads)
-    want = -(-2 * N_SMS // ctas)
+    want = -(-4 * N_SMS // ctas) if ctas < N_SMS else -(-2 * N_SMS // ctas)
     most = max(1, max_context // 128)
     return max(1, min(want, most, 32))
 
@@ -174,8 +174,9 @@ def use_tensor_core_gemm(on: bool) -> bool:
 
 
 class _Workspace:
-    """Scratch of sliced decode attention (the slices' partial results) and the word in which
-    kernels record a bounded wait that ran out. One per device, sized once."""
+    """Scratch of sliced decode attention (the slices' partial results, arrival counters that are
+    zero between launches) and the word in which kernels record a bounded wait that ran out.
+    One per device, sized once."""
 
     FLOATS = 4 * 1024 * 1024
     COUNTERS = 4096
@@ -429,8 +430,8 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
                            seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                            window: int, max_context: int) -> torch.Tensor | None:
     """Decode attention in ONE launch for a batch in which every row is an entry of its own: the
-    kernel writes the new keys and values to their cache slots and merges its slices inside a
-    thread-block cluster. Returns None when it does not take the case (the caller then writes
+    kernel writes the new keys and values to their cache slots, and the slice that finishes last
+    merges all slices of its row. Returns None when it does not take the case (the caller then writes
     the cache and calls `paged_attention`)."""
     group = n_heads // max(n_kv_heads, 1)
     if not (_fast_attention and _fused_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -446,15 +447,17 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
         raise KernelError("decode attention: the new keys and values do not fit the rows")
     slices = decode_slices(n, n_kv_heads, max_context)
-    slices = 8 if slices >= 8 else 4 if slices >= 4 else 2 if slices >= 2 else 1
-    if slices > 1 and group * head_dim > 512:
+    lib = _lib_for_head_dim("attention_decode", head_dim)
+    ws = _workspace(q.device)
+    if (lib.r2_attention_decode_scratch_floats(n, n_heads, slices) > ws.floats.numel()
+            or n * n_kv_heads > ws.counters.numel()):
         slices = 1
     out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
-    lib = _lib_for_head_dim("attention_decode", head_dim)
     status = lib.r2_attention_decode_fused(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride), page_size,
         n_pages, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
-        n_kv_heads, C.c_float(scale), window, slices, _p(k_new), _p(v_new), stride, _p(slot_mapping), _stream())
+        n_kv_heads, C.c_float(scale), window, slices, _p(k_new), _p(v_new), stride, _p(slot_mapping), _p(ws.floats),
+        C.c_longlong(ws.floats.numel()), _p(ws.counters), ws.counters.numel(), _stream())
     if status == -4:
         return None
     _check(status, "decode attention (fused)")
