@@ -120,6 +120,16 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// gelu_new for the bfloat16 epilogue: tanh through one fast exponential (the result is rounded
+// to bfloat16 anyway; the float32 path keeps tanhf).
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float k = 0.7978845608028654f;
+  float u = k * (x + 0.044715f * x * x * x);
+  float e = __expf(2.f * u);
+  float t = 1.f - __fdividef(2.f, e + 1.f);  // tanh(u); e = inf gives 1, e = 0 gives -1
+  return 0.5f * x * (1.f + t);
+}
+
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -426,7 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < 16; ++j) v[j] += bias_a;
           if (p.act == R2_ACT_GELU_TANH) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh_fast(v[j]);
           } else if (p.act == R2_ACT_GELU_ERF) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
@@ -470,7 +480,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if (p.act == R2_ACT_GELU_TANH) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh_fast(v[j]);
           } else if (p.act == R2_ACT_GELU_ERF) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
@@ -603,6 +613,36 @@ struct Plan {
   size_t smem;
 };
 
+// How many clusters of `size` CTAs (one CTA per SM at this shared-memory use) the GPU can hold at
+// once: an SM group that a cluster must fit into does not always divide evenly, so it is asked, not
+// computed. Queried once per size.
+int max_resident_clusters(int size) {
+  static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (size < 1 || size > 8) return 0;
+  if (cached[size] == 0) {
+    auto kernel = gemm_tc_kernel<true, false, true>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1, 1, size);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = 120 * 1024;  // more than half an SM's: one CTA per SM, as the plan assumes
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = unsigned(size);
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = N_SMS / size / 2;  // a cautious guess
+    }
+    cached[size] = n;
+  }
+  return cached[size];
+}
+
 Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   Plan pl;
   pl.swapped = m <= 64;
@@ -610,6 +650,9 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   pl.b_total = pl.swapped ? m : n;
   if (pl.swapped) {
     pl.bn = ((pl.b_total + 15) / 16) * 16;               // tokens, K-major: any multiple of 16
+    // more than 32 tokens and few feature tiles: two token tiles double the CTAs that stream the
+    // weights (the second pass over a weight tile comes from L2) and halve the leader's reduce buffer
+    if (pl.b_total > 32 && ((pl.a_total + BM - 1) / BM) * 8 < N_SMS) pl.bn = 32;
   } else if (w_is_nk) {
     pl.bn = pl.b_total >= 128 ? 128 : ((pl.b_total + 15) / 16) * 16;
   } else {
@@ -625,10 +668,15 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
     int s = N_SMS / tiles;
     if (s > 8) s = 8;
     if (s > pl.n_kb) s = pl.n_kb;
-    while (s > 1 && size_t(s - 1) * pl.bn * BM * 4 > 100 * 1024) --s;
+    for (; s > 1; --s) {
+      if (size_t(s - 1) * pl.bn * BM * 4 > 100 * 1024) continue;  // the leader's reduce buffer
+      int per = (pl.n_kb + s - 1) / s;
+      int actual = (pl.n_kb + per - 1) / per;
+      if (actual != s) continue;                                  // the same split with fewer CTAs comes later
+      if (tiles <= max_resident_clusters(s)) break;               // all clusters run at once
+    }
     if (s < 1) s = 1;
-    int per = (pl.n_kb + s - 1) / s;
-    pl.splits = (pl.n_kb + per - 1) / per;
+    pl.splits = s;
   }
   pl.kb_per_split = (pl.n_kb + pl.splits - 1) / pl.splits;
   const size_t a_bytes = BM * BK * 2, b_stride = (size_t(pl.bn) * BK * 2 + 1023) & ~size_t(1023);

@@ -82,10 +82,69 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int32_t* __
   }
 }
 
+// The same for a handful of rows (a decode step): one warp per row, the row in registers, no
+// block-wide barrier. Rows of up to 2,048 elements whose length is a multiple of 4.
+template <typename O>
+__global__ void __launch_bounds__(128)
+layer_norm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, O* __restrict__ out, int n_rows, int width, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float4* xr = reinterpret_cast<const float4*>(x + size_t(src) * width);
+  constexpr int CHUNKS = 2048 / 128;
+  float4 v[CHUNKS];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    int k = (lane + 32 * i) * 4;
+    v[i] = k < width ? xr[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum += v[i].x + v[i].y + v[i].z + v[i].w;
+  }
+  const float mean = warp_sum(sum) / float(width);
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    int k = (lane + 32 * i) * 4;
+    if (k < width) {
+      float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+      sq += a * a + b * b + c * c + d * d;
+    }
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / float(width) + eps);
+  O* o = out + size_t(r) * width;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    int k = (lane + 32 * i) * 4;
+    if (k < width) {
+      float4 g = *reinterpret_cast<const float4*>(gamma + k);
+      float4 b = *reinterpret_cast<const float4*>(beta + k);
+      o[k] = from_float<O>((v[i].x - mean) * inv * g.x + b.x);
+      o[k + 1] = from_float<O>((v[i].y - mean) * inv * g.y + b.y);
+      o[k + 2] = from_float<O>((v[i].z - mean) * inv * g.z + b.z);
+      o[k + 3] = from_float<O>((v[i].w - mean) * inv * g.w + b.w);
+    }
+  }
+}
+
 extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* gamma, const float* beta, void* out,
                              int n_rows, int width, float eps, int odtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (width < 1 || size_t(width) * 4 > 200 * 1024) return R2_BAD_SHAPE;
+  const bool aligned = width % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && !(reinterpret_cast<uintptr_t>(gamma) & 15) &&
+                       !(reinterpret_cast<uintptr_t>(beta) & 15);
+  if (n_rows <= 64 && width <= 2048 && aligned && (odtype == R2_F32 || odtype == R2_BF16)) {
+    dim3 grid((n_rows + 3) / 4);
+    if (odtype == R2_F32) {
+      r2_launch(layer_norm_warp_kernel<float>, grid, dim3(128), size_t(0), stream, x, rows, gamma, beta, (float*)out, n_rows, width, eps);
+    } else {
+      r2_launch(layer_norm_warp_kernel<bf16>, grid, dim3(128), size_t(0), stream, x, rows, gamma, beta, (bf16*)out, n_rows, width, eps);
+    }
+    return launch_status();
+  }
   int threads = width >= 1024 ? 256 : 128;
   size_t smem = size_t(width) * sizeof(float);
   if (odtype == R2_F32) {

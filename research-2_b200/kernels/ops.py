@@ -118,7 +118,7 @@ def build_all() -> None:
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
-_fused_norm = os.environ.get("R2_FUSED_NORM", "0") != "0"  # off: the separate LayerNorm kernel is faster so far
+_fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
 _fused_decode = os.environ.get("R2_FUSED_DECODE", "1") != "0"
 
 
