@@ -1,0 +1,70 @@
+"""Runs each hot kernel once or twice at benchmark shapes (GPT-2 124M), for ncu to capture.
+
+    ncu --set full --clock-control none -k regex:'gemm_tc_kernel|decode_kernel|prefill_kernel' -c 12 \
+        -o gpurun_out/kernels python profiles/profile_kernels.py
+
+Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu), the tied
+logits product for 8 and 64 rows (77 MB of weights), decode attention for 64 rows at context
+640 (126 MB of cache), prefill attention for 2 x 1,024 tokens.
+"""
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+from research_2_b200.kernels import ops  # noqa: E402
+
+dev = "cuda:0"
+torch.manual_seed(0)
+D, F, H, HD, V, PS = 768, 3072, 12, 64, 50257, 16
+
+
+def paged(batch, ctx_len):
+    n_pages = batch * (1024 // PS) + 1
+    page_stride = 2 * H * PS * HD
+    pool = torch.randn(n_pages, page_stride, device=dev).bfloat16()
+    flat = pool.view(-1)
+    tables = torch.arange(1, n_pages, dtype=torch.int32, device=dev).view(batch, 1024 // PS).contiguous()
+    return flat, flat[H * PS * HD:], tables, page_stride, n_pages
+
+
+def main():
+    x = torch.randn(2048, D, device=dev).bfloat16()
+    wqkv = (torch.randn(D, 3 * D, device=dev) * 0.02).bfloat16()
+    wfc = (torch.randn(D, F, device=dev) * 0.02).bfloat16()
+    wte = (torch.randn(V, D, device=dev) * 0.02).bfloat16()
+    bias = torch.zeros(F, device=dev)
+    for _ in range(2):
+        ops.linear(x, wqkv, bias[: 3 * D].contiguous())
+        ops.linear(x, wfc, bias, act="gelu_new")
+        ops.linear(x[:8].contiguous(), wte, None, w_is_nk=True, out_dtype=torch.float32)
+        ops.linear(x[:64].contiguous(), wte, None, w_is_nk=True, out_dtype=torch.float32)
+    # decode attention, 64 rows at context 640
+    batch, ctx_len = 64, 640
+    kc, vc, tables, page_stride, n_pages = paged(batch, ctx_len)
+    qkv = torch.randn(batch, 3 * D, device=dev).bfloat16()
+    rows = torch.arange(batch, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=dev)
+    lens = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
+    slots = (tables[:, (ctx_len - 1) // PS] * PS + (ctx_len - 1) % PS).to(torch.int32)
+    for _ in range(2):
+        ops.decode_attention_fused(qkv[:, :D], qkv[:, D: 2 * D], qkv[:, 2 * D:], slots, kc, vc, page_stride, PS, n_pages,
+                                   tables, rows, pos, lens, H, H, HD, 0.125, 0, 1024)
+    # prefill attention, 2 x 1,024 tokens
+    batch, n = 2, 1024
+    kc, vc, tables, page_stride, n_pages = paged(batch, n)
+    q = torch.randn(batch * n, D, device=dev).bfloat16()
+    row_entry = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(n)
+    positions = torch.arange(n, dtype=torch.int32, device=dev).repeat(batch)
+    lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0, n, 2 * n], dtype=torch.int32, device=dev)
+    for _ in range(2):
+        ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, 0.125, 0,
+                            q_start=q_start, n_tiles=batch * n // 64)
+    torch.cuda.synchronize()
+    print("ok", ops.device_errors())
+
+
+if __name__ == "__main__":
+    main()

@@ -84,7 +84,9 @@ prefill_kernel(const PrefillParams p) {
 
   // which entry and which 64 rows of it this CTA has: tiles are numbered entry by entry
   if (tid == 0) {
-    int left = blockIdx.x, found = -1, row0 = 0;
+    // tiles are handed out from the end: in a prompt the last rows see the most keys, and the
+    // longest-running CTAs should start first
+    int left = int(gridDim.x) - 1 - int(blockIdx.x), found = -1, row0 = 0;
     for (int e = 0; e < p.n_entries; ++e) {
       int rows = p.q_start[e + 1] - p.q_start[e];
       int tiles = (rows + BM - 1) / BM;

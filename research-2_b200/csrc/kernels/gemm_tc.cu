@@ -225,7 +225,7 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
 // A_MN / B_MN: the operand's tile in shared memory is MN-major (rows of 64 MN-elements, one row
 // per k) instead of K-major (rows of 64 k-elements, one row per MN index).
 // TRANSPOSED: the a side is the features and the b side the tokens.
-template <bool A_MN, bool B_MN, bool TRANSPOSED>
+template <bool A_MN, bool B_MN, bool TRANSPOSED, bool FUSED_LN = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -233,7 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t a_bytes = BM * BK * 2;
   const uint32_t b_bytes = uint32_t(p.bn) * BK * 2;
   const uint32_t b_stride = (b_bytes + 1023u) & ~1023u;
-  const bool fused_ln = TRANSPOSED && p.ln_x != nullptr;
+  constexpr bool fused_ln = TRANSPOSED && FUSED_LN;  // a variant of its own: the norm's registers stay out of the others
   const int b_slots = fused_ln ? p.kb_per_split : p.stages;  // with a fused norm every token tile stays resident
   uint8_t* a_tiles = smem;
   uint8_t* b_tiles = smem + size_t(p.stages) * a_bytes;
@@ -367,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   bool acc_ok = true;
   if (warp >= 2) {
     pdl_wait();  // the epilogue reads the residual stream and writes the output
-    if (TRANSPOSED && fused_ln) {
+    if constexpr (fused_ln) {
       build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor core
       __syncwarp();
@@ -572,13 +572,15 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, bool TRANSPOSED>
+template <bool A_MN, bool B_MN, bool TRANSPOSED, bool FUSED_LN = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-  auto kernel = gemm_tc_kernel<A_MN, B_MN, TRANSPOSED>;
+  auto kernel = gemm_tc_kernel<A_MN, B_MN, TRANSPOSED, FUSED_LN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return int(e);
+    // all of the SM's on-chip memory as shared memory: two CTAs of ~110 KB fit side by side
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   cudaLaunchConfig_t config = {};
@@ -786,9 +788,11 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   if (w_is_nk) {
     ok = ok && make_map(&ma, w, uint64_t(k), uint64_t(n), uint64_t(ldw), BK, BM);
     if (!ok) return R2_UNSUPPORTED;
-    return launch<false, false, true>(ma, mb, p, grid, smem, stream);
+    return fused_ln ? launch<false, false, true, true>(ma, mb, p, grid, smem, stream)
+                    : launch<false, false, true>(ma, mb, p, grid, smem, stream);
   }
   ok = ok && make_map(&ma, w, uint64_t(n), uint64_t(k), uint64_t(ldw), 64, BK);
   if (!ok) return R2_UNSUPPORTED;
-  return launch<true, false, true>(ma, mb, p, grid, smem, stream);
+  return fused_ln ? launch<true, false, true, true>(ma, mb, p, grid, smem, stream)
+                  : launch<true, false, true>(ma, mb, p, grid, smem, stream);
 }

@@ -82,8 +82,8 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int32_t* __
   }
 }
 
-// The same for a handful of rows (a decode step): one warp per row, the row in registers, no
-// block-wide barrier. Rows of up to 2,048 elements whose length is a multiple of 4.
+// The same with one warp per row, the row in registers, no block-wide barrier: rows of up to
+// 2,048 elements whose length is a multiple of 4 (wider or unaligned rows take the kernel above).
 template <typename O>
 __global__ void __launch_bounds__(128)
 layer_norm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ gamma,
@@ -136,7 +136,7 @@ extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* g
   if (width < 1 || size_t(width) * 4 > 200 * 1024) return R2_BAD_SHAPE;
   const bool aligned = width % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && !(reinterpret_cast<uintptr_t>(gamma) & 15) &&
                        !(reinterpret_cast<uintptr_t>(beta) & 15);
-  if (n_rows <= 64 && width <= 2048 && aligned && (odtype == R2_F32 || odtype == R2_BF16)) {
+  if (width <= 2048 && aligned && (odtype == R2_F32 || odtype == R2_BF16)) {
     dim3 grid((n_rows + 3) / 4);
     if (odtype == R2_F32) {
       r2_launch(layer_norm_warp_kernel<float>, grid, dim3(128), size_t(0), stream, x, rows, gamma, beta, (float*)out, n_rows, width, eps);
