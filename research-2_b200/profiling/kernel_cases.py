@@ -1,19 +1,15 @@
 """Runs each hot kernel once or twice at benchmark shapes (GPT-2 124M), for ncu to capture.
 
     ncu --set full --clock-control none -k regex:'gemm_tc_kernel|decode_kernel|prefill_kernel' -c 12 \
-        -o gpurun_out/kernels python profiles/profile_kernels.py
+        -o kernels python -m research_2_b200.profiling.kernel_cases
 
 Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu), the tied
 logits product for 8 and 64 rows (77 MB of weights), decode attention for 64 rows at context
 640 (126 MB of cache), prefill attention for 2 x 1,024 tokens.
 """
-import sys
-from pathlib import Path
-
 import torch
 
-sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
-from research_2_b200.kernels import ops  # noqa: E402
+from ..kernels import ops
 
 dev = "cuda:0"
 torch.manual_seed(0)
