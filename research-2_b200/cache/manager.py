@@ -121,12 +121,13 @@ class CacheManager:
     # ---- batches ---------------------------------------------------------------------------
     def fill(self, batch) -> None:
         """Positions, slots and block tables of a StepBatch whose entries are set."""
-        n = batch.n_entries
-        status = self._lib.r2_cache_fill_batch(
-            self._h, n, _ptr(batch.entry_req), _ptr(batch.entry_start), _ptr(batch.entry_rows), batch.t_cap, batch.r_cap,
-            _ptr(batch.positions), _ptr(batch.row_entry), _ptr(batch.q_start), _ptr(batch.seq_lens),
-            _ptr(batch.state_slot), _ptr(batch.fresh), _ptr(batch.slot_mapping_flat), _ptr(batch.block_tables_flat),
-        )
+        ptrs = getattr(batch, "_fill_ptrs", None)
+        if ptrs is None:  # the arrays of a batch never move: their pointers are made once
+            ptrs = batch._fill_ptrs = tuple(_ptr(a) for a in (
+                batch.entry_req, batch.entry_start, batch.entry_rows, batch.positions, batch.row_entry, batch.q_start,
+                batch.seq_lens, batch.state_slot, batch.fresh, batch.slot_mapping_flat, batch.block_tables_flat))
+        status = self._lib.r2_cache_fill_batch(self._h, batch.n_entries, ptrs[0], ptrs[1], ptrs[2], batch.t_cap, batch.r_cap,
+                                               *ptrs[3:])
         self._check(status, "fill batch")
 
     def _check(self, status: int, what: str) -> None:

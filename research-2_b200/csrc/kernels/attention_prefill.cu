@@ -188,19 +188,38 @@ prefill_kernel(const PrefillParams p) {
           mma_bf16(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
         }
       }
-      // scale, mask, online softmax: rows row_a (c0, c1) and row_b (c2, c3)
+      // scale, mask, online softmax: rows row_a (c0, c1) and row_b (c2, c3). Scores are kept in
+      // units of log2(e) so that one exp2 per element does the softmax's exponential.
+      const float scale2 = p.scale * 1.4426950408889634f;
       float mx_a = -INFINITY, mx_b = -INFINITY;
+      // every key of this tile is visible to every row of this warp: no mask to evaluate
+      const int warp_pmin = pmin + warp * 16, warp_pmax = pmin + min(warp * 16 + 15, rows_here - 1);
+      const bool all_visible = j0 + BN - 1 <= warp_pmin && warp * 16 + 15 < rows_here &&
+                               (p.window == 0 || j0 > warp_pmax - p.window);
+      if (all_visible) {
 #pragma unroll
-      for (int nt = 0; nt < BN / 8; ++nt) {
+        for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          int j = j0 + nt * 8 + 2 * tq + c;
-          bool va = j <= pos_a && (p.window == 0 || j > pos_a - p.window) && row_a < rows_here;
-          bool vb = j <= pos_b && (p.window == 0 || j > pos_b - p.window) && row_b < rows_here;
-          s[nt][c] = va ? s[nt][c] * p.scale : -INFINITY;
-          s[nt][2 + c] = vb ? s[nt][2 + c] * p.scale : -INFINITY;
-          mx_a = fmaxf(mx_a, s[nt][c]);
-          mx_b = fmaxf(mx_b, s[nt][2 + c]);
+          for (int c = 0; c < 2; ++c) {
+            s[nt][c] *= scale2;
+            s[nt][2 + c] *= scale2;
+            mx_a = fmaxf(mx_a, s[nt][c]);
+            mx_b = fmaxf(mx_b, s[nt][2 + c]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            int j = j0 + nt * 8 + 2 * tq + c;
+            bool va = j <= pos_a && (p.window == 0 || j > pos_a - p.window) && row_a < rows_here;
+            bool vb = j <= pos_b && (p.window == 0 || j > pos_b - p.window) && row_b < rows_here;
+            s[nt][c] = va ? s[nt][c] * scale2 : -INFINITY;
+            s[nt][2 + c] = vb ? s[nt][2 + c] * scale2 : -INFINITY;
+            mx_a = fmaxf(mx_a, s[nt][c]);
+            mx_b = fmaxf(mx_b, s[nt][2 + c]);
+          }
         }
       }
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -210,14 +229,14 @@ prefill_kernel(const PrefillParams p) {
       const float m_a = fmaxf(m_run[0], mx_a), m_b = fmaxf(m_run[1], mx_b);
       // a row that has seen no key yet keeps exp(-inf - -inf) out of the way
       const float base_a = m_a == -INFINITY ? 0.f : m_a, base_b = m_b == -INFINITY ? 0.f : m_b;
-      const float corr_a = __expf(m_run[0] - base_a), corr_b = __expf(m_run[1] - base_b);
+      const float corr_a = exp2f(m_run[0] - base_a), corr_b = exp2f(m_run[1] - base_b);
       float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          s[nt][c] = __expf(s[nt][c] - base_a);
-          s[nt][2 + c] = __expf(s[nt][2 + c] - base_b);
+          s[nt][c] = exp2f(s[nt][c] - base_a);
+          s[nt][2 + c] = exp2f(s[nt][2 + c] - base_b);
           sum_a += s[nt][c];
           sum_b += s[nt][2 + c];
         }

@@ -146,11 +146,18 @@ class StepBatch:
     def check(self) -> None:
         """Host-side statement of the invariant that the reference asserts on the device
         (kernels/ops/paged_attention.py:143-157): an entry's rows are its newest positions."""
-        for e in range(self.n_entries):
-            a, b = int(self.q_start[e]), int(self.q_start[e + 1])
-            want = np.arange(b - a, dtype=np.int32) + (self.seq_lens[e] - (b - a))
-            if not np.array_equal(self.positions[a:b], want) or not np.all(self.row_entry[a:b] == e):
-                raise AssertionError(f"entry {e}: rows are not its newest positions")
+        t, r = self.n_tokens, self.n_entries
+        if t == 0:
+            return
+        e = self.row_entry[:t]
+        if e.min() < 0 or e.max() >= r:
+            raise AssertionError("a row names an entry outside the batch")
+        rows = np.arange(t, dtype=np.int32)
+        want = self.seq_lens[e] - (self.q_start[1: r + 1][e] - rows)
+        inside = (rows >= self.q_start[:r][e]) & (rows < self.q_start[1: r + 1][e])
+        if not (np.array_equal(self.positions[:t], want) and inside.all()):
+            bad = int(e[np.argmax((self.positions[:t] != want) | ~inside)])
+            raise AssertionError(f"entry {bad}: rows are not its newest positions")
 
 
 def batch_for(table_widths, n_tokens: int, n_entries: int, n_logit_rows: int, pinned: bool = False) -> StepBatch:

@@ -62,7 +62,8 @@ class SchedulerConfig:
 
 @dataclass(frozen=True)
 class Plan:
-    """One step's entries, decode entries first (kelpie-core/src/scheduler.zig:1315-1328)."""
+    """One step's entries, decode entries first (kelpie-core/src/scheduler.zig:1315-1328). The
+    arrays are views of the scheduler's buffers: they hold until its next plan()."""
 
     req: np.ndarray
     start: np.ndarray
@@ -116,10 +117,27 @@ class StepEvent:
     t_commit_ns: int
 
 
-def _copy(ptr, n: int, dtype) -> np.ndarray:
-    if n == 0:
-        return np.zeros(0, dtype=dtype)
-    return np.ctypeslib.as_array(ptr, shape=(n,)).astype(dtype, copy=True)
+class _PlanBuffers:
+    """Arrays that receive a plan from the native side: sized once for the largest plan, filled by
+    memmove, handed out as views (a Plan is valid until the next plan() of its scheduler)."""
+
+    FIELDS = (("req", np.int32, False), ("start", np.int32, False), ("rows", np.int32, False), ("emits", np.int32, False),
+              ("kind", np.int32, False), ("input_ids", np.int32, True), ("temperature", np.float32, False),
+              ("top_k", np.int32, False), ("sample_pos", np.int32, False), ("key0", np.uint32, False),
+              ("key1", np.uint32, False))
+
+    def __init__(self, max_entries: int, max_tokens: int):
+        self.arrays = [np.zeros(max(max_tokens if per_token else max_entries, 1), dtype=dt) for _, dt, per_token in self.FIELDS]
+        self.addresses = [a.ctypes.data for a in self.arrays]
+
+    def take(self, p) -> list:
+        out = []
+        for (name, _, per_token), arr, addr in zip(self.FIELDS, self.arrays, self.addresses):
+            n = p.n_tokens if per_token else p.n_entries
+            if n:
+                C.memmove(addr, getattr(p, name), n * 4)
+            out.append(arr[:n])
+        return out
 
 
 class Scheduler:
@@ -139,6 +157,11 @@ class Scheduler:
             raise ValueError(f"scheduler: {_host.last_error()}")
         self._h = C.c_void_p(handle)
         self.cache = CacheManager(self.groups, config.max_requests, config.max_seq_len, _borrowed=self)
+        self._plan_buffers = _PlanBuffers(config.max_batch_reqs, config.max_batch_tokens)
+        self._plan_c = _host.PlanC()
+        self._poll_buf = np.zeros(config.max_seq_len, dtype=np.int32)
+        self._poll_ptr = self._poll_buf.ctypes.data_as(_host.I32P)
+        self._poll_flags = (C.c_int32(0), C.c_int32(0))
 
     def _cache_handle(self) -> int:
         return self._lib.r2_sched_cache(self._h)
@@ -196,13 +219,11 @@ class Scheduler:
             raise KeyError(f"no request {rid}")
 
     def poll(self, rid: int) -> Poll:
-        cap = self.config.max_seq_len
-        out = np.zeros(cap, dtype=np.int32)
-        finished, state = C.c_int32(0), C.c_int32(0)
-        n = self._lib.r2_sched_poll(self._h, rid, out.ctypes.data_as(_host.I32P), cap, C.byref(finished), C.byref(state))
+        finished, state = self._poll_flags
+        n = self._lib.r2_sched_poll(self._h, rid, self._poll_ptr, self.config.max_seq_len, C.byref(finished), C.byref(state))
         if n < 0:
             raise KeyError(f"no request {rid}")
-        return Poll([int(t) for t in out[:n]], bool(finished.value), STATE_NAMES[state.value])
+        return Poll(self._poll_buf[:n].tolist(), bool(finished.value), STATE_NAMES[state.value])
 
     def request_info(self, rid: int) -> dict:
         vals = [C.c_int32(0) for _ in range(5)]
@@ -215,17 +236,11 @@ class Scheduler:
     # ---- steps -----------------------------------------------------------------------------
     def plan(self) -> Plan:
         """The next step's entries (possibly none). Raises Stalled when nothing can run."""
-        p = _host.PlanC()
+        p = self._plan_c
         status = self._lib.r2_sched_plan(self._h, C.byref(p))
         if status != 0:
             raise RuntimeError("plan() while the previous plan has not been committed")
-        r, t = p.n_entries, p.n_tokens
-        plan = Plan(
-            _copy(p.req, r, np.int32), _copy(p.start, r, np.int32), _copy(p.rows, r, np.int32),
-            _copy(p.emits, r, np.int32), _copy(p.kind, r, np.int32), _copy(p.input_ids, t, np.int32),
-            _copy(p.temperature, r, np.float32), _copy(p.top_k, r, np.int32), _copy(p.sample_pos, r, np.int32),
-            _copy(p.key0, r, np.uint32), _copy(p.key1, r, np.uint32),
-        )
+        plan = Plan(*self._plan_buffers.take(p))
         stall = _host.StallC()
         if self._lib.r2_sched_stall(self._h, C.byref(stall)):
             self._lib.r2_sched_commit(self._h, None, 0)  # the empty plan is closed so that the caller can go on
