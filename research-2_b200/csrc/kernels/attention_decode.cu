@@ -34,7 +34,7 @@ struct DecodeParams {
   const bf16* q; int q_row_stride;
   bf16* out; int out_row_stride;
   const bf16* k_cache; const bf16* v_cache;
-  long long page_stride; int page_size; int n_pages;
+  long long page_stride; int page_size; int page_shift; int n_pages;
   const int32_t* block_tables; int table_width;
   const int32_t* row_entry; const int32_t* positions; const int32_t* seq_lens;
   int n_heads, n_kv_heads;
@@ -131,9 +131,9 @@ decode_kernel(const DecodeParams p) {
         my_k = (p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.k_cache;
         my_v = (p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.v_cache;
       } else {
-        int page = table[j / p.page_size];
+        int page = table[page_index(j, p.page_size, p.page_shift)];
         page = (page < 0 || page >= p.n_pages) ? 0 : page;
-        my_k = my_v = (long long)(size_t(page) * p.page_stride + head_off + size_t(j % p.page_size) * HD);
+        my_k = my_v = (long long)(size_t(page) * p.page_stride + head_off + size_t(page_offset(j, p.page_size, p.page_shift)) * HD);
       }
     }
     const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
@@ -162,9 +162,9 @@ decode_kernel(const DecodeParams p) {
     if (tile == tile_of_new) {
       // the newest key lies in this tile: this warp also puts its key and value into the cache
       const int slot = p.slot_mapping[t];
-      const int page = slot / p.page_size;
-      if (slot >= 0 && page < p.n_pages) {
-        const size_t dst = size_t(page) * p.page_stride + size_t(kvh) * p.page_size * HD + size_t(slot % p.page_size) * HD;
+      const int page = slot < 0 ? -1 : page_index(slot, p.page_size, p.page_shift);
+      if (page >= 0 && page < p.n_pages) {
+        const size_t dst = size_t(page) * p.page_stride + size_t(kvh) * p.page_size * HD + size_t(page_offset(slot, p.page_size, p.page_shift)) * HD;
         const __nv_bfloat162* ks = reinterpret_cast<const __nv_bfloat162*>(p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD);
         const __nv_bfloat162* vs = reinterpret_cast<const __nv_bfloat162*>(p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD);
         __nv_bfloat162* kd = reinterpret_cast<__nv_bfloat162*>(p.k_cache_w + dst);
@@ -392,7 +392,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
-  p.page_stride = page_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.page_stride = page_stride; p.page_size = page_size; p.page_shift = page_shift_of(page_size); p.n_pages = n_pages;
   p.block_tables = block_tables; p.table_width = table_width;
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
@@ -450,7 +450,7 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
-  p.page_stride = page_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.page_stride = page_stride; p.page_size = page_size; p.page_shift = page_shift_of(page_size); p.n_pages = n_pages;
   p.block_tables = block_tables; p.table_width = table_width;
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;

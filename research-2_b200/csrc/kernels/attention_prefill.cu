@@ -14,6 +14,8 @@
 // compile-time constant (-DHEAD_DIM=64), in steps of 16 up to 128: one library per head size.
 #include <math.h>
 
+#include <limits.h>
+
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -24,6 +26,10 @@ namespace {
 
 constexpr int HD = HEAD_DIM;
 constexpr int BM = 64, BN = 64, WARPS = 4;
+constexpr int STAGES = HD <= 64 ? 3 : 2;      // key/value tiles in flight or in use
+constexpr int CHUNKS = HD / 8;                // 16-byte pieces of a row
+constexpr int PIECES = BN * CHUNKS / (WARPS * 32);  // pieces of a tile that one thread copies
+static_assert(BN * CHUNKS % (WARPS * 32) == 0, "a tile's pieces divide among the threads");
 constexpr int ROW_BYTES = HD * 2 + 16;        // padded row in shared memory
 constexpr int TILE_BYTES = BN * ROW_BYTES;
 constexpr int KSTEPS = HD / 16;               // k-steps of q.k
@@ -34,7 +40,7 @@ struct PrefillParams {
   const bf16* q; int q_row_stride;
   bf16* out; int out_row_stride;
   const bf16* k_cache; const bf16* v_cache;
-  long long page_stride; int page_size; int n_pages;
+  long long page_stride; int page_size; int page_shift; int n_pages;
   const int32_t* block_tables; int table_width;
   const int32_t* q_start; const int32_t* seq_lens; int n_entries;
   int n_heads, n_kv_heads;
@@ -63,6 +69,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// 2^x by the hardware's approximation (2 ulp; 2^-inf = 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -74,8 +87,8 @@ prefill_kernel(const PrefillParams p) {
   pdl_wait();               // the previous kernel's writes are visible from here on
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_s = smem;                         // [BM] rows
-  uint8_t* k_s = smem + TILE_BYTES;            // 2 stages
-  uint8_t* v_s = smem + 3 * TILE_BYTES;        // 2 stages
+  uint8_t* k_s = smem + TILE_BYTES;                  // STAGES tiles
+  uint8_t* v_s = smem + (1 + STAGES) * TILE_BYTES;   // STAGES tiles
   __shared__ int tile_entry, tile_row0;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -121,29 +134,48 @@ prefill_kernel(const PrefillParams p) {
     cp_async16(smem_addr(q_s + row * ROW_BYTES + c * 16), src, ok);
   }
 
-  // Two threads per key row: one page lookup each, half of the row's 16-byte pieces each.
-  auto load_tile = [&](int j0, int stage) {
-    int row = tid >> 1, half = tid & 1;
-    int j = j0 + row;
-    bool ok = j >= lo && j <= pmax;
-    size_t off = 0;
-    if (ok) {
-      int page = table[j / p.page_size];
-      page = (page < 0 || page >= p.n_pages) ? 0 : page;
-      off = size_t(page) * p.page_stride + (size_t(kvh) * p.page_size + j % p.page_size) * HD;
+  // Key and value tiles are copied in 16-byte pieces, consecutive threads taking consecutive
+  // pieces of a row, so that one warp's copy reads whole rows (rows of a page lie one after
+  // another in memory). A thread has PIECES pieces per tile, each in a row of its own, so it
+  // looks up PIECES pages. The lookups of a tile are made one iteration before its copies are
+  // issued, and the copies STAGES - 1 iterations before the tile is used, so that neither
+  // latency is waited for.
+  auto pages_of = [&](int j0, int (&pages)[PIECES]) {
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      int j = j0 + (tid + i * WARPS * 32) / CHUNKS;
+      // the entry is checked where it is used, so that nothing waits for this load here; a row
+      // outside the tile's keys is marked with a page below every valid one
+      pages[i] = (j >= lo && j <= pmax) ? table[page_index(j, p.page_size, p.page_shift)] : INT_MIN;
     }
-    uint32_t kd = smem_addr(k_s + stage * TILE_BYTES + row * ROW_BYTES);
-    uint32_t vd = smem_addr(v_s + stage * TILE_BYTES + row * ROW_BYTES);
-    for (int c = half; c < HD / 8; c += 2) {
-      cp_async16(kd + c * 16, p.k_cache + off + c * 8, ok);
-      cp_async16(vd + c * 16, p.v_cache + off + c * 8, ok);
+  };
+  auto load_tile = [&](int j0, int stage, const int (&pages)[PIECES]) {
+#pragma unroll
+    for (int i = 0; i < PIECES; ++i) {
+      int id = tid + i * WARPS * 32;
+      int row = id / CHUNKS, c = id % CHUNKS;
+      int j = j0 + row;
+      bool ok = pages[i] != INT_MIN;
+      int page = (pages[i] < 0 || pages[i] >= p.n_pages) ? 0 : pages[i];  // a bad entry reads the null page
+      size_t off = ok ? size_t(page) * p.page_stride + (size_t(kvh) * p.page_size + page_offset(j, p.page_size, p.page_shift)) * HD + c * 8 : 0;
+      uint32_t dst = uint32_t(stage * TILE_BYTES + row * ROW_BYTES + c * 16);
+      cp_async16(smem_addr(k_s) + dst, p.k_cache + off, ok);
+      cp_async16(smem_addr(v_s) + dst, p.v_cache + off, ok);
     }
   };
 
   const int j_first = lo / BN * BN;
   const int n_tiles = (pmax - j_first) / BN + 1;
-  load_tile(j_first, 0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
+  int pages_next[PIECES];
+#pragma unroll
+  for (int t = 0; t < STAGES - 1; ++t) {
+    if (t < n_tiles) {
+      pages_of(j_first + t * BN, pages_next);
+      load_tile(j_first + t * BN, t, pages_next);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (STAGES - 1 < n_tiles) pages_of(j_first + (STAGES - 1) * BN, pages_next);
 
   float o[DTILES][4];
 #pragma unroll
@@ -155,12 +187,15 @@ prefill_kernel(const PrefillParams p) {
   const int pos_a = pmin + row_a, pos_b = pmin + row_b;
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
+    const int stage = it % STAGES;
     const int j0 = j_first + it * BN;
-    if (it + 1 < n_tiles) load_tile(j0 + BN, stage ^ 1);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    // tile `it` has landed (only the newest STAGES - 2 groups may still be in flight); after the
+    // barrier every thread's part of it is visible and the stage of tile it - 1 is free
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncthreads();
+    if (it + STAGES - 1 < n_tiles) load_tile(j0 + (STAGES - 1) * BN, (it + STAGES - 1) % STAGES, pages_next);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (it + STAGES < n_tiles) pages_of(j0 + STAGES * BN, pages_next);
     if (it == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -196,13 +231,13 @@ prefill_kernel(const PrefillParams p) {
       const int warp_pmin = pmin + warp * 16, warp_pmax = pmin + min(warp * 16 + 15, rows_here - 1);
       const bool all_visible = j0 + BN - 1 <= warp_pmin && warp * 16 + 15 < rows_here &&
                                (p.window == 0 || j0 > warp_pmax - p.window);
+      // (the scale is positive, so the largest raw score is the largest scaled one; it goes into
+      // the exponent's multiply-add)
       if (all_visible) {
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            s[nt][c] *= scale2;
-            s[nt][2 + c] *= scale2;
             mx_a = fmaxf(mx_a, s[nt][c]);
             mx_b = fmaxf(mx_b, s[nt][2 + c]);
           }
@@ -215,8 +250,8 @@ prefill_kernel(const PrefillParams p) {
             int j = j0 + nt * 8 + 2 * tq + c;
             bool va = j <= pos_a && (p.window == 0 || j > pos_a - p.window) && row_a < rows_here;
             bool vb = j <= pos_b && (p.window == 0 || j > pos_b - p.window) && row_b < rows_here;
-            s[nt][c] = va ? s[nt][c] * scale2 : -INFINITY;
-            s[nt][2 + c] = vb ? s[nt][2 + c] * scale2 : -INFINITY;
+            s[nt][c] = va ? s[nt][c] : -INFINITY;
+            s[nt][2 + c] = vb ? s[nt][2 + c] : -INFINITY;
             mx_a = fmaxf(mx_a, s[nt][c]);
             mx_b = fmaxf(mx_b, s[nt][2 + c]);
           }
@@ -226,17 +261,17 @@ prefill_kernel(const PrefillParams p) {
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-      const float m_a = fmaxf(m_run[0], mx_a), m_b = fmaxf(m_run[1], mx_b);
+      const float m_a = fmaxf(m_run[0], mx_a * scale2), m_b = fmaxf(m_run[1], mx_b * scale2);
       // a row that has seen no key yet keeps exp(-inf - -inf) out of the way
       const float base_a = m_a == -INFINITY ? 0.f : m_a, base_b = m_b == -INFINITY ? 0.f : m_b;
-      const float corr_a = exp2f(m_run[0] - base_a), corr_b = exp2f(m_run[1] - base_b);
+      const float corr_a = fast_exp2(m_run[0] - base_a), corr_b = fast_exp2(m_run[1] - base_b);
       float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          s[nt][c] = exp2f(s[nt][c] - base_a);
-          s[nt][2 + c] = exp2f(s[nt][2 + c] - base_b);
+          s[nt][c] = fast_exp2(fmaf(s[nt][c], scale2, -base_a));
+          s[nt][2 + c] = fast_exp2(fmaf(s[nt][2 + c], scale2, -base_b));
           sum_a += s[nt][c];
           sum_b += s[nt][2 + c];
         }
@@ -272,7 +307,6 @@ prefill_kernel(const PrefillParams p) {
         }
       }
     }
-    __syncthreads();  // the stage is free for the load after next
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
@@ -311,15 +345,19 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
-  p.page_stride = page_stride; p.page_size = page_size; p.n_pages = n_pages;
+  p.page_stride = page_stride; p.page_size = page_size; p.page_shift = page_shift_of(page_size); p.n_pages = n_pages;
   p.block_tables = block_tables; p.table_width = table_width;
   p.q_start = q_start; p.seq_lens = seq_lens; p.n_entries = n_entries;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window;
-  const size_t smem = 5 * size_t(TILE_BYTES);
+  if (!(scale > 0.f)) return R2_UNSUPPORTED;  // the softmax takes the largest raw score for the largest scaled one
+  const size_t smem = (1 + 2 * STAGES) * size_t(TILE_BYTES);
   static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
+  if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    // several CTAs per SM hide each other's waits: ask for the shared memory that takes
+    e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return int(e);
     configured = true;
   }

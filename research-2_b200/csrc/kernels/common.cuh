@@ -74,6 +74,18 @@ __device__ __forceinline__ float activate(float x, int act) {
   return x;
 }
 
+// A position's page and offset within it. Page sizes are powers of two in practice: the host
+// passes log2(size) as `shift` (-1 for another size), which spares the kernels' inner loops an
+// integer division whose instruction sequence is long.
+inline int page_shift_of(int page_size) {
+  if (page_size < 1 || (page_size & (page_size - 1)) != 0) return -1;
+  int s = 0;
+  while ((1 << s) < page_size) ++s;
+  return s;
+}
+__device__ __forceinline__ int page_index(int j, int page_size, int shift) { return shift >= 0 ? (j >> shift) : (j / page_size); }
+__device__ __forceinline__ int page_offset(int j, int page_size, int shift) { return shift >= 0 ? (j & (page_size - 1)) : (j % page_size); }
+
 // Programmatic dependent launch: a kernel may start while its predecessor in the stream is still
 // running. Everything it does before `pdl_wait()` must neither read what the predecessor writes
 // nor write anything; `pdl_wait()` returns once the predecessor has completed and its writes are

@@ -59,6 +59,9 @@ struct GemmParams {
   const float* ln_gamma;
   const float* ln_beta;
   float ln_eps;
+  // The weight of the product that runs next: asked into L2 while this one runs, a slice per CTA.
+  const uint8_t* prefetch;
+  long long prefetch_bytes;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -365,6 +368,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
   bool acc_ok = true;
+  if (threadIdx.x == 64 && p.prefetch != nullptr) {
+    // weights never change: this CTA's slice of the next product's weight goes to L2 right away
+    const long long n_ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+    const long long cta = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+    const long long per = ((p.prefetch_bytes + n_ctas - 1) / n_ctas + 4095) / 4096 * 4096;
+    const long long begin = cta * per, end = min(p.prefetch_bytes, begin + per);
+    for (long long at = begin; at < end; at += 4096) {
+      const uint32_t size = uint32_t(min(4096ll, end - at)) & ~15u;
+      if (size > 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + at), "r"(size) : "memory");
+    }
+  }
   if (warp >= 2) {
     pdl_wait();  // the epilogue reads the residual stream and writes the output
     if constexpr (fused_ln) {
@@ -721,10 +735,12 @@ extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, in
 //
 // With ln_x != null the tokens are LayerNorm(ln_x[ln_rows[i]] or ln_x[i]) computed inside the kernel
 // (`x` is then ignored); this form takes at most 16 tokens and k <= 1024, else R2_UNSUPPORTED.
+// `prefetch` (may be null) names memory, typically the next product's weight, that the kernel asks into L2.
 extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_is_nk, const float* bias,
                           const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
                           int out_dtype, int* error_flag, const float* ln_x, int ln_ldx, const int32_t* ln_rows,
-                          const float* ln_gamma, const float* ln_beta, float ln_eps, cudaStream_t stream) {
+                          const float* ln_gamma, const float* ln_beta, float ln_eps, const void* prefetch,
+                          long long prefetch_bytes, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return R2_OK;
   const bool fused_ln = ln_x != nullptr;
   if (fused_ln) {
@@ -748,6 +764,9 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   p.ln_gamma = ln_gamma;
   p.ln_beta = ln_beta;
   p.ln_eps = ln_eps;
+  const bool prefetch_ok = prefetch != nullptr && prefetch_bytes >= 16 && !(reinterpret_cast<uintptr_t>(prefetch) & 15);
+  p.prefetch = prefetch_ok ? static_cast<const uint8_t*>(prefetch) : nullptr;
+  p.prefetch_bytes = prefetch_ok ? prefetch_bytes : 0;
   p.a_total = pl.a_total;
   p.b_total = pl.b_total;
   p.k_total = k;

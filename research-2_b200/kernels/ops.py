@@ -120,6 +120,7 @@ _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
 _fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
 _fused_decode = os.environ.get("R2_FUSED_DECODE", "1") != "0"
+_weight_prefetch = os.environ.get("R2_WEIGHT_PREFETCH", "0") != "0"  # measured: no gain at batch 8, so off
 
 
 def use_fused_decode_attention(on: bool) -> bool:
@@ -249,6 +250,24 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: fl
     return out
 
 
+_next_weight: dict[int, tuple[int, int]] = {}
+
+
+def set_weight_order(weights: list[torch.Tensor]) -> None:
+    """Tell the products in which order their weights are used during a step: with few tokens a
+    product then asks the following product's weight into L2 while it runs (decode steps wait on
+    DRAM latency, not bandwidth). The last weight's successor is the first. Optional."""
+    _next_weight.clear()
+    for i, w in enumerate(weights):
+        nxt = weights[(i + 1) % len(weights)]
+        _next_weight[w.data_ptr()] = (nxt.data_ptr(), nxt.numel() * nxt.element_size())
+
+
+def _prefetch_args(w: torch.Tensor, m: int):
+    hint = _next_weight.get(w.data_ptr()) if m <= 64 and _weight_prefetch else None
+    return (C.c_void_p(hint[0]), C.c_longlong(hint[1])) if hint else (None, C.c_longlong(0))
+
+
 class NormedRows:
     """LayerNorm of float32 rows that has not been computed yet: `linear` may compute it inside
     its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel."""
@@ -283,7 +302,7 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
     status = _lib("gemm_tc").r2_gemm_tc(
         None, 0, _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _p(a.x), a.x.stride(0), _p(a.rows), _p(a.gamma),
-        _p(a.beta), C.c_float(a.eps), _stream())
+        _p(a.beta), C.c_float(a.eps), *_prefetch_args(w, m), _stream())
     if status == -4:
         return None
     _check(status, "linear (tensor cores, fused norm)")
@@ -332,7 +351,8 @@ def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: boo
         ws = _workspace(a.device)
         status = _lib("gemm_tc").r2_gemm_tc(
             _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
-            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0), _stream())
+            ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0),
+            *_prefetch_args(w, m), _stream())
         if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
             _check(status, "linear (tensor cores)")
             return out

@@ -43,6 +43,10 @@ class PagedAttention:
                              f"{self.n_heads} heads, {self.n_kv_heads} kv heads of {self.head_dim}")
         self.rotary = None  # a positions part that changes q and k may be attached by the model
 
+    def matrices(self):
+        """The weight matrices in the order in which forward() uses them."""
+        return [self.w_qkv, self.w_out]
+
     @property
     def cache_spec(self) -> MemberSpec:
         return MemberSpec(self.n_kv_heads, self.head_dim, self.window)

@@ -26,6 +26,10 @@ class DenseMLP:
 
     takes_lazy_norm = True  # the input goes straight into ops.linear
 
+    def matrices(self):
+        """The weight matrices in the order in which forward() uses them."""
+        return [self.w_in, self.w_out]
+
     def forward(self, h, residual, ctx):
         inner = ops.linear(h, self.w_in, self.b_in, act=self.activation)
         return ops.linear(inner, self.w_out, self.b_out, residual=residual)
