@@ -70,32 +70,40 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
 
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+// The barrier and tile arguments below are shared-memory addresses as 32-bit numbers: the loops
+// that use them are run by one thread each, at one dependent instruction every few cycles, so
+// pointer conversions, multiplications and divisions inside them show in the k-block rate.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
 }
 
 // Waits for the phase with the given parity to complete; false after SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t addr = smem_u32(bar);
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if (spin > 1024) __nanosleep(64);
   }
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait(smem_u32(bar), parity); }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
 
@@ -119,8 +127,8 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       : "memory");
 }
 
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // gelu_new for the bfloat16 epilogue: tanh through one fast exponential (the result is rounded
@@ -131,6 +139,16 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
   float e = __expf(2.f * u);
   float t = 1.f - __fdividef(2.f, e + 1.f);  // tanh(u); e = inf gives 1, e = 0 gives -1
   return 0.5f * x * (1.f + t);
+}
+
+// True in one lane of the (converged) warp. The loops that issue TMA and tensor-core
+// instructions are run by the whole warp with the instruction itself under this predicate:
+// their addresses and descriptors are then warp-uniform values, which is the form those
+// instructions take their operands in.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void cluster_sync() {
@@ -225,11 +243,197 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
   }
 }
 
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// gelu_new with the hardware's tanh (relative error about 2^-11, below bfloat16's rounding).
+__device__ __forceinline__ float gelu_tanh_hw(float x) {
+  const float x2 = x * x;
+  const float u = x * fmaf(x2, 0.7978845608028654f * 0.044715f, 0.7978845608028654f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+
+constexpr int STAGING_ROW = 36;                       // words per staged row: 32 and four of padding (rows stay 16-byte aligned)
+constexpr int STAGING_WORDS = 32 * STAGING_ROW;       // per epilogue warp
+constexpr int BIAS_SLOTS = 256;                       // floats: the widest tile
+
+// The epilogue of a 32-row slab of a token-major tile over the tile's columns [c_begin, c_end)
+// (one warp; lane = accumulator row). The accumulator comes out of tensor memory one row per
+// lane, which written straight to global memory is 32 scattered pieces per store and one exposed
+// load latency per piece of the residual. So each group of columns takes two steps: (1) bias and
+// activation on the lane's row, written to a padded shared-memory slab; (2) read back with eight
+// lanes to a row, 16 bytes each, so that every global access of the warp is four whole 128-byte
+// pieces of rows. The residual of a whole group is requested before step (1), so its latency
+// passes under it. An epilogue warp has a scheduler almost to itself and issues about one
+// instruction every six cycles, so the count of instructions per element is what is kept small.
+// `bias_s` holds the tile's bias (zeros without one), 16-byte aligned. bfloat16 output without a
+// residual moves 64 columns a group as packed pairs; everything else 32 columns as floats.
+// `slab` is the warp's 32 x STAGING_ROW words of shared memory, as a shared-space address.
+__device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t lane_addr, uint32_t slab, const float* bias_s,
+                                                 int row0, int col0, int c_begin, int c_end, int lane, bool have_acc) {
+  const int rows = min(32, p.a_total - row0);        // rows of this slab that exist
+  const int sub = lane >> 3, piece = lane & 7;       // step (2): the row within four, the 16-byte piece of it
+  auto row_values = [&](int c, float (&v)[32]) {     // 32 columns from c on: accumulator + bias, activated
+    uint32_t r[32];
+    if (have_acc) {
+      tmem_load32(lane_addr + uint32_t(c), r);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
+    const float4* b4 = reinterpret_cast<const float4*>(bias_s + (c & (BIAS_SLOTS - 1)));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 b = b4[j];
+      v[4 * j] = __uint_as_float(r[4 * j]) + b.x;
+      v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + b.y;
+      v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + b.z;
+      v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + b.w;
+    }
+    if (p.act == R2_ACT_GELU_TANH) {
+      if (p.out_is_bf16) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_hw(v[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
+      }
+    } else if (p.act == R2_ACT_GELU_ERF) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+    }
+  };
+  if (p.out_is_bf16 && p.residual == nullptr) {
+    bf16* out = reinterpret_cast<bf16*>(p.out);
+    const bool vec_ok = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (col0 & 7) == 0;
+    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+      if (col0 + c0 >= p.b_total) break;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[32];
+        if (c0 + 32 * h < c_end) {
+          row_values(c0 + 32 * h, v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_shared16(slab + uint32_t(lane * STAGING_ROW + 16 * h + 4 * j) * 4u, pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                        pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7]));
+          }
+        }
+      }
+      __syncwarp();
+      const int col = col0 + c0 + 8 * piece;                                   // this lane's eight columns
+      const int n_cols = min(8, min(c_end - (c0 + 8 * piece), p.b_total - col));
+      if (n_cols > 0) {
+#pragma unroll
+        for (int r4 = 0; r4 < 32; r4 += 4) {
+          const int r = r4 + sub;
+          const uint4 w = ld_shared16(slab + uint32_t(r * STAGING_ROW + 4 * piece) * 4u);
+          if (r < rows) {
+            bf16* d = out + size_t(row0 + r) * p.ldo + col;
+            if (n_cols == 8 && vec_ok) {
+              *reinterpret_cast<uint4*>(d) = w;
+            } else {
+              const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (j < n_cols) d[j] = __ushort_as_bfloat16(uint16_t(words[j >> 1] >> (16 * (j & 1))));
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+    return;
+  }
+  const bool vec_ok = (p.ldo & 3) == 0 && (p.out_is_bf16 || (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && (col0 & 3) == 0 &&
+                      (p.residual == nullptr || ((p.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    if (col0 + c0 >= p.b_total) break;
+    const int col = col0 + c0 + 4 * piece;                                     // this lane's four columns
+    const int n_cols = min(4, min(c_end - (c0 + 4 * piece), p.b_total - col));
+    const bool whole = n_cols == 4 && vec_ok;
+    float4 x[8];  // the residual of this lane's columns, its eight rows of the slab, in flight during step (1)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + sub;
+      x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.residual != nullptr && r < rows && n_cols > 0) {
+        const float* src = p.residual + size_t(row0 + r) * p.ldr + col;
+        if (whole) {
+          x[i] = *reinterpret_cast<const float4*>(src);
+        } else {
+          x[i].x = src[0];
+          if (n_cols > 1) x[i].y = src[1];
+          if (n_cols > 2) x[i].z = src[2];
+          if (n_cols > 3) x[i].w = src[3];
+        }
+      }
+    }
+    {
+      float v[32];
+      row_values(c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        st_shared16(slab + uint32_t(lane * STAGING_ROW + 4 * j) * 4u, __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                    __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+      }
+    }
+    __syncwarp();
+    if (n_cols > 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + sub;
+        const uint4 w = ld_shared16(slab + uint32_t(r * STAGING_ROW + 4 * piece) * 4u);
+        if (r < rows) {
+          const float y[4] = {__uint_as_float(w.x) + x[i].x, __uint_as_float(w.y) + x[i].y, __uint_as_float(w.z) + x[i].z,
+                              __uint_as_float(w.w) + x[i].w};
+          if (p.out_is_bf16) {
+            bf16* d = reinterpret_cast<bf16*>(p.out) + size_t(row0 + r) * p.ldo + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (j < n_cols) d[j] = __float2bfloat16_rn(y[j]);
+            }
+          } else {
+            float* d = reinterpret_cast<float*>(p.out) + size_t(row0 + r) * p.ldo + col;
+            if (whole) {
+              *reinterpret_cast<float4*>(d) = make_float4(y[0], y[1], y[2], y[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j < n_cols) d[j] = y[j];
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // A_MN / B_MN: the operand's tile in shared memory is MN-major (rows of 64 MN-elements, one row
 // per k) instead of K-major (rows of 64 k-elements, one row per MN index).
 // TRANSPOSED: the a side is the features and the b side the tokens.
 template <bool A_MN, bool B_MN, bool TRANSPOSED, bool FUSED_LN = false>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, TRANSPOSED ? 1 : 2)  // token-major tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -246,9 +450,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* tokens_ready = acc_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tokens_ready + 1);
   // partial sums of the other CTAs of the cluster, [rank - 1][column][row], used in the leader only
+  // (feature-major form); the token-major form keeps the tile's bias in the same place
   float* reduce = reinterpret_cast<float*>(tmem_slot + 4);
 
-  pdl_launch_dependents();  // the next kernel may set up and prefetch its weights meanwhile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
   uint32_t rank = 0;  // this CTA's place in its cluster = its slice of K
@@ -278,92 +482,132 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // The next kernel may start (set up, prefetch its weights) from here on, and not earlier: its
+  // CTAs allocate tensor memory before they wait for this kernel, so a CTA of this kernel that
+  // still had to allocate could find every column taken by CTAs that wait for it.
+  pdl_launch_dependents();
   // The weight is never written by a kernel, so its first tiles are requested before the wait
   // on the previous kernel; the activations, which that kernel may have written, after it.
-  auto load_weight = [&](int i, int s) {
-    int k0 = (kb_begin + i) * BK;
+  const uint32_t a_base = smem_u32(a_tiles), b_base = smem_u32(b_tiles);
+  const uint32_t full_base = smem_u32(full), empty_base = smem_u32(empty);
+  auto load_weight = [&](int k0, uint32_t a_dst, uint32_t b_dst, uint32_t bar) {
     if (TRANSPOSED) {
-      uint8_t* a_dst = a_tiles + size_t(s) * a_bytes;
       if (A_MN) {  // [k rows][64 a-elements] boxes, one per 64 a-elements
-        tma_load_2d(a_dst, &map_a, a0, k0, &full[s]);
-        tma_load_2d(a_dst + BK * 128, &map_a, a0 + 64, k0, &full[s]);
+        tma_load_2d(a_dst, &map_a, a0, k0, bar);
+        tma_load_2d(a_dst + BK * 128, &map_a, a0 + 64, k0, bar);
       } else {     // [a rows][64 k-elements]
-        tma_load_2d(a_dst, &map_a, k0, a0, &full[s]);
+        tma_load_2d(a_dst, &map_a, k0, a0, bar);
       }
     } else {
-      uint8_t* b_dst = b_tiles + size_t(s) * b_stride;
       if (B_MN) {
-        for (int j = 0; j < p.bn; j += 64) tma_load_2d(b_dst + size_t(j / 64) * BK * 128, &map_b, b0 + j, k0, &full[s]);
+        for (int j = 0; j < p.bn; j += 64, b_dst += BK * 128) tma_load_2d(b_dst, &map_b, b0 + j, k0, bar);
       } else {
-        tma_load_2d(b_dst, &map_b, k0, b0, &full[s]);
+        tma_load_2d(b_dst, &map_b, k0, b0, bar);
       }
     }
   };
-  auto load_tokens = [&](int i, int s) {
-    int k0 = (kb_begin + i) * BK;
+  auto load_tokens = [&](int k0, uint32_t a_dst, uint32_t b_dst, uint32_t bar) {
     if (TRANSPOSED) {
-      tma_load_2d(b_tiles + size_t(s) * b_stride, &map_b, k0, b0, &full[s]);  // tokens are K-major
+      tma_load_2d(b_dst, &map_b, k0, b0, bar);  // tokens are K-major
     } else {
-      tma_load_2d(a_tiles + size_t(s) * a_bytes, &map_a, k0, a0, &full[s]);
+      tma_load_2d(a_dst, &map_a, k0, a0, bar);
     }
   };
   const int first = min(n_kb, p.stages);
   const uint32_t stage_bytes = a_bytes + (fused_ln ? 0u : b_bytes);
-  if (warp == 0 && lane == 0) {
-    for (int i = 0; i < first; ++i) {
-      mbar_expect_tx(&full[i], stage_bytes);
-      load_weight(i, i);
-    }
+  // the first round of the ring: lane s of warp 0 fills stage s, all at the same time
+  const bool fills = warp == 0 && lane < first;
+  const int fill_k0 = (kb_begin + lane) * BK;
+  const uint32_t fill_a = a_base + uint32_t(lane) * a_bytes, fill_b = b_base + uint32_t(lane) * b_stride;
+  const uint32_t fill_bar = full_base + uint32_t(lane) * 8u;
+  if (fills) {
+    mbar_expect_tx(fill_bar, stage_bytes);
+    load_weight(fill_k0, fill_a, fill_b, fill_bar);
   }
   __syncwarp();
   if (p.splits > 1) cluster_sync();  // every CTA of the cluster is running before anyone writes into another
 
-  if (warp == 0 && lane == 0) {
-    // ---- producer: one thread feeds the ring of stages -------------------------------------
-    pdl_wait();
-    if (!fused_ln) {
-      for (int i = 0; i < first; ++i) load_tokens(i, i);
+  if (warp == 0) {
+    if (fills) {
+      pdl_wait();
+      if (!fused_ln) load_tokens(fill_k0, fill_a, fill_b, fill_bar);
     }
-    for (int i = first; i < n_kb; ++i) {
-      int s = i % p.stages;
-      if (!mbar_wait(&empty[s], uint32_t((i / p.stages - 1) & 1))) {
-        atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
-        break;
+    __syncwarp();
+    if (first < n_kb) {
+      // ---- producer: from the ring's second round on the warp runs the loop and one elected
+      // lane issues ------------------------------------------------------------------------
+      int stage = 0, k0 = (kb_begin + first) * BK;   // first == p.stages here
+      uint32_t parity = 0, a_dst = a_base, b_dst = b_base;
+      for (int i = first; i < n_kb; ++i) {
+        if (!mbar_wait(empty_base + uint32_t(stage) * 8u, parity)) {
+          if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
+          break;
+        }
+        if (elect_one()) {
+          const uint32_t bar = full_base + uint32_t(stage) * 8u;
+          mbar_expect_tx(bar, stage_bytes);
+          load_weight(k0, a_dst, b_dst, bar);
+          if (!fused_ln) load_tokens(k0, a_dst, b_dst, bar);
+        }
+        __syncwarp();
+        k0 += BK;
+        a_dst += a_bytes;
+        b_dst += b_stride;
+        if (++stage == p.stages) {
+          stage = 0;
+          parity ^= 1u;
+          a_dst = a_base;
+          b_dst = b_base;
+        }
       }
-      mbar_expect_tx(&full[s], stage_bytes);
-      load_weight(i, s);
-      if (!fused_ln) load_tokens(i, s);
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer ------------------------------------------------------------------------
-    uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(A_MN) << 15) | (uint32_t(B_MN) << 16) |
-                     (uint32_t(p.bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+  } else if (warp == 1) {
+    // ---- MMA issuer: the warp runs the loop, one elected lane issues -------------------------
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(A_MN) << 15) | (uint32_t(B_MN) << 16) |
+                           (uint32_t(p.bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
     bool ok = true;
     if (fused_ln && !mbar_wait(tokens_ready, 0)) {
-      atomicMax(p.error_flag, R2_ERR_TIMEOUT_TOKENS);
+      if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_TOKENS);
       ok = false;
     }
+    // Descriptors without their address field, and the address (in 16-byte units) of the current
+    // stage's tiles. 16 k-elements further is 32 bytes along a K-major row, or 16 rows of 128
+    // bytes in an MN-major tile, whose 64-element chunks lie 8192 bytes apart.
+    const uint64_t da_fixed = A_MN ? smem_desc(0, BK * 128, 1024) : smem_desc(0, 16, 1024);
+    const uint64_t db_fixed = B_MN ? smem_desc(0, BK * 128, 1024) : smem_desc(0, 16, 1024);
+    constexpr uint32_t a_step = (A_MN ? UMMA_K * 128 : 32) >> 4, b_step = (B_MN ? UMMA_K * 128 : 32) >> 4;
+    int stage = 0;
+    // (only the offset within the CTA's shared memory goes into a descriptor: in a cluster the
+    // address of a CTA other than the first carries its rank in high bits)
+    const uint32_t a_first = (a_base >> 4) & 0x3FFFu, b_first = (b_base >> 4) & 0x3FFFu;
+    uint32_t parity = 0, a_at = a_first, b_at = b_first;
     for (int i = 0; i < n_kb && ok; ++i) {
-      int s = i % p.stages;
-      if (!mbar_wait(&full[s], uint32_t((i / p.stages) & 1))) {
-        atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
+      if (!mbar_wait(full_base + uint32_t(stage) * 8u, parity)) {
+        if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t a_addr = smem_u32(a_tiles + size_t(s) * a_bytes);
-      uint32_t b_addr = smem_u32(b_tiles + size_t(fused_ln ? i : s) * b_stride);
+      if (elect_one()) {
 #pragma unroll
-      for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-        // K-major: 16 k-elements further along the swizzled row = 32 bytes.
-        // MN-major: 16 k-rows of 128 bytes further = 2048 bytes; 64-element chunks are 8192 bytes apart.
-        uint64_t da = A_MN ? smem_desc(a_addr + kk * (UMMA_K * 128), BK * 128, 1024) : smem_desc(a_addr + kk * 32, 16, 1024);
-        uint64_t db = B_MN ? smem_desc(b_addr + kk * (UMMA_K * 128), BK * 128, 1024) : smem_desc(b_addr + kk * 32, 16, 1024);
-        umma_bf16(tmem_base, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          umma_bf16(tmem_base, da_fixed + uint64_t(a_at + kk * a_step), db_fixed + uint64_t(b_at + kk * b_step), idesc,
+                    (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_base + uint32_t(stage) * 8u);  // the stage is free once these MMAs have read it
       }
-      umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+      __syncwarp();
+      a_at += a_bytes >> 4;
+      b_at += b_stride >> 4;  // with a fused norm the token tiles are not a ring: tile i follows tile i - 1
+      if (++stage == p.stages) {
+        stage = 0;
+        parity ^= 1u;
+        a_at = a_first;
+        if (!fused_ln) b_at = b_first;
+      }
     }
-    umma_commit(acc_ready);    // arrives when every MMA above has completed (also on the error path)
+    if (elect_one()) umma_commit(smem_u32(acc_ready));  // arrives when every MMA above has completed (also on the error path)
+    __syncwarp();
   }
 
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
@@ -388,6 +632,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tokens_ready)) : "memory");
     }
     const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
+    if constexpr (!TRANSPOSED) {
+      // the tile's bias, once for the four epilogue warps, while the products run
+      for (int j = int(threadIdx.x) - 64; j < p.bn; j += 128) reduce[j] = (p.bias != nullptr && b0 + j < p.b_total) ? p.bias[b0 + j] : 0.f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -419,8 +668,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int a = a0 + q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
     const bool ok = acc_ok;
-    const bool finish = true;
-    if (finish && ok) {
+    if constexpr (!TRANSPOSED) {
+      // every product has completed: the first tiles' shared memory serves as the warps' slabs
+      if (ok && a0 + q * 32 < p.a_total) {
+        finish_tile_rows(p, lane_addr, smem_u32(a_tiles) + uint32_t(q * STAGING_WORDS) * 4u, reduce, a0 + q * 32, b0, 0, p.bn, lane, n_kb > 0);
+      }
+    } else if (ok) {
       const bool a_ok = a < p.a_total;
       // In the transposed form the thread's feature is fixed: one bias value serves every column.
       const float bias_a = (TRANSPOSED && a_ok && p.bias != nullptr) ? p.bias[a] : 0.f;
@@ -444,7 +697,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const int nb = min(16, p.b_total - (b0 + c0));  // columns of this chunk that exist
         if (!a_ok || nb <= 0) continue;
-        if (TRANSPOSED) {
+        {
           // lanes hold consecutive features: every column is one coalesced row segment
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] += bias_a;
@@ -474,72 +727,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (j < nb) dst[size_t(j) * p.ldo] = v[j];
             }
           }
-        } else {
-          // the thread holds 16 consecutive features of its token's row
-          const int f0 = b0 + c0;
-          if (p.bias != nullptr) {
-            if (nb == 16 && (reinterpret_cast<uintptr_t>(p.bias + f0) & 15) == 0) {
-              const float4* b4 = reinterpret_cast<const float4*>(p.bias + f0);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float4 t = __ldg(b4 + j);
-                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j < nb) v[j] += p.bias[f0 + j];
-              }
-            }
-          }
-          if (p.act == R2_ACT_GELU_TANH) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh_fast(v[j]);
-          } else if (p.act == R2_ACT_GELU_ERF) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
-          }
-          if (p.residual != nullptr) {
-            const float* rrow = p.residual + size_t(a) * p.ldr + f0;
-            if (nb == 16 && (reinterpret_cast<uintptr_t>(rrow) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float4 t = *reinterpret_cast<const float4*>(rrow + 4 * j);
-                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j < nb) v[j] += rrow[j];
-              }
-            }
-          }
-          if (p.out_is_bf16) {
-            bf16* dst = reinterpret_cast<bf16*>(p.out) + size_t(a) * p.ldo + f0;
-            if (nb == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              uint4 w0, w1;
-              w0.x = pack2(v[0], v[1]); w0.y = pack2(v[2], v[3]); w0.z = pack2(v[4], v[5]); w0.w = pack2(v[6], v[7]);
-              w1.x = pack2(v[8], v[9]); w1.y = pack2(v[10], v[11]); w1.z = pack2(v[12], v[13]); w1.w = pack2(v[14], v[15]);
-              reinterpret_cast<uint4*>(dst)[0] = w0;
-              reinterpret_cast<uint4*>(dst)[1] = w1;
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j < nb) dst[j] = __float2bfloat16_rn(v[j]);
-              }
-            }
-          } else {
-            float* dst = reinterpret_cast<float*>(p.out) + size_t(a) * p.ldo + f0;
-            if (nb == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j < nb) dst[j] = v[j];
-              }
-            }
-          }
         }
       }
     }
@@ -550,6 +737,217 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---- the pair form: two CTAs, one 256 x BN tile ------------------------------------------------
+//
+// For many tokens the product is bound by what the SMs can pull from L2, so the tile is doubled
+// without doubling any CTA's loads: the two CTAs of a cluster each hold 128 token rows and HALF of
+// the weight tile's columns, and the leader's MMA thread issues tcgen05.mma.cta_group::2, which
+// reads both CTAs' shared memory and writes each CTA's 128 x BN accumulator into its own tensor
+// memory. Per CTA and k-block that is 16 KB of tokens + BN/2 x 128 B of weights for 128 x BN x 64
+// multiply-adds: half the bytes per flop of the single-CTA tile of the same width.
+//
+// Each CTA's TMA loads signal the LEADER's `full` barrier (the loads carry .cta_group::2, which
+// lets the barrier lie in the peer CTA); the leader's commits arrive on the `empty` and
+// `acc_ready` barriers of both CTAs (multicast commit). Both CTAs allocate and free tensor memory
+// as a pair. Waits are bounded as in the single-CTA kernel.
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs
+// issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(uint16_t(3)) : "memory");
+}
+
+constexpr int PAIR_THREADS = 320;  // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: epilogue
+
+template <bool B_MN>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int half = p.bn / 2;                              // weight columns held by one CTA
+  const uint32_t a_bytes = BM * BK * 2;
+  const uint32_t b_bytes = uint32_t(half) * BK * 2;       // a multiple of 1024: half is a multiple of 8
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + size_t(p.stages) * a_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + size_t(p.stages) * b_bytes);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_ready = empty + MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  float* bias_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));  // the tile's bias, BIAS_SLOTS floats
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int a0 = blockIdx.x * BM;                          // the cluster lies along x: rows of the pair's two halves
+  const int b_tile0 = blockIdx.y * p.bn;                   // first column of the pair's tile
+  const int b0 = b_tile0 + int(rank) * half;               // first column this CTA loads
+  const int n_kb = p.n_kb;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < uint32_t(p.bn)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers exist before either's loads or commits signal them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  // The next kernel may start (set up, prefetch its weights) from here on, and not earlier: its
+  // CTAs allocate tensor memory before they wait for this kernel, so a CTA of this kernel that
+  // still had to allocate could find every column taken by CTAs that wait for it.
+  pdl_launch_dependents();
+
+  const uint32_t a_base = smem_u32(a_tiles), b_base = smem_u32(b_tiles);
+  const uint32_t full_base = smem_u32(full), empty_base = smem_u32(empty);
+  uint32_t leader_full_base;  // the leader's `full` barriers as seen from this CTA
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_full_base) : "r"(full_base), "r"(0u));
+  auto load_weight = [&](int k0, uint32_t b_dst, uint32_t bar) {
+    if (B_MN) {
+      for (int j = 0; j < half; j += 64, b_dst += BK * 128) tma_load_2d_pair(b_dst, &map_b, b0 + j, k0, bar);
+    } else {
+      tma_load_2d_pair(b_dst, &map_b, k0, b0, bar);
+    }
+  };
+  const int first = min(n_kb, p.stages);
+  const uint32_t pair_bytes = 2u * (a_bytes + b_bytes);  // what both CTAs bring into one stage
+
+  if (warp == 0) {
+    // the first round of the ring: lane s fills stage s; weights may be asked for before the
+    // previous kernel has finished, the tokens it may have written only after it
+    if (lane < first) {
+      const int k0 = lane * BK;
+      const uint32_t bar = leader_full_base + uint32_t(lane) * 8u;
+      if (rank == 0) mbar_expect_tx(full_base + uint32_t(lane) * 8u, pair_bytes);
+      load_weight(k0, b_base + uint32_t(lane) * b_bytes, bar);
+      pdl_wait();
+      tma_load_2d_pair(a_base + uint32_t(lane) * a_bytes, &map_a, k0, a0, bar);
+    }
+    __syncwarp();
+    if (first < n_kb) {
+      // ---- producer: from the ring's second round on the warp runs the loop and one elected
+      // lane issues ------------------------------------------------------------------------
+      int stage = 0, k0 = first * BK;
+      uint32_t parity = 0, a_dst = a_base, b_dst = b_base;
+      for (int i = first; i < n_kb; ++i) {
+        if (!mbar_wait(empty_base + uint32_t(stage) * 8u, parity)) {
+          if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
+          break;
+        }
+        if (elect_one()) {
+          const uint32_t bar = leader_full_base + uint32_t(stage) * 8u;
+          if (rank == 0) mbar_expect_tx(full_base + uint32_t(stage) * 8u, pair_bytes);
+          load_weight(k0, b_dst, bar);
+          tma_load_2d_pair(a_dst, &map_a, k0, a0, bar);
+        }
+        __syncwarp();
+        k0 += BK;
+        a_dst += a_bytes;
+        b_dst += b_bytes;
+        if (++stage == p.stages) {
+          stage = 0;
+          parity ^= 1u;
+          a_dst = a_base;
+          b_dst = b_base;
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ---- MMA issuer of the pair (M = 256 over the two CTAs, N = bn): the warp runs the loop, one
+    // elected lane issues ------------------------------------------------------------------------
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(B_MN) << 16) | (uint32_t(p.bn >> 3) << 17) |
+                           (uint32_t((2 * BM) >> 4) << 24);
+    const uint64_t da_fixed = smem_desc(0, 16, 1024);
+    const uint64_t db_fixed = B_MN ? smem_desc(0, BK * 128, 1024) : smem_desc(0, 16, 1024);
+    constexpr uint32_t a_step = 32 >> 4, b_step = (B_MN ? UMMA_K * 128 : 32) >> 4;
+    int stage = 0;
+    // (only the offset within the CTA's shared memory goes into a descriptor: in a cluster the
+    // address of a CTA other than the first carries its rank in high bits)
+    const uint32_t a_first = (a_base >> 4) & 0x3FFFu, b_first = (b_base >> 4) & 0x3FFFu;
+    uint32_t parity = 0, a_at = a_first, b_at = b_first;
+    for (int i = 0; i < n_kb; ++i) {
+      if (!mbar_wait(full_base + uint32_t(stage) * 8u, parity)) {
+        if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          umma_bf16_pair(tmem_base, da_fixed + uint64_t(a_at + kk * a_step), db_fixed + uint64_t(b_at + kk * b_step), idesc,
+                         (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit_pair(empty_base + uint32_t(stage) * 8u);
+      }
+      __syncwarp();
+      a_at += a_bytes >> 4;
+      b_at += b_bytes >> 4;
+      if (++stage == p.stages) {
+        stage = 0;
+        parity ^= 1u;
+        a_at = a_first;
+        b_at = b_first;
+      }
+    }
+    if (elect_one()) umma_commit_pair(smem_u32(acc_ready));  // also on the error path: both epilogues go on and the flag tells
+    __syncwarp();
+  }
+
+  // ---- epilogue: each CTA writes its own 128 rows of the tile's bn columns -------------------
+  if (warp >= 2) {
+    pdl_wait();
+    const int q = warp & 3;              // the accumulator rows (tensor-memory lanes) this warp may read
+    const int side = (warp - 2) >> 2;    // warps 2..5 take the tile's first half of the columns, 6..9 the second
+    for (int j = int(threadIdx.x) - 64; j < p.bn; j += PAIR_THREADS - 64) bias_s[j] = (p.bias != nullptr && b_tile0 + j < p.b_total) ? p.bias[b_tile0 + j] : 0.f;
+    asm volatile("bar.sync 1, %0;" ::"n"(PAIR_THREADS - 64) : "memory");
+    bool ok = mbar_wait(acc_ready, 0);
+    if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    // every product of the pair has completed: the first tiles' shared memory serves as the slabs
+    if (ok && a0 + q * 32 < p.a_total) {
+      finish_tile_rows(p, lane_addr, smem_u32(a_tiles) + uint32_t((warp - 2) * STAGING_WORDS) * 4u, bias_s, a0 + q * 32, b_tile0,
+                       side * half, (side + 1) * half, lane, true);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();  // neither CTA frees tensor memory or leaves while the other may still use it
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
@@ -696,7 +1094,8 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   }
   pl.kb_per_split = (pl.n_kb + pl.splits - 1) / pl.splits;
   const size_t a_bytes = BM * BK * 2, b_stride = (size_t(pl.bn) * BK * 2 + 1023) & ~size_t(1023);
-  const size_t fixed = 1024 + (2 * MAX_STAGES + 2) * 8 + 32 + size_t(pl.splits - 1) * pl.bn * BM * 4;
+  const size_t fixed = 1024 + (2 * MAX_STAGES + 2) * 8 + 32 +
+                       (pl.swapped ? size_t(pl.splits - 1) * pl.bn * BM * 4 : size_t(BIAS_SLOTS) * 4);  // partial sums, or the bias
   // with more tiles than SMs, leave room for two CTAs on an SM: one's epilogue under the other's loads
   const size_t budget = (tiles * pl.splits > N_SMS ? 113 * 1024 : 227 * 1024) - fixed;
   if (fused_ln) {
@@ -713,12 +1112,97 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > pl.kb_per_split) stages = pl.kb_per_split;
   if (stages < 1) stages = 1;
+  // the token-major epilogue lays its four slabs over the tiles: a short K keeps stages it does not fill
+  while (!pl.swapped && size_t(stages) * (a_bytes + b_stride) < 4 * size_t(STAGING_WORDS) * 4) ++stages;
   pl.stages = stages;
   pl.smem = fixed + size_t(stages) * (a_bytes + b_stride);
   return pl;
 }
 
+// The pair form: tile width (256, or 128 when that gives too few CTAs), stages, shared memory.
+struct PairPlan {
+  bool use;
+  int bn, n_kb, stages;
+  size_t smem;
+  dim3 grid;
+};
+
+PairPlan make_pair_plan(int m, int n, int k, int w_is_nk) {
+  PairPlan pl;
+  pl.use = false;
+  if (m < 192 || n < 128) return pl;  // the second CTA of a pair would hold (almost) no rows, or the tile no columns
+  (void)w_is_nk;
+  // Measured (2,048 and 8,192 rows, K 768 and 3,072): with more 128 x 128 tiles than SMs the
+  // single-CTA form runs two CTAs to an SM, one's epilogue under the other's products, and wins
+  // unless K is long; with fewer tiles, or a long K, the pair's cheaper k-blocks win.
+  const int single_tiles = ((m + BM - 1) / BM) * ((n + 127) / 128);
+  if (single_tiles > N_SMS && k < 2048) return pl;
+  const int row_pairs = (m + 2 * BM - 1) / (2 * BM);
+  pl.bn = 256;
+  if (n < 256 || 2 * row_pairs * ((n + 255) / 256) < (N_SMS * 3) / 5) pl.bn = 128;
+  const int col_tiles = (n + pl.bn - 1) / pl.bn;
+  const int ctas = 2 * row_pairs * col_tiles;
+  pl.n_kb = (k + BK - 1) / BK;
+  const size_t stage = size_t(BM) * BK * 2 + size_t(pl.bn / 2) * BK * 2;
+  const size_t fixed = 1024 + (2 * MAX_STAGES + 1) * 8 + 48 + size_t(BIAS_SLOTS) * 4;
+  (void)ctas;
+  const size_t budget = 227 * 1024 - fixed;  // one CTA per SM: its eight epilogue warps need the registers
+  int stages = int(budget / stage);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > pl.n_kb) stages = pl.n_kb;
+  if (stages < 1) return pl;
+  const size_t slabs = 8 * size_t(STAGING_WORDS) * 4;  // the epilogue's slabs lie over the tiles:
+  while (size_t(stages) * stage < slabs) ++stages;     // a short K keeps stages it does not fill
+  pl.stages = stages;
+  pl.smem = fixed + size_t(stages) * stage;
+  pl.grid = dim3(2 * row_pairs, col_tiles, 1);
+  pl.use = true;
+  return pl;
+}
+
+template <bool B_MN>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, const PairPlan& pl, cudaStream_t stream) {
+  auto kernel = gemm_tc_pair_kernel<B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return int(e);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = pl.grid;
+  config.blockDim = dim3(PAIR_THREADS);
+  config.dynamicSmemBytes = pl.smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+  attr[n_attr].val.clusterDim.x = 2;
+  attr[n_attr].val.clusterDim.y = 1;
+  attr[n_attr].val.clusterDim.z = 1;
+  ++n_attr;
+  if (g_r2_pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  config.attrs = attr;
+  config.numAttrs = n_attr;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, ma, mb, p);
+  if (e != cudaSuccess) return int(e);
+  return launch_status();
+}
+
+bool g_pair_form = true;  // r2_gemm_tc_set_pair switches it (tests and measurements compare the two forms)
+
 }  // namespace
+
+extern "C" int r2_gemm_tc_set_pair(int on) {
+  int before = g_pair_form ? 1 : 0;
+  g_pair_form = on != 0;
+  return before;
+}
 
 // How r2_gemm_tc would run (m, n, k): tile width on the b side, CTAs per cluster (slices of K), stages.
 extern "C" int r2_gemm_tc_plan(int m, int n, int k, int w_is_nk, int* bn_out, int* splits_out, int* stages_out) {
@@ -786,6 +1270,29 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   const int bn = pl.bn;
   const size_t smem = pl.smem;
   dim3 grid((p.a_total + BM - 1) / BM, (p.b_total + bn - 1) / bn, pl.splits);
+
+  if (!pl.swapped && !fused_ln && g_pair_form) {
+    const PairPlan pp = make_pair_plan(m, n, k, w_is_nk);
+    if (pp.use) {
+      p.bn = pp.bn;
+      p.stages = pp.stages;
+      p.splits = 1;
+      p.kb_per_split = pp.n_kb;
+      CUtensorMap pa, pb;
+      bool maps = make_map(&pa, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, BM);
+      if (w_is_nk) {
+        maps = maps && make_map(&pb, w, uint64_t(k), uint64_t(n), uint64_t(ldw), BK, uint32_t(pp.bn / 2));
+        if (maps) return launch_pair<false>(pa, pb, p, pp, stream);
+      } else {
+        maps = maps && make_map(&pb, w, uint64_t(n), uint64_t(k), uint64_t(ldw), 64, BK);
+        if (maps) return launch_pair<true>(pa, pb, p, pp, stream);
+      }
+      p.bn = pl.bn;  // no tensor map: the single-CTA form decides
+      p.stages = pl.stages;
+      p.splits = pl.splits;
+      p.kb_per_split = pl.kb_per_split;
+    }
+  }
 
   CUtensorMap ma, mb;
   bool ok;

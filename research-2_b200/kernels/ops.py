@@ -174,6 +174,17 @@ def use_tensor_core_gemm(on: bool) -> bool:
     return before
 
 
+def use_pair_gemm(on: bool) -> bool:
+    """Switch the two-CTA form (tcgen05.mma.cta_group::2, 256-row tiles) of the tensor-core product
+    for many rows on or off; off, every product runs as single-CTA 128-row tiles. Returns the
+    previous setting."""
+    return bool(_lib("gemm_tc").r2_gemm_tc_set_pair(int(bool(on))))
+
+
+if os.environ.get("R2_PAIR_GEMM", "1") == "0":
+    use_pair_gemm(False)
+
+
 class _Workspace:
     """Scratch of sliced decode attention (the slices' partial results, arrival counters that are
     zero between launches) and the word in which kernels record a bounded wait that ran out.

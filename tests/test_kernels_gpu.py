@@ -81,6 +81,39 @@ def test_linear(m, k, n, dtype, w_is_nk):
     torch.testing.assert_close(got, base + bias + res, **(t if dtype == torch.float32 else dict(atol=2e-4, rtol=2e-4)))
 
 
+@pytest.mark.parametrize("m,k,n", [(192, 64, 128), (300, 200, 520), (2048, 768, 2304), (1000, 3072, 768), (257, 96, 1031), (512, 768, 3072)])
+@pytest.mark.parametrize("w_is_nk", [False, True])
+def test_linear_many_rows_on_a_cta_pair(m, k, n, w_is_nk):
+    """192 rows or more run as 256-row tiles over two CTAs (tcgen05.mma.cta_group::2): same result
+    as the single-CTA tiles and as a float32 statement, with every epilogue and ragged edges."""
+    o = ops()
+    torch.manual_seed(m + k + n)
+    a = torch.randn(m, k).bfloat16().to(DEV)
+    w = (torch.randn(n, k) if w_is_nk else torch.randn(k, n)).mul(k**-0.5).bfloat16().to(DEV)
+    bias = torch.randn(n).to(DEV)
+    res = torch.randn(m, n).to(DEV)
+    base = a.float() @ (w.float().T if w_is_nk else w.float())
+
+    def run():
+        return (o.linear(a, w, bias, w_is_nk=w_is_nk, act="gelu_new"),
+                o.linear(a, w, bias, w_is_nk=w_is_nk, residual=res),
+                o.linear(a, w, None, w_is_nk=w_is_nk, out_dtype=torch.float32))
+
+    before = o.use_pair_gemm(True)
+    try:
+        pair = run()
+        o.use_pair_gemm(False)
+        single = run()
+    finally:
+        o.use_pair_gemm(before)
+    assert o.device_errors() == 0
+    for x, y in zip(pair, single):
+        torch.testing.assert_close(x.float(), y.float(), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(pair[0].float(), F.gelu(base + bias, approximate="tanh"), **tol(torch.bfloat16))
+    torch.testing.assert_close(pair[1], base + bias + res, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(pair[2], base, atol=2e-4, rtol=2e-4)
+
+
 @pytest.mark.parametrize("m,k,n", [(1, 768, 2304), (8, 768, 3072), (64, 768, 2304), (5, 96, 288), (33, 1600, 4800), (17, 320, 96)])
 @pytest.mark.parametrize("w_is_nk", [False, True])
 def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
