@@ -141,7 +141,7 @@ class DecodeLoop:
             self.step_fn(b)
         torch.cuda.synchronize()
         # every decode step's batch, precomputed into one pinned array
-        self.graph = self.step_fn._graph(batch)
+        self.graph = self.step_fn._graph(batch, batch)  # the decode-only bucket: rows == entries
         host = self.graph.host
         self.skip = host.section("positions")[0]  # input_ids stay on the device
         self.staged = torch.zeros(n_steps, host.buf.shape[0], dtype=torch.int32).pin_memory()
@@ -193,7 +193,7 @@ def prefill_point(model, cfg, pk: dict) -> dict:
     from research_2_b200.engine.step import StepFunction
 
     n_req, length = 2, 1024
-    step_fn = StepFunction(model, PAGE, n_req * length // PAGE, n_req)
+    step_fn = StepFunction(model, PAGE, n_req * length // PAGE, n_req, capture=True)  # a shape that repeats runs as a graph
     cache = CacheManager(step_fn.cache_groups(), n_req, model.max_seq_len)
     gen = torch.Generator().manual_seed(SEED + 1)
     prompts = torch.randint(0, model.vocab_size, (n_req, length), generator=gen, dtype=torch.int32).numpy()

@@ -7,10 +7,15 @@ place; the cache manager and the scheduler own the indices. Reference shape of t
 `Step.forward(plan) -> logits`, `Step.sample` (kelpie-models/kelpie_models/sdk/step.py:102-184),
 `to_device` (kelpie-models/kelpie_models/sdk/device.py:124-149).
 
-Decode-only batches (every entry one row) can run as a CUDA graph per batch-size bucket: the
-batch is copied into the graph's static buffer and the graph is replayed; forward pass and
-sampling are both inside it. The reference captures its decode buckets the same way and keeps
-prefill eager (kelpie-models/kelpie_models/sdk/captured.py:8-17,117-191).
+With `capture` on, a step runs as a CUDA graph per shape bucket: the batch is copied into the
+graph's static buffer and the graph is replayed; forward pass and sampling are both inside it.
+Decode-only batches (every entry one row) have a bucket per batch size, captured at first use,
+as the reference captures its decode buckets (kelpie-models/kelpie_models/sdk/captured.py:8-17,
+117-191). The reference keeps prefill eager; here a step with prompt portions has a bucket per
+(rows rounded up to 128, entries rounded up), captured when a shape comes a second time, since
+a step of some hundred launches of a few microseconds each is otherwise bound by the host.
+Everything beyond a batch's own counts is inert padding (rows of no entry, entries of no rows),
+so what a graph computes for the real rows does not depend on its capacity.
 """
 
 from __future__ import annotations
@@ -37,9 +42,9 @@ class StepContext:
         # shape facts that choose kernels: inside a graph every row is an entry of its own and
         # contexts may reach the whole table; outside, the host batch says what is there
         if self.captured:
-            self.decode_only = True
+            self.decode_only = bool(r == t)
             self.max_context = host.max_context_bound
-            self.n_attention_tiles = 0
+            self.n_attention_tiles = 0 if self.decode_only else t // 64 + r  # each entry may end in a partial tile
         else:
             self.decode_only = bool(r == t and r > 0)
             self.max_context = int(host.seq_lens[:r].max()) if r else 0
@@ -80,19 +85,20 @@ def _bucket(n: int) -> int:
     return b if n <= 8 else -(-n // 8) * 8
 
 
-class DecodeGraph:
-    """Forward pass + sampling of a decode-only batch of up to `cap` entries, as one CUDA graph."""
+class StepGraph:
+    """Forward pass + sampling of a batch of up to `t_cap` rows in up to `r_cap` entries (one
+    logit row per entry), as one CUDA graph. t_cap == r_cap is the decode-only form."""
 
-    def __init__(self, step_fn: "StepFunction", cap: int):
-        self.cap = cap
-        self.host = StepBatch(BatchLayout(cap, cap, cap, step_fn.table_widths), pinned=True)
+    def __init__(self, step_fn: "StepFunction", t_cap: int, r_cap: int):
+        self.cap = r_cap
+        self.host = StepBatch(BatchLayout(t_cap, r_cap, r_cap, step_fn.table_widths), pinned=True)
         self.host.max_context_bound = step_fn.model.max_seq_len
         self.host.pad()
         self.host.set_logit_rows([])
         self.host.set_sampling([], [], [], [], [])
         self.dev = torch.zeros(self.host.buf.shape[0], dtype=torch.int32, device=step_fn.device)
         self.dev.copy_(self.host._pinned_tensor)
-        self.ctx = StepContext(self.host, self.dev, counts=(cap, cap, cap))
+        self.ctx = StepContext(self.host, self.dev, counts=(t_cap, r_cap, r_cap))
         side = torch.cuda.Stream(device=step_fn.device)
         side.wait_stream(torch.cuda.current_stream(step_fn.device))
         with torch.cuda.stream(side):  # inert warm-up: every row is a pad row
@@ -112,7 +118,7 @@ class DecodeGraph:
     def _capture(self, step_fn: "StepFunction") -> None:
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, pool=step_fn.graph_pool()):
             self.logits = step_fn.forward(self.ctx)
             self.tokens = step_fn.sample(self.logits, self.ctx)
         self.kernels = ops.launch_count() - before
@@ -140,9 +146,18 @@ class StepFunction:
         # A mixer with state of its own folds an entry's rows on the host side of the launch, so
         # only models whose mixers all say `capturable` may run inside a CUDA graph.
         self.capture = capture and all(getattr(b.mixer, "capturable", False) for b in model.blocks)
-        self._graphs: dict[int, DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], StepGraph] = {}
+        self._seen: set[tuple[int, int]] = set()   # shapes with prompt portions that came once
+        self._pool = None
         self._batches: dict[tuple[int, int, int], StepBatch] = {}
         self.h2d_bytes = 0
+
+    def graph_pool(self):
+        """One memory pool for every graph of this step function: they never run at the same time,
+        so their activations may share memory. A graph's outputs hold until the next step."""
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        return self._pool
 
     def cache_groups(self) -> list[GroupSpec]:
         return list(self.groups)
@@ -151,11 +166,20 @@ class StepFunction:
     def new_batch(self, n_tokens: int, n_entries: int, n_logit_rows: int, decode_only: bool = False) -> StepBatch:
         """A pinned host batch with room for the given counts. Batches are kept and handed
         out again; one is not reused before its last upload has finished."""
-        if decode_only and self.capture:
-            batch = self._graph(n_entries).host
+        t_cap = _bucket(n_tokens) if n_tokens <= 64 else -(-n_tokens // 128) * 128
+        r_cap = _bucket(max(n_entries, 1))
+        graph = None
+        if self.capture and decode_only:
+            graph = self._graph(r_cap, r_cap)
+        elif self.capture and n_logit_rows <= n_entries and t_cap > r_cap:  # (t_cap == r_cap is the decode-only graph)
+            if (t_cap, r_cap) in self._graphs or (t_cap, r_cap) in self._seen:
+                graph = self._graph(t_cap, r_cap)
+            else:
+                self._seen.add((t_cap, r_cap))
+        if graph is not None:
+            batch = graph.host
         else:
-            t_cap = _bucket(n_tokens) if n_tokens <= 64 else -(-n_tokens // 128) * 128
-            key = (t_cap, _bucket(max(n_entries, 1)), _bucket(max(n_logit_rows, 1)) if n_logit_rows <= 64 else t_cap)
+            key = (t_cap, r_cap, _bucket(max(n_logit_rows, 1)) if n_logit_rows <= 64 else t_cap)
             batch = self._batches.get(key)
             if batch is None:
                 batch = StepBatch(BatchLayout(key[0], key[1], max(key[2], n_logit_rows), self.table_widths), pinned=True)
@@ -165,14 +189,17 @@ class StepFunction:
             done.synchronize()
         return batch
 
-    def _graph(self, n_entries: int) -> DecodeGraph:
-        cap = _bucket(n_entries)
-        graph = self._graphs.get(cap)
+    def _graph(self, t_cap: int, r_cap: int) -> StepGraph:
+        graph = self._graphs.get((t_cap, r_cap))
         if graph is None:
             with torch.cuda.device(self.device):
-                graph = DecodeGraph(self, cap)
-            self._graphs[cap] = graph
+                graph = StepGraph(self, t_cap, r_cap)
+            self._graphs[(t_cap, r_cap)] = graph
         return graph
+
+    def _graph_of(self, batch: StepBatch) -> StepGraph | None:
+        graph = self._graphs.get((batch.t_cap, batch.r_cap)) if self.capture else None
+        return graph if graph is not None and batch is graph.host else None
 
     def upload(self, batch: StepBatch) -> StepContext:
         batch.pad()
@@ -213,6 +240,12 @@ class StepFunction:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
         self.validate(batch)
         with torch.cuda.device(self.device):
+            graph = self._graph_of(batch)
+            if graph is not None:
+                batch.pad()
+                graph.replay()
+                self.h2d_bytes += batch.buf.nbytes
+                return graph.logits[: batch.n_logit_rows]
             return self.forward(self.upload(batch))
 
     @torch.no_grad()
@@ -220,8 +253,8 @@ class StepFunction:
         """One token per logit row (int32, on the device); `batch.set_sampling` has been called."""
         self.validate(batch)
         with torch.cuda.device(self.device):
-            graph = self._graphs.get(batch.r_cap) if self.capture else None
-            if graph is not None and batch is graph.host:
+            graph = self._graph_of(batch)
+            if graph is not None:
                 batch.pad()
                 graph.replay()
                 self.h2d_bytes += batch.buf.nbytes

@@ -76,6 +76,22 @@ def test_bfloat16_generation_runs_with_and_without_graphs(wide_b):
     assert all(len(t) == 20 for t in eager)
 
 
+def test_prompt_portions_run_as_graphs_when_a_shape_repeats(wide_b):
+    """With capture on, a step with prompt portions is captured the second time its shape comes
+    and replayed from then on: rows and entries beyond the batch's own are padding, and the
+    tokens are those of the plain implementation (float32, so the comparison is exact)."""
+    import research_2_b200 as r2
+    from research_2_b200.engine.api import generate_with
+
+    prompts = [random_tokens(60 + i, n, 1031) for i, n in enumerate((100, 100, 100, 100, 37, 100, 150, 100))]
+    want = plain_generate(wide_b, prompts, 10, temperature=0.7, seed=11)
+    with r2.run(wide_b, dtype="float32", block_size=8, max_requests=3, max_batch_tokens=64, capture=True) as engine:
+        got = generate_with(engine, prompts, 10, temperature=0.7, seed=11)
+        shapes = [key for key in engine.step_fn._graphs if key[0] > key[1]]
+        assert shapes, "no step with prompt portions was captured"
+    assert got == want
+
+
 def test_few_pages_preempt_and_recompute(wide_a):
     """So few pages that running requests are preempted: the tokens stay the same."""
     import research_2_b200 as r2
