@@ -6,7 +6,7 @@ import ctypes as C
 
 from ..csrc.build import host_library
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 I32P = C.POINTER(C.c_int32)
 
 
@@ -28,6 +28,19 @@ class PlanC(C.Structure):
         ("req", I32P), ("start", I32P), ("rows", I32P), ("emits", I32P), ("kind", I32P),
         ("input_ids", I32P), ("temperature", C.POINTER(C.c_float)), ("top_k", I32P),
         ("sample_pos", I32P), ("key0", C.POINTER(C.c_uint32)), ("key1", C.POINTER(C.c_uint32)),
+    ]
+
+
+class StepBatchC(C.Structure):
+    """A step batch's arrays in the caller's memory with their capacities (R2StepBatch)."""
+
+    _fields_ = [
+        ("t_cap", C.c_int32), ("r_cap", C.c_int32), ("w_cap", C.c_int32), ("reserved", C.c_int32),
+        ("input_ids", C.c_void_p), ("positions", C.c_void_p), ("row_entry", C.c_void_p), ("q_start", C.c_void_p),
+        ("seq_lens", C.c_void_p), ("state_slot", C.c_void_p), ("fresh", C.c_void_p), ("logit_rows", C.c_void_p),
+        ("temperature", C.c_void_p), ("top_k", C.c_void_p), ("key0", C.c_void_p), ("key1", C.c_void_p),
+        ("sample_pos", C.c_void_p), ("slot_mapping", C.c_void_p), ("block_tables", C.c_void_p),
+        ("entry_req", C.c_void_p), ("entry_start", C.c_void_p), ("entry_rows", C.c_void_p),
     ]
 
 
@@ -83,6 +96,7 @@ def lib() -> C.CDLL:
         "r2_sched_submit": (i32, [vp, I32P, i32, i32, f32, i32, u64, I32P, i32]),
         "r2_sched_cancel": (i32, [vp, i32]),
         "r2_sched_plan": (i32, [vp, C.POINTER(PlanC)]),
+        "r2_sched_fill_step_batch": (i32, [vp, C.POINTER(StepBatchC)]),
         "r2_sched_commit": (i32, [vp, I32P, i32]),
         "r2_sched_poll": (i32, [vp, i32, I32P, i32, I32P, I32P]),
         "r2_sched_stall": (i32, [vp, C.POINTER(StallC)]),
@@ -97,7 +111,7 @@ def lib() -> C.CDLL:
         fn.argtypes = args
     if h.r2_abi_version() != ABI_VERSION:
         raise RuntimeError(f"host library ABI {h.r2_abi_version()} != expected {ABI_VERSION}")
-    for which, struct in enumerate((GroupSpecC, SchedulerConfigC, PlanC, StallC, StepEventC)):
+    for which, struct in enumerate((GroupSpecC, SchedulerConfigC, PlanC, StallC, StepEventC, StepBatchC)):
         if h.r2_sizeof(which) != C.sizeof(struct):
             raise RuntimeError(f"host library struct {struct.__name__}: size {h.r2_sizeof(which)} != {C.sizeof(struct)}")
     _lib = h

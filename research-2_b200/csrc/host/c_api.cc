@@ -45,6 +45,7 @@ int32_t r2_sizeof(int32_t which) {
     case 2: return sizeof(R2Plan);
     case 3: return sizeof(R2Stall);
     case 4: return sizeof(R2StepEvent);
+    case 5: return sizeof(R2StepBatch);
     default: return -1;
   }
 }
@@ -159,6 +160,7 @@ int32_t r2_sched_plan(void* sched, R2Plan* out) {
   return r2::SCHED_OK;
 }
 
+int32_t r2_sched_fill_step_batch(void* sched, const R2StepBatch* out) { return SC(sched)->fill_step_batch(*out); }
 int32_t r2_sched_commit(void* sched, const int32_t* tokens, int32_t n) { return SC(sched)->commit(tokens, n); }
 int32_t r2_sched_poll(void* sched, int32_t id, int32_t* out, int32_t cap, int32_t* finished, int32_t* state) {
   return SC(sched)->poll(id, out, cap, finished, state);

@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define R2_ABI_VERSION 1
+#define R2_ABI_VERSION 2
 
 typedef struct {
   int32_t page_size;
@@ -48,6 +48,31 @@ typedef struct {
   const uint32_t* key0;
   const uint32_t* key1;
 } R2Plan;
+
+/* A step batch's arrays in the caller's memory (typically one pinned buffer), with their
+   capacities: t_cap rows, r_cap entries, w_cap logit rows. slot_mapping is [n_groups][t_cap],
+   block_tables the concatenation over groups of [r_cap][table width]. */
+typedef struct {
+  int32_t t_cap, r_cap, w_cap, reserved;
+  int32_t* input_ids;
+  int32_t* positions;
+  int32_t* row_entry;
+  int32_t* q_start;
+  int32_t* seq_lens;
+  int32_t* state_slot;
+  int32_t* fresh;
+  int32_t* logit_rows;
+  float* temperature;
+  int32_t* top_k;
+  uint32_t* key0;
+  uint32_t* key1;
+  int32_t* sample_pos;
+  int32_t* slot_mapping;
+  int32_t* block_tables;
+  int32_t* entry_req;   /* host-only facts about the entries: request, first position, rows */
+  int32_t* entry_start;
+  int32_t* entry_rows;
+} R2StepBatch;
 
 typedef struct {
   int32_t stalled;
@@ -99,6 +124,10 @@ int32_t r2_sched_submit(void* sched, const int32_t* prompt, int32_t n, int32_t m
                         int32_t top_k, uint64_t seed, const int32_t* stops, int32_t n_stops);
 int32_t r2_sched_cancel(void* sched, int32_t id);
 int32_t r2_sched_plan(void* sched, R2Plan* out);
+/* The outstanding plan as a whole step batch: tokens, positions, slots, block tables, one logit row
+   per entry (its last row) with its sampling parameters, and inert padding up to the capacities.
+   Every index it writes lies inside the pool by construction. Negative on a plan that does not fit. */
+int32_t r2_sched_fill_step_batch(void* sched, const R2StepBatch* out);
 int32_t r2_sched_commit(void* sched, const int32_t* tokens, int32_t n);
 int32_t r2_sched_poll(void* sched, int32_t id, int32_t* out, int32_t cap, int32_t* finished, int32_t* state);
 int32_t r2_sched_stall(const void* sched, R2Stall* out);

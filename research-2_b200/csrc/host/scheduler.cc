@@ -353,4 +353,62 @@ int32_t Scheduler::set_reserve_ratio(float v) {
   return SCHED_OK;
 }
 
+int32_t Scheduler::fill_step_batch(const R2StepBatch& o) const {
+  if (!outstanding_) return SCHED_NO_PLAN;
+  const Plan& p = plan_;
+  const int32_t n = p.n_entries(), t = p.n_tokens;
+  if (n > o.r_cap || t > o.t_cap || n > o.w_cap) return SCHED_BAD_ARGS;
+  if (n > 0) {
+    int32_t status = cache_.fill_batch(n, p.req.data(), p.start.data(), p.rows.data(), o.t_cap, o.r_cap, o.positions,
+                                       o.row_entry, o.q_start, o.seq_lens, o.state_slot, o.fresh, o.slot_mapping,
+                                       o.block_tables);
+    if (status != CACHE_OK) return status;
+  } else {
+    o.q_start[0] = 0;
+  }
+  std::copy(p.input_ids.begin(), p.input_ids.end(), o.input_ids);
+  for (int32_t e = 0; e < n; ++e) {
+    o.entry_req[e] = p.req[e];
+    o.entry_start[e] = p.start[e];
+    o.entry_rows[e] = p.rows[e];
+    o.logit_rows[e] = o.q_start[e + 1] - 1;  // the entry's last row
+    o.temperature[e] = p.temperature[e];
+    o.top_k[e] = p.top_k[e];
+    o.key0[e] = p.key0[e];
+    o.key1[e] = p.key1[e];
+    o.sample_pos[e] = p.sample_pos[e];
+  }
+  // everything beyond the counts is inert: rows of no entry that write to the null page, entries
+  // of no rows, greedy logit rows on row 0
+  for (int32_t i = t; i < o.t_cap; ++i) {
+    o.input_ids[i] = 0;
+    o.positions[i] = 0;
+    o.row_entry[i] = -1;
+  }
+  for (int32_t g = 0; g < cache_.n_groups(); ++g) {
+    std::fill(o.slot_mapping + size_t(g) * o.t_cap + t, o.slot_mapping + size_t(g + 1) * o.t_cap, 0);
+  }
+  for (int32_t e = n; e < o.r_cap; ++e) {
+    o.q_start[e + 1] = t;
+    o.seq_lens[e] = 0;
+    o.state_slot[e] = 0;
+    o.fresh[e] = 0;
+  }
+  size_t offset = 0;
+  for (int32_t g = 0; g < cache_.n_groups(); ++g) {
+    const size_t width = size_t(cache_.table_width(g));
+    std::fill(o.block_tables + offset + size_t(n) * width, o.block_tables + offset + size_t(o.r_cap) * width, 0);
+    offset += size_t(o.r_cap) * width;
+  }
+  for (int32_t e = n; e < o.w_cap; ++e) {
+    o.logit_rows[e] = 0;
+    o.temperature[e] = 1.f;
+    o.top_k[e] = 1;
+    o.key0[e] = 0;
+    o.key1[e] = 0;
+    o.sample_pos[e] = 0;
+  }
+  return n;
+}
+
 }  // namespace r2

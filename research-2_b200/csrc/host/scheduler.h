@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "cache_manager.h"
+#include "engine_abi.h"
 
 namespace r2 {
 
@@ -128,6 +129,8 @@ class Scheduler {
   int32_t poll(int32_t id, int32_t* out, int32_t cap, int32_t* finished, int32_t* state);
 
   const Plan& current_plan() const { return plan_; }
+  // The outstanding plan written as a step batch into the caller's arrays (see R2StepBatch).
+  int32_t fill_step_batch(const R2StepBatch& out) const;
   const Stall& stall() const { return stall_; }
   const StepEvent& last_event() const { return event_; }
   CacheManager& cache() { return cache_; }

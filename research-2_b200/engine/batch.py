@@ -81,6 +81,24 @@ class StepBatch:
         self.n_entries = 0
         self.n_tokens = 0
         self.n_logit_rows = 0
+        self.trusted = False   # filled and padded natively by the scheduler: nothing left to pad or check
+        self._native = None
+
+    def native(self):
+        """The batch's arrays as the native side's struct (made once: the buffer never moves)."""
+        if self._native is None:
+            from ..cache import _host
+
+            n = _host.StepBatchC()
+            n.t_cap, n.r_cap, n.w_cap = self.t_cap, self.r_cap, self.w_cap
+            for name in ("input_ids", "positions", "row_entry", "q_start", "seq_lens", "state_slot", "fresh", "logit_rows",
+                         "temperature", "top_k", "key0", "key1", "sample_pos"):
+                setattr(n, name, getattr(self, name).ctypes.data)
+            n.slot_mapping = self.slot_mapping_flat.ctypes.data
+            n.block_tables = self.block_tables_flat.ctypes.data
+            n.entry_req, n.entry_start, n.entry_rows = (a.ctypes.data for a in (self.entry_req, self.entry_start, self.entry_rows))
+            self._native = n
+        return self._native
 
     def section(self, name: str) -> tuple[int, int]:
         return self._sections[name]
@@ -92,6 +110,7 @@ class StepBatch:
         if n > self.r_cap or total > self.t_cap:
             raise ValueError(f"batch of {n} entries / {total} rows exceeds its capacity {self.r_cap} / {self.t_cap}")
         self.n_entries, self.n_tokens = n, total
+        self.trusted = False
         at = 0
         for i, (req, start, toks) in enumerate(zip(reqs, starts, token_lists)):
             if len(toks) < 1:

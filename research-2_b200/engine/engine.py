@@ -95,8 +95,10 @@ class Engine:
         self._plan = None
 
     def build_batch(self, plan: Plan):
-        decode_only = bool((plan.rows == 1).all())
-        batch = self.step_fn.new_batch(plan.n_tokens, plan.n_entries, plan.n_entries, decode_only=decode_only)
+        batch = self.step_fn.new_batch(plan.n_tokens, plan.n_entries, plan.n_entries, decode_only=plan.decode_only)
+        if plan is self.scheduler._plan:
+            self.scheduler.fill(batch)  # one native call: entries, cache indices, logit rows, sampling, padding
+            return batch
         batch.set_entries(plan.req, plan.start, plan.token_lists())
         self.scheduler.cache.fill(batch)
         batch.set_logit_rows(batch.last_rows())
@@ -109,11 +111,30 @@ class Engine:
         if plan is None:
             return None
         tokens = self.step_fn.step_and_sample(self.build_batch(plan))
-        self.commit(tokens.cpu().numpy() if hasattr(tokens, "cpu") else np.asarray(tokens, dtype=np.int32))
+        self.commit(self._to_host(tokens))
         event = self.scheduler.event()
         if self.keep_events:
             self.events.append(event)
         return event
+
+    def _to_host(self, tokens) -> np.ndarray:
+        """The step's tokens on the host: an asynchronous copy into pinned memory and one wait."""
+        if not hasattr(tokens, "is_cuda"):
+            return np.asarray(tokens, dtype=np.int32)
+        if not tokens.is_cuda:
+            return tokens.numpy()
+        n = tokens.shape[0]
+        pinned = getattr(self, "_token_buffer", None)
+        if pinned is None or pinned.shape[0] < n:
+            import torch
+
+            pinned = self._token_buffer = torch.empty(max(n, self.scheduler.config.max_batch_reqs), dtype=tokens.dtype).pin_memory()
+            self._token_view = pinned.numpy()
+        pinned[:n].copy_(tokens, non_blocking=True)
+        import torch
+
+        torch.cuda.current_stream(tokens.device).synchronize()
+        return self._token_view[:n]
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()

@@ -60,30 +60,33 @@ class SchedulerConfig:
     reserve_ratio: float = 0.0
 
 
-@dataclass(frozen=True)
 class Plan:
-    """One step's entries, decode entries first (kelpie-core/src/scheduler.zig:1315-1328). The
-    arrays are views of the scheduler's buffers: they hold until its next plan()."""
+    """One step's entries, decode entries first (kelpie-core/src/scheduler.zig:1315-1328): the
+    counts, and per entry `req`, `start`, `rows`, `emits`, `kind`, `temperature`, `top_k`,
+    `sample_pos`, `key0`, `key1`, per row `input_ids`. The arrays are copied out of the
+    scheduler when one of them is first asked for (a step that fills its batch natively never
+    asks) and are views of the scheduler's buffers: they hold until its next plan()."""
 
-    req: np.ndarray
-    start: np.ndarray
-    rows: np.ndarray
-    emits: np.ndarray
-    kind: np.ndarray
-    input_ids: np.ndarray
-    temperature: np.ndarray
-    top_k: np.ndarray
-    sample_pos: np.ndarray
-    key0: np.ndarray
-    key1: np.ndarray
+    ARRAYS = ("req", "start", "rows", "emits", "kind", "input_ids", "temperature", "top_k", "sample_pos", "key0", "key1")
+
+    def __init__(self, scheduler: "Scheduler", n_entries: int, n_tokens: int):
+        self._scheduler = scheduler
+        self.n_entries = n_entries
+        self.n_tokens = n_tokens
+
+    def __getattr__(self, name: str):  # reached only for what is not set yet: the arrays
+        if name in Plan.ARRAYS:
+            if self._scheduler._plan is not self:
+                raise RuntimeError("this plan's arrays were not read before the scheduler's next plan()")
+            for field, value in zip(Plan.ARRAYS, self._scheduler._plan_buffers.take(self._scheduler._plan_c)):
+                object.__setattr__(self, field, value)
+            return self.__dict__[name]
+        raise AttributeError(name)
 
     @property
-    def n_entries(self) -> int:
-        return len(self.req)
-
-    @property
-    def n_tokens(self) -> int:
-        return len(self.input_ids)
+    def decode_only(self) -> bool:
+        """Every entry has one row (an entry has at least one)."""
+        return self.n_entries > 0 and self.n_tokens == self.n_entries
 
     def token_lists(self) -> list[np.ndarray]:
         out, at = [], 0
@@ -124,7 +127,7 @@ class _PlanBuffers:
     FIELDS = (("req", np.int32, False), ("start", np.int32, False), ("rows", np.int32, False), ("emits", np.int32, False),
               ("kind", np.int32, False), ("input_ids", np.int32, True), ("temperature", np.float32, False),
               ("top_k", np.int32, False), ("sample_pos", np.int32, False), ("key0", np.uint32, False),
-              ("key1", np.uint32, False))
+              ("key1", np.uint32, False))  # in Plan.ARRAYS' order
 
     def __init__(self, max_entries: int, max_tokens: int):
         self.arrays = [np.zeros(max(max_tokens if per_token else max_entries, 1), dtype=dt) for _, dt, per_token in self.FIELDS]
@@ -159,6 +162,7 @@ class Scheduler:
         self.cache = CacheManager(self.groups, config.max_requests, config.max_seq_len, _borrowed=self)
         self._plan_buffers = _PlanBuffers(config.max_batch_reqs, config.max_batch_tokens)
         self._plan_c = _host.PlanC()
+        self._plan: Plan | None = None
         self._poll_buf = np.zeros(config.max_seq_len, dtype=np.int32)
         self._poll_ptr = self._poll_buf.ctypes.data_as(_host.I32P)
         self._poll_flags = (C.c_int32(0), C.c_int32(0))
@@ -240,12 +244,25 @@ class Scheduler:
         status = self._lib.r2_sched_plan(self._h, C.byref(p))
         if status != 0:
             raise RuntimeError("plan() while the previous plan has not been committed")
-        plan = Plan(*self._plan_buffers.take(p))
-        stall = _host.StallC()
-        if self._lib.r2_sched_stall(self._h, C.byref(stall)):
-            self._lib.r2_sched_commit(self._h, None, 0)  # the empty plan is closed so that the caller can go on
-            raise Stalled(stall.req_id, stall.n_work, stall.need_pages, stall.free_pages)
+        plan = self._plan = Plan(self, p.n_entries, p.n_tokens)
+        if p.n_entries == 0:
+            stall = _host.StallC()
+            if self._lib.r2_sched_stall(self._h, C.byref(stall)):
+                self._lib.r2_sched_commit(self._h, None, 0)  # the empty plan is closed so that the caller can go on
+                raise Stalled(stall.req_id, stall.n_work, stall.need_pages, stall.free_pages)
         return plan
+
+    def fill(self, batch) -> None:
+        """The outstanding plan as a whole step batch, written natively into `batch`: tokens,
+        positions, slots, block tables, one logit row per entry (its last) with its sampling
+        parameters, padding. What it writes lies inside the pool by construction, so the step
+        function does not check such a batch again."""
+        status = self._lib.r2_sched_fill_step_batch(self._h, batch.native())
+        if status < 0:
+            raise RuntimeError(f"the plan does not fit the batch, or a row's page is not reserved (status {status})")
+        p = self._plan_c
+        batch.n_entries, batch.n_tokens, batch.n_logit_rows = p.n_entries, p.n_tokens, p.n_entries
+        batch.trusted = True
 
     def commit(self, tokens) -> None:
         tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)

@@ -276,6 +276,23 @@ def test_random_caller_against_the_token_oracle(seed):
             batch.set_entries(plan.req, plan.start, plan.token_lists())
             sched.cache.fill(batch)
             batch.pad()
+            # the native fill of a whole step batch writes what these calls write, padding included
+            batch.set_logit_rows(batch.last_rows())
+            batch.set_sampling(plan.temperature, plan.top_k, plan.key0, plan.key1, plan.sample_pos)
+            roomy = batch_for(sched.cache.table_widths, plan.n_tokens + 5, plan.n_entries + 3, plan.n_entries + 3)
+            roomy.buf[:] = 77  # stale values everywhere
+            sched.fill(roomy)
+            assert roomy.trusted and (roomy.n_tokens, roomy.n_entries, roomy.n_logit_rows) == (plan.n_tokens, plan.n_entries, plan.n_entries)
+            by_hand = batch_for(sched.cache.table_widths, plan.n_tokens + 5, plan.n_entries + 3, plan.n_entries + 3)
+            by_hand.set_entries(plan.req, plan.start, plan.token_lists())
+            sched.cache.fill(by_hand)
+            by_hand.set_logit_rows(by_hand.last_rows())
+            by_hand.set_sampling(plan.temperature, plan.top_k, plan.key0, plan.key1, plan.sample_pos)
+            by_hand.pad()
+            for name, (at, size) in roomy._sections.items():
+                if not name.startswith("_"):
+                    assert np.array_equal(roomy.buf[at: at + size], by_hand.buf[at: at + size]), f"native fill: {name} differs"
+            assert np.array_equal(roomy.entry_rows[: plan.n_entries], plan.rows)
             assert plan.n_tokens <= cfg.max_batch_tokens and plan.n_entries <= cfg.max_batch_reqs
             assert len(set(plan.req.tolist())) == plan.n_entries, "a request is in the batch twice"
             kinds = plan.kind.tolist()
