@@ -356,6 +356,8 @@ bool configure_smem() {
   static bool done = false;
   if (!done) {
     if (cudaFuncSetAttribute(decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
+    // the CTAs hide each other's waits: ask for the shared memory that lets as many as fit be resident
+    if (cudaFuncSetAttribute(decode_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess) return false;
     done = true;
   }
   return true;

@@ -43,6 +43,7 @@ struct GemmParams {
   int a_total, b_total, k_total;  // extents of the a side, the b side and K
   int bn;                         // tile width on the b side = UMMA N (multiple of 16, <= 256)
   int n_kb, kb_per_split, splits, stages;
+  int n_tiles, col_tiles;         // the pair form: tiles in all, and per row of tiles (tile = row * col_tiles + column)
   const float* bias;
   const float* residual;
   int ldr;
@@ -270,6 +271,15 @@ __device__ __forceinline__ float gelu_tanh_hw(float x) {
   return fmaf(hx, t, hx);
 }
 
+// The same load without its wait: several may be in flight before one tmem_wait().
+__device__ __forceinline__ void tmem_load32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 constexpr int STAGING_ROW = 36;                       // words per staged row: 32 and four of padding (rows stay 16-byte aligned)
 constexpr int STAGING_WORDS = 32 * STAGING_ROW;       // per epilogue warp
 constexpr int BIAS_SLOTS = 256;                       // floats: the widest tile
@@ -290,14 +300,8 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
                                                  int row0, int col0, int c_begin, int c_end, int lane, bool have_acc) {
   const int rows = min(32, p.a_total - row0);        // rows of this slab that exist
   const int sub = lane >> 3, piece = lane & 7;       // step (2): the row within four, the 16-byte piece of it
-  auto row_values = [&](int c, float (&v)[32]) {     // 32 columns from c on: accumulator + bias, activated
-    uint32_t r[32];
-    if (have_acc) {
-      tmem_load32(lane_addr + uint32_t(c), r);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = 0u;
-    }
+  // 32 columns from c on, given their accumulators: + bias, activated
+  auto finish_values = [&](int c, const uint32_t (&r)[32], float (&v)[32]) {
     const float4* b4 = reinterpret_cast<const float4*>(bias_s + (c & (BIAS_SLOTS - 1)));
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -320,24 +324,62 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
       for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
     }
   };
+  auto row_values = [&](int c, float (&v)[32]) {     // the same, reading the accumulators first
+    uint32_t r[32];
+    if (have_acc) {
+      tmem_load32(lane_addr + uint32_t(c), r);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
+    finish_values(c, r, v);
+  };
+  const bool inside = rows == 32 && col0 + c_end <= p.b_total;  // the whole slab lies inside the output
   if (p.out_is_bf16 && p.residual == nullptr) {
     bf16* out = reinterpret_cast<bf16*>(p.out);
     const bool vec_ok = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (col0 & 7) == 0;
     for (int c0 = c_begin; c0 < c_end; c0 += 64) {
       if (col0 + c0 >= p.b_total) break;
+      {
+        // both halves' accumulators are asked for before either is waited for
+        const bool two = c0 + 32 < c_end;
+        uint32_t r0[32], r1[32];
+        if (have_acc) {
+          tmem_load32_issue(lane_addr + uint32_t(c0), r0);
+          if (two) tmem_load32_issue(lane_addr + uint32_t(c0 + 32), r1);
+          tmem_wait();
+        } else {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+          for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+        }
         float v[32];
-        if (c0 + 32 * h < c_end) {
-          row_values(c0 + 32 * h, v);
+        finish_values(c0, r0, v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          st_shared16(slab + uint32_t(lane * STAGING_ROW + 4 * j) * 4u, pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                      pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7]));
+        }
+        if (two) {
+          finish_values(c0 + 32, r1, v);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            st_shared16(slab + uint32_t(lane * STAGING_ROW + 16 * h + 4 * j) * 4u, pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+            st_shared16(slab + uint32_t(lane * STAGING_ROW + 16 + 4 * j) * 4u, pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
                         pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7]));
           }
         }
       }
       __syncwarp();
+      if (inside && vec_ok && c0 + 64 <= c_end) {
+        // the common case, free of per-element conditions
+        bf16* d = out + size_t(row0 + sub) * p.ldo + (col0 + c0 + 8 * piece);
+        const size_t step = size_t(4) * p.ldo;
+#pragma unroll
+        for (int r4 = 0; r4 < 32; r4 += 4, d += step) {
+          *reinterpret_cast<uint4*>(d) = ld_shared16(slab + uint32_t((r4 + sub) * STAGING_ROW + 4 * piece) * 4u);
+        }
+        __syncwarp();
+        continue;
+      }
       const int col = col0 + c0 + 8 * piece;                                   // this lane's eight columns
       const int n_cols = min(8, min(c_end - (c0 + 8 * piece), p.b_total - col));
       if (n_cols > 0) {
@@ -368,6 +410,37 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
   for (int c0 = c_begin; c0 < c_end; c0 += 32) {
     if (col0 + c0 >= p.b_total) break;
     const int col = col0 + c0 + 4 * piece;                                     // this lane's four columns
+    if (inside && vec_ok && c0 + 32 <= c_end && !p.out_is_bf16) {
+      // the common case, free of per-element conditions
+      float4 x[8];
+      if (p.residual != nullptr) {
+        const float* src = p.residual + size_t(row0 + sub) * p.ldr + col;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = *reinterpret_cast<const float4*>(src + size_t(4 * i) * p.ldr);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      {
+        float v[32];
+        row_values(c0, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          st_shared16(slab + uint32_t(lane * STAGING_ROW + 4 * j) * 4u, __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                      __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+        }
+      }
+      __syncwarp();
+      float* d = reinterpret_cast<float*>(p.out) + size_t(row0 + sub) * p.ldo + col;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 w = ld_shared16(slab + uint32_t((4 * i + sub) * STAGING_ROW + 4 * piece) * 4u);
+        *reinterpret_cast<float4*>(d + size_t(4 * i) * p.ldo) =
+            make_float4(__uint_as_float(w.x) + x[i].x, __uint_as_float(w.y) + x[i].y, __uint_as_float(w.z) + x[i].z, __uint_as_float(w.w) + x[i].w);
+      }
+      __syncwarp();
+      continue;
+    }
     const int n_cols = min(4, min(c_end - (c0 + 4 * piece), p.b_total - col));
     const bool whole = n_cols == 4 && vec_ok;
     float4 x[8];  // the residual of this lane's columns, its eight rows of the slab, in flight during step (1)
@@ -740,19 +813,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// ---- the pair form: two CTAs, one 256 x BN tile ------------------------------------------------
+// ---- the pair form: two CTAs, 256 x BN tiles, one after another -----------------------------
 //
-// For many tokens the product is bound by what the SMs can pull from L2, so the tile is doubled
-// without doubling any CTA's loads: the two CTAs of a cluster each hold 128 token rows and HALF of
-// the weight tile's columns, and the leader's MMA thread issues tcgen05.mma.cta_group::2, which
-// reads both CTAs' shared memory and writes each CTA's 128 x BN accumulator into its own tensor
-// memory. Per CTA and k-block that is 16 KB of tokens + BN/2 x 128 B of weights for 128 x BN x 64
-// multiply-adds: half the bytes per flop of the single-CTA tile of the same width.
+// For many tokens the product is bound by what the SMs can pull from L2 and by the shared-memory
+// reads of the tensor core, so the tile is doubled without doubling any CTA's loads: the two CTAs
+// of a cluster each hold 128 token rows and HALF of the weight tile's columns, and the leader's
+// MMA warp issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory and writes each
+// CTA's 128 x BN accumulator into its own tensor memory. Per CTA and k-block that is 16 KB of
+// tokens + BN/2 x 128 B of weights for 128 x BN x 64 multiply-adds: half the bytes per flop of
+// the single-CTA tile of the same width.
 //
-// Each CTA's TMA loads signal the LEADER's `full` barrier (the loads carry .cta_group::2, which
-// lets the barrier lie in the peer CTA); the leader's commits arrive on the `empty` and
-// `acc_ready` barriers of both CTAs (multicast commit). Both CTAs allocate and free tensor memory
-// as a pair. Waits are bounded as in the single-CTA kernel.
+// The kernel is persistent: a pair takes tiles pair, pair + n_pairs, ... and keeps TWO
+// accumulators in tensor memory, so that the eight epilogue warps write tile i out while the
+// products of tile i + 1 run. The ring of stages runs on across tiles.
+//
+// Barriers. `full[s]` (leader's): both CTAs' TMA loads signal it (the loads carry .cta_group::2,
+// which lets the barrier lie in the peer CTA). `empty[s]`, `acc_full[b]` (each CTA's own): the
+// leader's commits arrive on both CTAs' (multicast commit). `acc_empty[b]` (leader's): every
+// epilogue warp of both CTAs arrives on it once it has read accumulator b. Both CTAs allocate
+// and free tensor memory as a pair. Waits are bounded as in the single-CTA kernel.
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
   asm volatile(
@@ -777,7 +856,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                ::"r"(bar), "h"(uint16_t(3)) : "memory");
 }
 
-constexpr int PAIR_THREADS = 320;  // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: epilogue
+// One arrival on a barrier given by its address in the cluster's shared memory (possibly the
+// peer's). Relaxed: it hands over tensor memory that this warp has finished reading (ordered by
+// tcgen05.wait::ld and the tcgen05 fence before it), and must not wait for the warp's global
+// stores, as a release would.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+constexpr int PAIR_THREADS = 320;        // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: epilogue
+constexpr int PAIR_EPILOGUE_WARPS = 8;
+constexpr int PAIR_SLAB_BYTES = PAIR_EPILOGUE_WARPS * STAGING_WORDS * 4;
 
 template <bool B_MN>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
@@ -789,28 +878,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t b_bytes = uint32_t(half) * BK * 2;       // a multiple of 1024: half is a multiple of 8
   uint8_t* a_tiles = smem;
   uint8_t* b_tiles = smem + size_t(p.stages) * a_bytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + size_t(p.stages) * b_bytes);
+  uint8_t* slabs = b_tiles + size_t(p.stages) * b_bytes;  // the epilogue warps' staging rows
+  uint64_t* full = reinterpret_cast<uint64_t*>(slabs + PAIR_SLAB_BYTES);
   uint64_t* empty = full + MAX_STAGES;
-  uint64_t* acc_ready = empty + MAX_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  uint64_t* acc_full = empty + MAX_STAGES;                // [2]
+  uint64_t* acc_empty = acc_full + 2;                     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   float* bias_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));  // the tile's bias, BIAS_SLOTS floats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  const int a0 = blockIdx.x * BM;                          // the cluster lies along x: rows of the pair's two halves
-  const int b_tile0 = blockIdx.y * p.bn;                   // first column of the pair's tile
-  const int b0 = b_tile0 + int(rank) * half;               // first column this CTA loads
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;  // the cluster lies along x
   const int n_kb = p.n_kb;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < uint32_t(p.bn)) tmem_cols <<= 1;
+  while (tmem_cols < 2u * uint32_t(p.bn)) tmem_cols <<= 1;      // two accumulators
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 2 * PAIR_EPILOGUE_WARPS);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -821,7 +913,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  cluster_sync();  // both CTAs' barriers exist before either's loads or commits signal them
+  cluster_sync();  // both CTAs' barriers exist before either's loads, commits or arrivals signal them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   // The next kernel may start (set up, prefetch its weights) from here on, and not earlier: its
@@ -831,48 +923,52 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const uint32_t a_base = smem_u32(a_tiles), b_base = smem_u32(b_tiles);
   const uint32_t full_base = smem_u32(full), empty_base = smem_u32(empty);
-  uint32_t leader_full_base;  // the leader's `full` barriers as seen from this CTA
+  const uint32_t acc_full_base = smem_u32(acc_full);
+  uint32_t leader_full_base, leader_acc_empty_base;  // the leader's barriers as seen from this CTA
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_full_base) : "r"(full_base), "r"(0u));
-  auto load_weight = [&](int k0, uint32_t b_dst, uint32_t bar) {
-    if (B_MN) {
-      for (int j = 0; j < half; j += 64, b_dst += BK * 128) tma_load_2d_pair(b_dst, &map_b, b0 + j, k0, bar);
-    } else {
-      tma_load_2d_pair(b_dst, &map_b, k0, b0, bar);
-    }
-  };
-  const int first = min(n_kb, p.stages);
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(leader_acc_empty_base) : "r"(smem_u32(acc_empty)), "r"(0u));
   const uint32_t pair_bytes = 2u * (a_bytes + b_bytes);  // what both CTAs bring into one stage
 
   if (warp == 0) {
-    // the first round of the ring: lane s fills stage s; weights may be asked for before the
-    // previous kernel has finished, the tokens it may have written only after it
-    if (lane < first) {
-      const int k0 = lane * BK;
-      const uint32_t bar = leader_full_base + uint32_t(lane) * 8u;
-      if (rank == 0) mbar_expect_tx(full_base + uint32_t(lane) * 8u, pair_bytes);
-      load_weight(k0, b_base + uint32_t(lane) * b_bytes, bar);
-      pdl_wait();
-      tma_load_2d_pair(a_base + uint32_t(lane) * a_bytes, &map_a, k0, a0, bar);
-    }
-    __syncwarp();
-    if (first < n_kb) {
-      // ---- producer: from the ring's second round on the warp runs the loop and one elected
-      // lane issues ------------------------------------------------------------------------
-      int stage = 0, k0 = first * BK;
-      uint32_t parity = 0, a_dst = a_base, b_dst = b_base;
-      for (int i = first; i < n_kb; ++i) {
-        if (!mbar_wait(empty_base + uint32_t(stage) * 8u, parity)) {
+    // ---- producer: the warp runs the loop, one elected lane issues. A stage is waited for with
+    // the opposite of the ring's parity, which a fresh barrier passes at once. -----------------
+    int stage = 0;
+    uint32_t parity = 0, a_dst = a_base, b_dst = b_base;
+    bool waited = false, ok = true;
+    for (int tile = pair; tile < p.n_tiles && ok; tile += n_pairs) {
+      const int a0 = ((tile / p.col_tiles) * 2 + int(rank)) * BM;
+      const int b0 = (tile % p.col_tiles) * p.bn + int(rank) * half;
+      for (int kb = 0; kb < n_kb; ++kb) {
+        if (!mbar_wait(empty_base + uint32_t(stage) * 8u, parity ^ 1u)) {
           if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_EMPTY);
+          ok = false;
           break;
         }
-        if (elect_one()) {
-          const uint32_t bar = leader_full_base + uint32_t(stage) * 8u;
+        const uint32_t bar = leader_full_base + uint32_t(stage) * 8u;
+        const int k0 = kb * BK;
+        auto load_weights = [&]() {
           if (rank == 0) mbar_expect_tx(full_base + uint32_t(stage) * 8u, pair_bytes);
-          load_weight(k0, b_dst, bar);
-          tma_load_2d_pair(a_dst, &map_a, k0, a0, bar);
+          if (B_MN) {
+            uint32_t dst = b_dst;
+            for (int j = 0; j < half; j += 64, dst += BK * 128) tma_load_2d_pair(dst, &map_b, b0 + j, k0, bar);
+          } else {
+            tma_load_2d_pair(b_dst, &map_b, k0, b0, bar);
+          }
+        };
+        if (waited) {
+          if (elect_one()) {
+            load_weights();
+            tma_load_2d_pair(a_dst, &map_a, k0, a0, bar);
+          }
+        } else {
+          // the weights of the first k-block go on their way; the tokens may have been written by
+          // the previous kernel, so they are asked for only once it has completed
+          if (elect_one()) load_weights();
+          pdl_wait();
+          waited = true;
+          if (elect_one()) tma_load_2d_pair(a_dst, &map_a, k0, a0, bar);
         }
         __syncwarp();
-        k0 += BK;
         a_dst += a_bytes;
         b_dst += b_bytes;
         if (++stage == p.stages) {
@@ -892,53 +988,80 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint64_t db_fixed = B_MN ? smem_desc(0, BK * 128, 1024) : smem_desc(0, 16, 1024);
     constexpr uint32_t a_step = 32 >> 4, b_step = (B_MN ? UMMA_K * 128 : 32) >> 4;
     int stage = 0;
-    // (only the offset within the CTA's shared memory goes into a descriptor: in a cluster the
-    // address of a CTA other than the first carries its rank in high bits)
     const uint32_t a_first = (a_base >> 4) & 0x3FFFu, b_first = (b_base >> 4) & 0x3FFFu;
     uint32_t parity = 0, a_at = a_first, b_at = b_first;
-    for (int i = 0; i < n_kb; ++i) {
-      if (!mbar_wait(full_base + uint32_t(stage) * 8u, parity)) {
-        if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
+    bool ok = true;
+    int local = 0;  // this pair's count of tiles: accumulator local & 1, its use number local >> 1
+    for (int tile = pair; tile < p.n_tiles && ok; tile += n_pairs, ++local) {
+      const uint32_t buf = uint32_t(local & 1);
+      // the epilogue warps have read this accumulator's previous tile (a fresh barrier passes)
+      if (!mbar_wait(smem_u32(acc_empty) + buf * 8u, (uint32_t(local >> 1) & 1u) ^ 1u)) {
+        if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
+        ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          umma_bf16_pair(tmem_base, da_fixed + uint64_t(a_at + kk * a_step), db_fixed + uint64_t(b_at + kk * b_step), idesc,
-                         (i > 0 || kk > 0) ? 1u : 0u);
+      const uint32_t acc = tmem_base + buf * uint32_t(p.bn);
+      for (int kb = 0; kb < n_kb; ++kb) {
+        if (!mbar_wait(full_base + uint32_t(stage) * 8u, parity)) {
+          if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_FULL);
+          ok = false;
+          break;
         }
-        umma_commit_pair(empty_base + uint32_t(stage) * 8u);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            umma_bf16_pair(acc, da_fixed + uint64_t(a_at + kk * a_step), db_fixed + uint64_t(b_at + kk * b_step), idesc,
+                           (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(empty_base + uint32_t(stage) * 8u);
+        }
+        __syncwarp();
+        a_at += a_bytes >> 4;
+        b_at += b_bytes >> 4;
+        if (++stage == p.stages) {
+          stage = 0;
+          parity ^= 1u;
+          a_at = a_first;
+          b_at = b_first;
+        }
       }
+      // also on the error path: the epilogues go on and the flag tells
+      if (elect_one()) umma_commit_pair(acc_full_base + buf * 8u);
       __syncwarp();
-      a_at += a_bytes >> 4;
-      b_at += b_bytes >> 4;
-      if (++stage == p.stages) {
-        stage = 0;
-        parity ^= 1u;
-        a_at = a_first;
-        b_at = b_first;
-      }
     }
-    if (elect_one()) umma_commit_pair(smem_u32(acc_ready));  // also on the error path: both epilogues go on and the flag tells
-    __syncwarp();
-  }
-
-  // ---- epilogue: each CTA writes its own 128 rows of the tile's bn columns -------------------
-  if (warp >= 2) {
+  } else if (warp >= 2) {
+    // ---- epilogue: each CTA writes its own 128 rows of each tile's bn columns ------------------
     pdl_wait();
     const int q = warp & 3;              // the accumulator rows (tensor-memory lanes) this warp may read
     const int side = (warp - 2) >> 2;    // warps 2..5 take the tile's first half of the columns, 6..9 the second
-    for (int j = int(threadIdx.x) - 64; j < p.bn; j += PAIR_THREADS - 64) bias_s[j] = (p.bias != nullptr && b_tile0 + j < p.b_total) ? p.bias[b_tile0 + j] : 0.f;
-    asm volatile("bar.sync 1, %0;" ::"n"(PAIR_THREADS - 64) : "memory");
-    bool ok = mbar_wait(acc_ready, 0);
-    if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
-    // every product of the pair has completed: the first tiles' shared memory serves as the slabs
-    if (ok && a0 + q * 32 < p.a_total) {
-      finish_tile_rows(p, lane_addr, smem_u32(a_tiles) + uint32_t((warp - 2) * STAGING_WORDS) * 4u, bias_s, a0 + q * 32, b_tile0,
-                       side * half, (side + 1) * half, lane, true);
+    const uint32_t slab = smem_u32(slabs) + uint32_t((warp - 2) * STAGING_WORDS) * 4u;
+    bool ok = true;
+    int local = 0;
+    for (int tile = pair; tile < p.n_tiles; tile += n_pairs, ++local) {
+      const uint32_t buf = uint32_t(local & 1);
+      const int a0 = ((tile / p.col_tiles) * 2 + int(rank)) * BM;
+      const int b_tile0 = (tile % p.col_tiles) * p.bn;
+      // the tile's bias, once for the eight warps: after all have finished the previous tile
+      asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_WARPS * 32) : "memory");
+      for (int j = int(threadIdx.x) - 64; j < p.bn; j += PAIR_EPILOGUE_WARPS * 32) {
+        bias_s[j] = (p.bias != nullptr && b_tile0 + j < p.b_total) ? p.bias[b_tile0 + j] : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_WARPS * 32) : "memory");
+      if (ok && !mbar_wait(acc_full_base + buf * 8u, uint32_t(local >> 1) & 1u)) {
+        if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
+        ok = false;  // this and the later tiles are not written; the flag tells
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok && a0 + q * 32 < p.a_total) {
+        const uint32_t lane_addr = tmem_base + buf * uint32_t(p.bn) + (uint32_t(q * 32) << 16);
+        finish_tile_rows(p, lane_addr, slab, bias_s, a0 + q * 32, b_tile0, side * half, (side + 1) * half, lane, true);
+      }
+      // this warp has read the accumulator: the leader may overwrite it with the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty_base + buf * 8u);
     }
   }
 
@@ -1122,40 +1245,78 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
 // The pair form: tile width (256, or 128 when that gives too few CTAs), stages, shared memory.
 struct PairPlan {
   bool use;
-  int bn, n_kb, stages;
+  int bn, n_kb, stages, n_tiles, col_tiles;
   size_t smem;
   dim3 grid;
 };
 
-PairPlan make_pair_plan(int m, int n, int k, int w_is_nk) {
+// How many CTA pairs the GPU holds at once (one CTA to an SM at this kernel's shared-memory use).
+int max_resident_pairs() {
+  static int cached = 0;
+  if (cached == 0) {
+    auto kernel = gemm_tc_pair_kernel<true>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2, 1, 1);
+    config.blockDim = dim3(PAIR_THREADS);
+    config.dynamicSmemBytes = 200 * 1024;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = N_SMS / 2 - 2;  // a cautious guess
+    }
+    cached = n;
+  }
+  return cached;
+}
+
+PairPlan make_pair_plan(int m, int n, int k, int w_is_nk, bool always) {
   PairPlan pl;
   pl.use = false;
   if (m < 192 || n < 128) return pl;  // the second CTA of a pair would hold (almost) no rows, or the tile no columns
   (void)w_is_nk;
-  // Measured (2,048 and 8,192 rows, K 768 and 3,072): with more 128 x 128 tiles than SMs the
-  // single-CTA form runs two CTAs to an SM, one's epilogue under the other's products, and wins
-  // unless K is long; with fewer tiles, or a long K, the pair's cheaper k-blocks win.
+  // Measured at 512 to 8,192 rows (K 768 and 3,072, N 768 to 3,072): the persistent pairs reach
+  // 0.9 to 1.3 PFLOP/s once every pair has several tiles, but pay about a microsecond more of
+  // set-up and an epilogue that nothing hides; with fewer than about 2.5 single-CTA tiles per SM
+  // the single-CTA form (two CTAs to an SM) is the faster one.
   const int single_tiles = ((m + BM - 1) / BM) * ((n + 127) / 128);
-  if (single_tiles > N_SMS && k < 2048) return pl;
+  if (!always && 2 * single_tiles < 5 * N_SMS) return pl;
   const int row_pairs = (m + 2 * BM - 1) / (2 * BM);
-  pl.bn = 256;
-  if (n < 256 || 2 * row_pairs * ((n + 255) / 256) < (N_SMS * 3) / 5) pl.bn = 128;
-  const int col_tiles = (n + pl.bn - 1) / pl.bn;
-  const int ctas = 2 * row_pairs * col_tiles;
+  const int pairs = max_resident_pairs();
   pl.n_kb = (k + BK - 1) / BK;
+  // Tile width by a small model of the pair's time, in cycles measured on a B200: a k-block takes
+  // about 545 (width 256, bound by the tensor core) or 361 (width 128, bound by the issue of its
+  // four MMAs), and the last tile's epilogue, which nothing hides, about 3,900 or 2,000.
+  long best = -1;
+  pl.bn = 128;
+  for (int bn = 256; bn >= 128; bn -= 128) {
+    if (n < bn) continue;
+    const long tiles = long(row_pairs) * ((n + bn - 1) / bn);
+    const long rounds = (tiles + pairs - 1) / pairs;
+    const long cost = rounds * pl.n_kb * (bn == 256 ? 545 : 361) + (bn == 256 ? 3900 : 2000);
+    if (best < 0 || cost < best) {
+      best = cost;
+      pl.bn = bn;
+    }
+  }
+  pl.col_tiles = (n + pl.bn - 1) / pl.bn;
+  pl.n_tiles = row_pairs * pl.col_tiles;
   const size_t stage = size_t(BM) * BK * 2 + size_t(pl.bn / 2) * BK * 2;
-  const size_t fixed = 1024 + (2 * MAX_STAGES + 1) * 8 + 48 + size_t(BIAS_SLOTS) * 4;
-  (void)ctas;
+  const size_t fixed = 1024 + size_t(PAIR_SLAB_BYTES) + (2 * MAX_STAGES + 4) * 8 + 48 + size_t(BIAS_SLOTS) * 4;
   const size_t budget = 227 * 1024 - fixed;  // one CTA per SM: its eight epilogue warps need the registers
   int stages = int(budget / stage);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
-  if (stages > pl.n_kb) stages = pl.n_kb;
   if (stages < 1) return pl;
-  const size_t slabs = 8 * size_t(STAGING_WORDS) * 4;  // the epilogue's slabs lie over the tiles:
-  while (size_t(stages) * stage < slabs) ++stages;     // a short K keeps stages it does not fill
   pl.stages = stages;
   pl.smem = fixed + size_t(stages) * stage;
-  pl.grid = dim3(2 * row_pairs, col_tiles, 1);
+  pl.grid = dim3(2 * unsigned(pl.n_tiles < pairs ? pl.n_tiles : pairs), 1, 1);
   pl.use = true;
   return pl;
 }
@@ -1194,13 +1355,13 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   return launch_status();
 }
 
-bool g_pair_form = true;  // r2_gemm_tc_set_pair switches it (tests and measurements compare the two forms)
+int g_pair_form = 1;  // 0: never, 1: where it is the faster form, 2: wherever it can run (r2_gemm_tc_set_pair; tests compare the forms)
 
 }  // namespace
 
-extern "C" int r2_gemm_tc_set_pair(int on) {
-  int before = g_pair_form ? 1 : 0;
-  g_pair_form = on != 0;
+extern "C" int r2_gemm_tc_set_pair(int mode) {
+  int before = g_pair_form;
+  g_pair_form = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
   return before;
 }
 
@@ -1271,13 +1432,15 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   const size_t smem = pl.smem;
   dim3 grid((p.a_total + BM - 1) / BM, (p.b_total + bn - 1) / bn, pl.splits);
 
-  if (!pl.swapped && !fused_ln && g_pair_form) {
-    const PairPlan pp = make_pair_plan(m, n, k, w_is_nk);
+  if (!pl.swapped && !fused_ln && g_pair_form != 0) {
+    const PairPlan pp = make_pair_plan(m, n, k, w_is_nk, g_pair_form == 2);
     if (pp.use) {
       p.bn = pp.bn;
       p.stages = pp.stages;
       p.splits = 1;
       p.kb_per_split = pp.n_kb;
+      p.n_tiles = pp.n_tiles;
+      p.col_tiles = pp.col_tiles;
       CUtensorMap pa, pb;
       bool maps = make_map(&pa, x, uint64_t(k), uint64_t(m), uint64_t(lda), BK, BM);
       if (w_is_nk) {

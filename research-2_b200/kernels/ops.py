@@ -174,11 +174,14 @@ def use_tensor_core_gemm(on: bool) -> bool:
     return before
 
 
-def use_pair_gemm(on: bool) -> bool:
-    """Switch the two-CTA form (tcgen05.mma.cta_group::2, 256-row tiles) of the tensor-core product
-    for many rows on or off; off, every product runs as single-CTA 128-row tiles. Returns the
-    previous setting."""
-    return bool(_lib("gemm_tc").r2_gemm_tc_set_pair(int(bool(on))))
+def use_pair_gemm(mode):
+    """The two-CTA persistent form (tcgen05.mma.cta_group::2, 256-row tiles) of the tensor-core
+    product: False never, True where it is the faster form (many tiles per SM), "always" wherever
+    it can run (192 rows and 128 columns or more; tests compare it with the single-CTA form).
+    Returns the previous setting in the same terms."""
+    names = {0: False, 1: True, 2: "always"}
+    code = {False: 0, True: 1, "always": 2}[mode]
+    return names[_lib("gemm_tc").r2_gemm_tc_set_pair(code)]
 
 
 if os.environ.get("R2_PAIR_GEMM", "1") == "0":

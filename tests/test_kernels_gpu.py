@@ -81,11 +81,12 @@ def test_linear(m, k, n, dtype, w_is_nk):
     torch.testing.assert_close(got, base + bias + res, **(t if dtype == torch.float32 else dict(atol=2e-4, rtol=2e-4)))
 
 
-@pytest.mark.parametrize("m,k,n", [(192, 64, 128), (300, 200, 520), (2048, 768, 2304), (1000, 3072, 768), (257, 96, 1031), (512, 768, 3072)])
+@pytest.mark.parametrize("m,k,n", [(192, 64, 128), (300, 200, 520), (2048, 768, 2304), (1000, 3072, 768), (257, 96, 1031), (512, 768, 3072), (5000, 136, 1160)])
 @pytest.mark.parametrize("w_is_nk", [False, True])
 def test_linear_many_rows_on_a_cta_pair(m, k, n, w_is_nk):
-    """192 rows or more run as 256-row tiles over two CTAs (tcgen05.mma.cta_group::2): same result
-    as the single-CTA tiles and as a float32 statement, with every epilogue and ragged edges."""
+    """256-row tiles over two CTAs (tcgen05.mma.cta_group::2), persistent with two accumulators in
+    tensor memory (the last shape gives every pair several tiles): same result as the single-CTA
+    tiles and as a float32 statement, with every epilogue and ragged edges."""
     o = ops()
     torch.manual_seed(m + k + n)
     a = torch.randn(m, k).bfloat16().to(DEV)
@@ -99,7 +100,7 @@ def test_linear_many_rows_on_a_cta_pair(m, k, n, w_is_nk):
                 o.linear(a, w, bias, w_is_nk=w_is_nk, residual=res),
                 o.linear(a, w, None, w_is_nk=w_is_nk, out_dtype=torch.float32))
 
-    before = o.use_pair_gemm(True)
+    before = o.use_pair_gemm("always")
     try:
         pair = run()
         o.use_pair_gemm(False)
