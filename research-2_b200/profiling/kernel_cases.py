@@ -1,11 +1,12 @@
 """Runs each hot kernel once or twice at benchmark shapes (GPT-2 124M), for ncu to capture.
 
-    ncu --set full --clock-control none -k regex:'gemm_tc_kernel|decode_kernel|prefill_kernel' -c 12 \
+    ncu --set full --clock-control none -k regex:'gemm_tc|decode_kernel|prefill_kernel' -c 16 \
         -o kernels python -m research_2_b200.profiling.kernel_cases
 
-Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu), the tied
-logits product for 8 and 64 rows (77 MB of weights), decode attention for 64 rows at context
-640 (126 MB of cache), prefill attention for 2 x 1,024 tokens.
+Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu: single-CTA
+tiles) and at 8,192 tokens (the same two: persistent CTA pairs), the tied logits product for 8
+and 64 rows (77 MB of weights), decode attention for 64 rows at context 640 (126 MB of cache),
+prefill attention for 2 x 1,024 tokens.
 """
 import torch
 
@@ -31,9 +32,12 @@ def main():
     wfc = (torch.randn(D, F, device=dev) * 0.02).bfloat16()
     wte = (torch.randn(V, D, device=dev) * 0.02).bfloat16()
     bias = torch.zeros(F, device=dev)
+    x8k = torch.randn(8192, D, device=dev).bfloat16()
     for _ in range(2):
         ops.linear(x, wqkv, bias[: 3 * D].contiguous())
         ops.linear(x, wfc, bias, act="gelu_new")
+        ops.linear(x8k, wqkv, bias[: 3 * D].contiguous())
+        ops.linear(x8k, wfc, bias, act="gelu_new")
         ops.linear(x[:8].contiguous(), wte, None, w_is_nk=True, out_dtype=torch.float32)
         ops.linear(x[:64].contiguous(), wte, None, w_is_nk=True, out_dtype=torch.float32)
     # decode attention, 64 rows at context 640
