@@ -3,18 +3,26 @@
 // decoded tokens. The new keys and values are already in the cache when it runs.
 //
 // A CTA takes 64 consecutive rows of one entry and one query head; each of its four warps owns
-// 16 rows. Keys and values come in tiles of 64 through a two-stage cp.async pipeline, fetched
-// row by row through the block table (any page size), rows padded by 16 bytes in shared memory
-// so that ldmatrix is free of bank conflicts for every head size. Scores are scaled and masked
+// 16 rows. Keys and values come in tiles of 64 through a ring of stages, in one of two ways:
+//   * TMA (head size 64, page sizes 8, 16, 32 or a multiple of 64): one 4-D tensor copy per page
+//     and matrix ([dim][offset in page][kv head][page], 128-byte swizzle), issued by the lanes of
+//     warp 0, signalled through an mbarrier; shared-memory rows are 128 bytes, swizzled in
+//     16-byte pieces by the row index, which keeps ldmatrix free of bank conflicts;
+//   * cp.async (any head size up to 128 and any page size): 16-byte pieces fetched through the
+//     block table, rows padded by 16 bytes against bank conflicts. Scores are scaled and masked
 // in float (causal, window, context length), softmax is online, P is rounded to bfloat16 for
 // the second product, the output is normalised at the end. Key rows that no row of the tile may
 // see at all are filled with zeros instead of being read.
 //
 // Formulas: kelpie-models/kelpie_models/kernels/ops/paged_attention.py:160-240. HEAD_DIM is a
 // compile-time constant (-DHEAD_DIM=64), in steps of 16 up to 128: one library per head size.
+#include <cuda.h>
+#include <limits.h>
 #include <math.h>
 
-#include <limits.h>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -45,7 +53,14 @@ struct PrefillParams {
   const int32_t* q_start; const int32_t* seq_lens; int n_entries;
   int n_heads, n_kv_heads;
   float scale; int window;
+  int box_rows;      // TMA form: key rows per tensor copy (the page size, or 64 for larger pages)
+  int* error_flag;   // TMA form: where a bounded wait that ran out is recorded
 };
+
+bool g_prefill_tma = true;                    // r2_attention_prefill_set_tma
+constexpr int TMA_TILE_BYTES = BN * 128;       // TMA form (head size 64): unpadded 128-byte rows
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+#define R2_ERR_TIMEOUT_KV_TILE 5
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
@@ -76,20 +91,60 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Waits for the phase with the given parity; false after SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (spin > 1024) __nanosleep(64);
+  }
+  return false;
+}
+// One page's rows of one kv head: coordinates (dim, offset in page, kv head, page).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(WARPS * 32)
-prefill_kernel(const PrefillParams p) {
+// Threads: four warps that compute; the TMA form adds a fifth that only issues the tensor copies
+// (a tile's two or more copies cost the issuing thread several hundred cycles, which would
+// otherwise come out of one computing warp and hold the other three at the next barrier).
+template <bool TMA>
+__global__ void __launch_bounds__(WARPS * 32 + (TMA ? 32 : 0))
+prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t* q_s = smem;                         // [BM] rows
-  uint8_t* k_s = smem + TILE_BYTES;                  // STAGES tiles
-  uint8_t* v_s = smem + (1 + STAGES) * TILE_BYTES;   // STAGES tiles
+  uint8_t* q_s = smem;                         // [BM] rows, padded
+  // cp.async form: STAGES padded tiles of keys, then of values. TMA form: the same at 1,024-byte
+  // alignment (the swizzle works on address bits), 128-byte rows.
+  constexpr int KV_TILE = TMA ? TMA_TILE_BYTES : TILE_BYTES;
+  uint8_t* k_s = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem + TILE_BYTES) + 1023) & ~uintptr_t(1023))
+                     : smem + TILE_BYTES;
+  uint8_t* v_s = k_s + STAGES * KV_TILE;
   __shared__ int tile_entry, tile_row0;
+  __shared__ __align__(8) uint64_t full[STAGES];    // TMA form: a stage's copies have landed
+  __shared__ __align__(8) uint64_t empty[STAGES];   // TMA form: the four computing warps are done with a stage
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
@@ -127,7 +182,7 @@ prefill_kernel(const PrefillParams p) {
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
 
   // ---- the query tile ----
-  for (int id = tid; id < BM * (HD / 8); id += WARPS * 32) {
+  for (int id = tid; id < BM * (HD / 8) && tid < WARPS * 32; id += WARPS * 32) {
     int row = id / (HD / 8), c = id % (HD / 8);
     bool ok = row < rows_here;
     const bf16* src = p.q + size_t(t0 + r0 + (ok ? row : 0)) * p.q_row_stride + size_t(h) * HD + c * 8;
@@ -167,15 +222,76 @@ prefill_kernel(const PrefillParams p) {
   const int j_first = lo / BN * BN;
   const int n_tiles = (pmax - j_first) / BN + 1;
   int pages_next[PIECES];
-#pragma unroll
-  for (int t = 0; t < STAGES - 1; ++t) {
-    if (t < n_tiles) {
-      pages_of(j_first + t * BN, pages_next);
-      load_tile(j_first + t * BN, t, pages_next);
+
+  // TMA form: lane b of the producer warp brings box b of a tile (box_rows key rows of one page,
+  // keys and values); a box no row of which any query row may see is left out. The page of a box
+  // is looked up one tile before its copies are issued.
+  const uint32_t full_base = smem_addr(full), empty_base = smem_addr(empty);
+  const int n_boxes = TMA ? BN / p.box_rows : 0;
+  int box_page = INT_MIN;  // lane's page for the tile whose copies are issued next
+  auto box_lookup = [&](int j0) {
+    box_page = INT_MIN;
+    if (lane < n_boxes) {
+      const int jb = j0 + lane * p.box_rows;
+      if (jb + p.box_rows - 1 >= lo && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto box_issue = [&](int j0, int stage) {  // the whole producer warp, converged
+    const bool mine = box_page != INT_MIN;
+    const uint32_t n_mine = __popc(__ballot_sync(0xffffffffu, mine));
+    const uint32_t bar = full_base + uint32_t(stage) * 8u;
+    const uint32_t box_bytes = uint32_t(p.box_rows) * 128u;
+    if (lane == 0) mbar_expect_tx(bar, 2u * n_mine * box_bytes);  // with no box at all the phase completes at once
+    __syncwarp();
+    if (mine) {
+      const int jb = j0 + lane * p.box_rows;
+      const int page = (box_page < 0 || box_page >= p.n_pages) ? 0 : box_page;  // a bad entry reads the null page
+      const int off = page_offset(jb, p.page_size, p.page_shift);
+      const uint32_t dst = uint32_t(stage * TMA_TILE_BYTES) + uint32_t(lane) * box_bytes;
+      tma_load_4d(smem_addr(k_s) + dst, &map_k, 0, off, kvh, page, bar);
+      tma_load_4d(smem_addr(v_s) + dst, &map_v, 0, off, kvh, page, bar);
+    }
+  };
+  if (TMA) {
+    if (tid == 0) {
+      for (int st = 0; st < STAGES; ++st) {
+        mbar_init(full_base + uint32_t(st) * 8u, 1);
+        mbar_init(empty_base + uint32_t(st) * 8u, WARPS);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == WARPS) {
+      // ---- the producer warp: tile after tile into the ring, a stage as soon as the computing
+      // warps have let go of it (the ring's first round finds every stage free) -----------------
+      uint32_t round_parity = 0;
+      box_lookup(j_first);
+      for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % STAGES;
+        if (it >= STAGES && !mbar_wait(empty_base + uint32_t(stage) * 8u, round_parity ^ 1u)) {
+          if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_KV_TILE);
+          break;
+        }
+        box_issue(j_first + it * BN, stage);
+        if (it + 1 < n_tiles) box_lookup(j_first + (it + 1) * BN);
+        if (stage == STAGES - 1) round_parity ^= 1u;
+      }
+      return;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // the query tile
+  } else {
+#pragma unroll
+    for (int t = 0; t < STAGES - 1; ++t) {
+      if (t < n_tiles) {
+        pages_of(j_first + t * BN, pages_next);
+        load_tile(j_first + t * BN, t, pages_next);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (STAGES - 1 < n_tiles) pages_of(j_first + (STAGES - 1) * BN, pages_next);
   }
-  if (STAGES - 1 < n_tiles) pages_of(j_first + (STAGES - 1) * BN, pages_next);
+  uint32_t tile_parity = 0;  // TMA form: parity of the ring's current round
+  bool tiles_ok = true;
 
   float o[DTILES][4];
 #pragma unroll
@@ -189,13 +305,41 @@ prefill_kernel(const PrefillParams p) {
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it % STAGES;
     const int j0 = j_first + it * BN;
-    // tile `it` has landed (only the newest STAGES - 2 groups may still be in flight); after the
-    // barrier every thread's part of it is visible and the stage of tile it - 1 is free
-    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
-    __syncthreads();
-    if (it + STAGES - 1 < n_tiles) load_tile(j0 + (STAGES - 1) * BN, (it + STAGES - 1) % STAGES, pages_next);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    if (it + STAGES < n_tiles) pages_of(j0 + STAGES * BN, pages_next);
+    if (TMA) {
+      if (it == 0) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the query tile
+        asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
+      }
+      // tile `it` has landed when its barrier's phase completes
+      if (tiles_ok && !mbar_wait(full_base + uint32_t(stage) * 8u, tile_parity)) {
+        if (tid == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_KV_TILE);
+        tiles_ok = false;
+      }
+      if (stage == STAGES - 1) tile_parity ^= 1u;
+      if (j0 < lo || j0 + BN - 1 > pmax) {
+        // Rows of the tile outside the keys that any query row may see were not copied, or hold
+        // whatever their slots held: their scores are masked by selection, but a value row is
+        // multiplied by p = 0, so it has to be finite. They are set to zero.
+        for (int row = tid; row < BN; row += WARPS * 32) {
+          const int j = j0 + row;
+          if (j < lo || j > pmax) {
+            const uint32_t dst = smem_addr(v_s) + uint32_t(stage * TMA_TILE_BYTES + row * 128);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + c * 16), "r"(0u) : "memory");
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // later tensor copies overwrite these rows
+        asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");     // the four computing warps
+      }
+    } else {
+      // tile `it` has landed (only the newest STAGES - 2 groups may still be in flight); after the
+      // barrier every thread's part of it is visible and the stage of tile it - 1 is free
+      asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+      __syncthreads();
+      if (it + STAGES - 1 < n_tiles) load_tile(j0 + (STAGES - 1) * BN, (it + STAGES - 1) % STAGES, pages_next);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (it + STAGES < n_tiles) pages_of(j0 + STAGES * BN, pages_next);
+    }
     if (it == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -206,8 +350,12 @@ prefill_kernel(const PrefillParams p) {
     // a warp whose 16 rows all lie past the entry's rows, or before every key of this tile, rests
     const bool warp_active = warp * 16 < rows_here && j0 <= pmin + min(warp * 16 + 15, rows_here - 1);
     if (warp_active) {
-      const uint8_t* kt = k_s + stage * TILE_BYTES;
-      const uint8_t* vt = v_s + stage * TILE_BYTES;
+      const uint32_t kt = smem_addr(k_s) + uint32_t(stage * KV_TILE);
+      const uint32_t vt = smem_addr(v_s) + uint32_t(stage * KV_TILE);
+      // a row's 16-byte piece `c`: padded rows, or 128-byte rows swizzled by the row index
+      auto piece = [&](uint32_t tile, int row, int c) -> uint32_t {
+        return TMA ? tile + uint32_t(row * 128 + ((c ^ (row & 7)) << 4)) : tile + uint32_t(row * ROW_BYTES + c * 16);
+      };
       float s[BN / 8][4];
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -217,8 +365,7 @@ prefill_kernel(const PrefillParams p) {
         for (int np = 0; np < BN / 16; ++np) {  // two 8-key tiles per ldmatrix
           uint32_t b0, b1, b2, b3;
           int key = np * 16 + (lane & 7) + 8 * (lane >> 4);
-          int d = ks * 16 + 8 * ((lane >> 3) & 1);
-          ldmatrix_x4(smem_addr(kt + key * ROW_BYTES + d * 2), b0, b1, b2, b3);
+          ldmatrix_x4(piece(kt, key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
           mma_bf16(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
           mma_bf16(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
         }
@@ -300,12 +447,16 @@ prefill_kernel(const PrefillParams p) {
         for (int dp = 0; dp < DTILES / 2; ++dp) {  // two 8-wide output tiles per ldmatrix
           uint32_t b0, b1, b2, b3;
           int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-          int d = dp * 16 + 8 * (lane >> 4);
-          ldmatrix_x4_trans(smem_addr(vt + key * ROW_BYTES + d * 2), b0, b1, b2, b3);
+          ldmatrix_x4_trans(piece(vt, key, dp * 2 + (lane >> 4)), b0, b1, b2, b3);
           mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
           mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
         }
       }
+    }
+    if (TMA) {
+      // this warp is done with the stage (its ldmatrix reads have returned): the producer may refill it
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_base + uint32_t(stage) * 8u) : "memory");
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -329,18 +480,107 @@ prefill_kernel(const PrefillParams p) {
 
 extern "C" int r2_attention_prefill_head_dim(void) { return HD; }
 
-// n_tiles: the sum over entries of ceil(rows / 64), which the host knows from the batch.
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// One layer's keys (or values) in the page pool as a 4-D tensor [page][kv head][offset][dim] of
+// bfloat16, copied in boxes of `box_rows` offsets of one head of one page, 128-byte swizzle.
+// Maps are kept per (base, geometry): a model asks for the same few again every step.
+struct MapKey {
+  const void* base;
+  long long page_stride;
+  int page_size, n_kv_heads, n_pages, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && page_stride == o.page_stride && page_size == o.page_size && n_kv_heads == o.n_kv_heads &&
+           n_pages == o.n_pages && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    h = h * 1315423911u + std::hash<long long>()(k.page_stride);
+    h = h * 1315423911u + size_t(k.page_size) * 131u + size_t(k.n_kv_heads) * 31u + size_t(k.n_pages) * 7u + size_t(k.box_rows);
+    return h;
+  }
+};
+
+bool page_map(CUtensorMap* out, const void* base, long long page_stride, int page_size, int n_kv_heads, int n_pages, int box_rows) {
+  static std::mutex lock;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  const MapKey key{base, page_stride, page_size, n_kv_heads, n_pages, box_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(page_size), cuuint64_t(n_kv_heads), cuuint64_t(n_pages)};
+  cuuint64_t strides[3] = {cuuint64_t(HD) * 2, cuuint64_t(page_size) * HD * 2, cuuint64_t(page_stride) * 2};
+  cuuint32_t box[4] = {cuuint32_t(HD), cuuint32_t(box_rows), 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUtensorMap map;
+  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    return false;
+  }
+  if (maps.size() > 4096) maps.clear();  // pools that came and went
+  maps.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+template <bool TMA>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_tiles, cudaStream_t stream) {
+  const size_t smem = TMA ? size_t(TILE_BYTES) + 1024 + 2 * STAGES * size_t(TMA_TILE_BYTES) : (1 + 2 * STAGES) * size_t(TILE_BYTES);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    // several CTAs per SM hide each other's waits: ask for the shared memory that takes
+    e = cudaFuncSetAttribute(prefill_kernel<TMA>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  r2_launch(prefill_kernel<TMA>, dim3(dim3(n_tiles, p.n_heads)), dim3(WARPS * 32 + (TMA ? 32 : 0)), size_t(smem), stream, mk, mv, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// n_tiles: the sum over entries of ceil(rows / 64), which the host knows from the batch (more is
+// harmless: the CTAs beyond find no tile). error_flag: a device word in which a bounded wait that
+// ran out is recorded (may be null; the tensor-copy form is then not used).
 extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                     const void* v_cache, long long page_stride, int page_size, int n_pages,
                                     const int32_t* block_tables, int table_width, const int32_t* q_start,
                                     const int32_t* seq_lens, int n_entries, int n_tiles, int n_heads, int n_kv_heads,
-                                    float scale, int window, cudaStream_t stream) {
+                                    float scale, int window, int* error_flag, cudaStream_t stream) {
   if (n_entries <= 0 || n_tiles <= 0) return R2_OK;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
   if (page_stride % 8 != 0 || q_row_stride % 8 != 0 || out_row_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) {
     return R2_BAD_ALIGN;
   }
+  if (!(scale > 0.f)) return R2_UNSUPPORTED;  // the softmax takes the largest raw score for the largest scaled one
   PrefillParams p;
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
@@ -350,17 +590,26 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   p.q_start = q_start; p.seq_lens = seq_lens; p.n_entries = n_entries;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window;
-  if (!(scale > 0.f)) return R2_UNSUPPORTED;  // the softmax takes the largest raw score for the largest scaled one
-  const size_t smem = (1 + 2 * STAGES) * size_t(TILE_BYTES);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return int(e);
-    // several CTAs per SM hide each other's waits: ask for the shared memory that takes
-    e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
+  p.box_rows = 0;
+  p.error_flag = error_flag;
+  CUtensorMap mk, mv;
+  const bool page_fits = page_size == 8 || page_size == 16 || page_size == 32 || page_size % 64 == 0;
+  if (HD == 64 && page_fits && error_flag != nullptr && g_prefill_tma) {
+    p.box_rows = page_size < 64 ? page_size : 64;
+    if (page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows) &&
+        page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows)) {
+      return launch<true>(mk, mv, p, n_tiles, stream);
+    }
+    p.box_rows = 0;
   }
-  r2_launch(prefill_kernel, dim3(dim3(n_tiles, n_heads)), dim3(WARPS * 32), size_t(smem), stream, p);
-  return launch_status();
+  memset(&mk, 0, sizeof(mk));
+  memset(&mv, 0, sizeof(mv));
+  return launch<false>(mk, mv, p, n_tiles, stream);
+}
+
+// Tests and measurements compare the two ways of bringing the tiles in.
+extern "C" int r2_attention_prefill_set_tma(int on) {
+  int before = g_prefill_tma ? 1 : 0;
+  g_prefill_tma = on != 0;
+  return before;
 }

@@ -138,6 +138,13 @@ def use_fused_norm(on: bool) -> bool:
 N_SMS = 148
 
 
+def use_prefill_tma(on: bool, head_dim: int = 64) -> bool:
+    """Switch how the prefill attention kernel brings key and value tiles in: 4-D tensor copies
+    (TMA, one per page; head size 64 and page sizes 8, 16, 32 or multiples of 64) or 16-byte
+    cp.async pieces (every shape). Returns the previous setting."""
+    return bool(_lib_for_head_dim("attention_prefill", head_dim).r2_attention_prefill_set_tma(int(bool(on))))
+
+
 def use_fast_attention(on: bool) -> bool:
     """Switch bfloat16 attention between the fast kernels and the general CUDA-core one."""
     global _fast_attention
@@ -447,7 +454,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         status = lib.r2_attention_prefill(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
             page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens),
-            q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _stream())
+            q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error),
+            _stream())
         _check(status, "paged_attention (prefill)")
         return out
     status = _lib("attention_simt").r2_attention_simt(

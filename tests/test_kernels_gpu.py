@@ -293,6 +293,37 @@ DECODE_CASES = [
 ]
 
 
+TMA_CASES = [
+    ([(0, 200), (100, 130), (511, 1), (0, 64), (64, 65)], 4, 2, 64, 8),
+    ([(3, 129), (0, 2), (300, 77)], 6, 6, 64, 32),
+    ([(40, 100), (0, 333)], 2, 1, 64, 64),
+    ([(0, 70), (190, 70)], 3, 3, 64, 128),
+]
+
+
+@pytest.mark.parametrize("case", TMA_CASES, ids=[f"p{c[4]}_h{c[1]}kv{c[2]}_{len(c[0])}e" for c in TMA_CASES])
+@pytest.mark.parametrize("window", [0, 13, 70])
+def test_prefill_attention_tiles_by_tensor_copies(case, window):
+    """Head size 64 with pages of 8, 16, 32 or a multiple of 64 keys brings its tiles in by 4-D
+    tensor copies into swizzled rows: the same numbers as the piecewise copies (to rounding of the
+    same arithmetic: bit-equal), and as the plain statement; slots never written do not leak."""
+    entries, h, hkv, hd, page = case
+    o = ops()
+    pc = PagedCase(entries, h, hkv, hd, page, torch.bfloat16, seed=page + window, garbage=float("inf"))
+    scale = hd**-0.5 / 1.5
+    before = o.use_prefill_tma(True)
+    try:
+        by_tma = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
+        o.use_prefill_tma(False)
+        by_pieces = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
+    finally:
+        o.use_prefill_tma(before)
+    assert o.device_errors() == 0
+    assert torch.isfinite(by_tma.float()).all(), "a slot that was never written leaked in"
+    assert torch.equal(by_tma, by_pieces)
+    torch.testing.assert_close(by_tma.float().cpu(), pc.plain(scale, window), atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("case", DECODE_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in DECODE_CASES])
 @pytest.mark.parametrize("window", [0, 40])
 @pytest.mark.parametrize("sliced", [False, True])
