@@ -175,17 +175,17 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
 // tensor core reads: warp `w` of the four takes rows w, w + 4, ...; a lane holds every 32nd group
 // of four elements of its row (rows of at most 1,024 elements, at most 16 tokens); mean and
 // variance are two passes over registers, in float
-// (kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23). Rows past the last token are zeros.
+// (kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23). Rows past the last token are not
+// written: their columns of the product are never stored. The gain and shift are weights, so they
+// are fetched before the wait on the previous kernel.
 constexpr int LN_MAX_K = 1024;
 constexpr int LN_MAX_TOKENS = 16;
 constexpr int LN_CHUNKS = LN_MAX_K / 128;
 
-__device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t* b_tiles, uint32_t b_stride, int kb_begin,
-                                                    int n_kb, int w, int lane) {
-  const int k_total = p.k_total;
-  const int k_lo = kb_begin * BK, k_end = (kb_begin + n_kb) * BK, k_hi = min(k_total, k_end);
-  // gain and shift for the lane's elements inside this CTA's share of K, fetched once
-  float4 gam[LN_CHUNKS], bet[LN_CHUNKS];
+// Gain and shift for the lane's elements inside this CTA's share of K.
+__device__ __forceinline__ void load_norm_weights(const GemmParams& p, int kb_begin, int n_kb, int lane, float4 (&gam)[LN_CHUNKS],
+                                                  float4 (&bet)[LN_CHUNKS]) {
+  const int k_lo = kb_begin * BK, k_hi = min(p.k_total, (kb_begin + n_kb) * BK);
 #pragma unroll
   for (int i = 0; i < LN_CHUNKS; ++i) {
     int k = (lane + 32 * i) * 4;
@@ -193,7 +193,15 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
     gam[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_gamma + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
     bet[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_beta + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (int r0 = w; r0 < p.bn; r0 += 8) {  // two rows at a time: both rows' loads are in flight together
+}
+
+__device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t* b_tiles, uint32_t b_stride, int kb_begin,
+                                                    int n_kb, int w, int lane, const float4 (&gam)[LN_CHUNKS],
+                                                    const float4 (&bet)[LN_CHUNKS]) {
+  const int k_total = p.k_total;
+  const int k_lo = kb_begin * BK, k_end = (kb_begin + n_kb) * BK, k_hi = min(k_total, k_end);
+  // Rows past the last token are left as they are: their columns of the product are never stored.
+  for (int r0 = w; r0 < p.b_total; r0 += 8) {  // two rows at a time: both rows' loads are in flight together
     float4 v[2][LN_CHUNKS];
     bool live[2];
 #pragma unroll
@@ -211,7 +219,7 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int r = r0 + 4 * u;
-      if (r >= p.bn) continue;
+      if (!live[u]) continue;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < LN_CHUNKS; ++i) sum += v[u][i].x + v[u][i].y + v[u][i].z + v[u][i].w;
@@ -521,15 +529,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* acc_ready = empty + MAX_STAGES;
   uint64_t* tokens_ready = acc_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tokens_ready + 1);
+  uint64_t* partials_ready = tokens_ready + 1;  // leader: the other CTAs' partial sums have landed (counted in bytes)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(partials_ready + 1);
   // partial sums of the other CTAs of the cluster, [rank - 1][column][row], used in the leader only
   // (feature-major form); the token-major form keeps the tile's bias in the same place
-  float* reduce = reinterpret_cast<float*>(tmem_slot + 4);
+  float* reduce = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
   uint32_t rank = 0;  // this CTA's place in its cluster = its slice of K
   if (p.splits > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  // feature-major split-K: columns (tokens) of this tile that exist, rounded up to 16-byte pieces
+  const int live_cols = min(p.bn, ((p.b_total - b0 + 3) / 4) * 4);
   const int kb_begin = int(rank) * p.kb_per_split;
   const int kb_end = min(p.n_kb, kb_begin + p.kb_per_split);
   const int n_kb = kb_end - kb_begin;
@@ -543,6 +554,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     mbar_init(acc_ready, 1);
     mbar_init(tokens_ready, 4);  // one arrival per epilogue warp
+    mbar_init(partials_ready, 1);
+    if (p.splits > 1 && rank == 0) {
+      // every other CTA sends its whole tile of partial sums, rows padded
+      mbar_expect_tx(smem_u32(partials_ready), uint32_t(p.splits - 1) * BM * (uint32_t(live_cols) + 4u) * 4u);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -685,6 +701,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
   bool acc_ok = true;
+  float bias_ahead = 0.f, res_ahead[16];  // feature-major epilogue: the lane's bias, and its residual for the first 16 tokens
+#pragma unroll
+  for (int j = 0; j < 16; ++j) res_ahead[j] = 0.f;
   if (threadIdx.x == 64 && p.prefetch != nullptr) {
     // weights never change: this CTA's slice of the next product's weight goes to L2 right away
     const long long n_ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
@@ -697,9 +716,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
   if (warp >= 2) {
+    float4 gam[fused_ln ? LN_CHUNKS : 1], bet[fused_ln ? LN_CHUNKS : 1];
+    if constexpr (fused_ln) load_norm_weights(p, kb_begin, n_kb, lane, gam, bet);
     pdl_wait();  // the epilogue reads the residual stream and writes the output
     if constexpr (fused_ln) {
-      build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane);
+      build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane, gam, bet);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor core
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tokens_ready)) : "memory");
@@ -710,17 +731,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int j = int(threadIdx.x) - 64; j < p.bn; j += 128) reduce[j] = (p.bias != nullptr && b0 + j < p.b_total) ? p.bias[b0 + j] : 0.f;
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
+    if constexpr (TRANSPOSED) {
+      // what the epilogue adds does not depend on the products: it is fetched while they run
+      const int a = a0 + q * 32 + lane;
+      if (rank == 0 && a < p.a_total) {
+        if (p.bias != nullptr) bias_ahead = p.bias[a];
+        if (p.residual != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) res_ahead[j] = b0 + j < p.b_total ? p.residual[size_t(b0 + j) * p.ldr + a] : 0.f;
+        }
+      }
+    }
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
     acc_ok = ok;
     if (p.splits > 1 && rank != 0) {
-      // send this slice's partial sums to the leader's shared memory
-      uint32_t remote;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(reduce)), "r"(0u));
-      remote += (uint32_t(rank - 1) * uint32_t(p.bn) * BM + uint32_t(q * 32 + lane)) * 4u;
-      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      // This slice's partial sums go to the leader's shared memory as [rank - 1][row][column] with
+      // rows padded by 16 bytes (the leader's 16-byte reads of 32 rows then fall on different
+      // banks): they are laid out in this CTA's own (otherwise unused) copy of the buffer first,
+      // and one bulk copy carries the whole tile over, its bytes counted on the leader's barrier.
+      // (Thousands of separate 16-byte remote stores took more than a microsecond to land.)
+      // Only the columns of tokens that exist are sent.
+      const uint32_t row_words = uint32_t(live_cols) + 4u;
+      const uint32_t mine = smem_u32(reduce) + uint32_t(q * 32 + lane) * row_words * 4u;
+      for (int c0 = 0; c0 < live_cols; c0 += 16) {
         uint32_t r[16];
         if (ok && n_kb > 0) {
           tmem_load16(lane_addr + uint32_t(c0), r);
@@ -729,13 +765,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + uint32_t(c0 + j) * BM * 4u), "r"(r[j]) : "memory");
+        for (int j = 0; j < 16; j += 4) {
+          if (c0 + j < live_cols) st_shared16(mine + uint32_t(c0 + j) * 4u, r[j], r[j + 1], r[j + 2], r[j + 3]);
         }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes, read by the bulk copy
+      asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
+      if (threadIdx.x == 64) {
+        uint32_t remote, remote_bar;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(reduce)), "r"(0u));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(partials_ready)), "r"(0u));
+        const uint32_t tile_bytes = BM * row_words * 4u;
+        asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(remote + uint32_t(rank - 1) * tile_bytes), "r"(smem_u32(reduce)), "r"(tile_bytes), "r"(remote_bar)
+                     : "memory");
       }
     }
   }
-  if (p.splits > 1) cluster_sync();  // partial sums have landed in the leader (release / acquire)
+  if (p.splits > 1 && warp >= 2 && rank == 0 && acc_ok) {
+    // the other CTAs' partial sums have landed in this CTA's shared memory
+    if (!mbar_wait(partials_ready, 0)) {
+      atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
+      acc_ok = false;
+    }
+  }
   if (warp >= 2 && rank == 0) {
     const int q = warp & 3;
     const int a = a0 + q * 32 + lane;
@@ -749,7 +802,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (ok) {
       const bool a_ok = a < p.a_total;
       // In the transposed form the thread's feature is fixed: one bias value serves every column.
-      const float bias_a = (TRANSPOSED && a_ok && p.bias != nullptr) ? p.bias[a] : 0.f;
+      const float bias_a = bias_ahead;
+      const uint32_t row_words = uint32_t(live_cols) + 4u;
+      const uint32_t my_row = smem_u32(reduce) + uint32_t(q * 32 + lane) * row_words * 4u;
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
         float v[16];
         {
@@ -764,9 +819,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
         }
         for (int z = 1; z < p.splits; ++z) {  // rank order: the sum is the same bits every run
-          const float* part = reduce + (size_t(z - 1) * p.bn + c0) * BM + q * 32 + lane;
+          const uint32_t part = my_row + (uint32_t(z - 1) * BM * row_words + uint32_t(c0)) * 4u;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] += part[size_t(j) * BM];
+          for (int j = 0; j < 16; j += 4) {
+            if (c0 + j >= live_cols) break;
+            const uint4 w = ld_shared16(part + uint32_t(j) * 4u);
+            v[j] += __uint_as_float(w.x);
+            v[j + 1] += __uint_as_float(w.y);
+            v[j + 2] += __uint_as_float(w.z);
+            v[j + 3] += __uint_as_float(w.w);
+          }
         }
         const int nb = min(16, p.b_total - (b0 + c0));  // columns of this chunk that exist
         if (!a_ok || nb <= 0) continue;
@@ -782,9 +844,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
           }
           if (p.residual != nullptr) {
+            if (c0 == 0) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (j < nb) v[j] += p.residual[size_t(b0 + c0 + j) * p.ldr + a];
+              for (int j = 0; j < 16; ++j) v[j] += res_ahead[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j < nb) v[j] += p.residual[size_t(b0 + c0 + j) * p.ldr + a];
+              }
             }
           }
           if (p.out_is_bf16) {
@@ -807,6 +874,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // A CTA whose tile is still being copied out of its shared memory must not leave: the leader
+  // comes here after it has received every tile, the others wait for it here.
+  if (p.splits > 1) cluster_sync();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
@@ -1206,7 +1276,7 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
     if (s > 8) s = 8;
     if (s > pl.n_kb) s = pl.n_kb;
     for (; s > 1; --s) {
-      if (size_t(s - 1) * pl.bn * BM * 4 > 100 * 1024) continue;  // the leader's reduce buffer
+      if (size_t(s - 1) * (pl.bn + 4) * BM * 4 > 100 * 1024) continue;  // the leader's reduce buffer
       int per = (pl.n_kb + s - 1) / s;
       int actual = (pl.n_kb + per - 1) / per;
       if (actual != s) continue;                                  // the same split with fewer CTAs comes later
@@ -1217,8 +1287,8 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   }
   pl.kb_per_split = (pl.n_kb + pl.splits - 1) / pl.splits;
   const size_t a_bytes = BM * BK * 2, b_stride = (size_t(pl.bn) * BK * 2 + 1023) & ~size_t(1023);
-  const size_t fixed = 1024 + (2 * MAX_STAGES + 2) * 8 + 32 +
-                       (pl.swapped ? size_t(pl.splits - 1) * pl.bn * BM * 4 : size_t(BIAS_SLOTS) * 4);  // partial sums, or the bias
+  const size_t fixed = 1024 + (2 * MAX_STAGES + 3) * 8 + 32 +
+                       (pl.swapped ? size_t(pl.splits - 1) * (pl.bn + 4) * BM * 4 : size_t(BIAS_SLOTS) * 4);  // partial sums, or the bias
   // with more tiles than SMs, leave room for two CTAs on an SM: one's epilogue under the other's loads
   const size_t budget = (tiles * pl.splits > N_SMS ? 113 * 1024 : 227 * 1024) - fixed;
   if (fused_ln) {

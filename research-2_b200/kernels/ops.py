@@ -118,7 +118,7 @@ def build_all() -> None:
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
-_fused_norm = os.environ.get("R2_FUSED_NORM", "0") != "0"  # measured at batch 8: the norm as a kernel of its own is a little faster
+_fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
 _fused_decode = os.environ.get("R2_FUSED_DECODE", "1") != "0"
 _weight_prefetch = os.environ.get("R2_WEIGHT_PREFETCH", "0") != "0"  # measured: no gain at batch 8, so off
 
