@@ -195,20 +195,36 @@ __device__ __forceinline__ void load_norm_weights(const GemmParams& p, int kb_be
   }
 }
 
+// Two sums over the warp at once: the shuffles of one hide the latency of the other's.
+__device__ __forceinline__ void warp_sum2(float& a, float& b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ta = __shfl_xor_sync(0xffffffffu, a, o), tb = __shfl_xor_sync(0xffffffffu, b, o);
+    a += ta;
+    b += tb;
+  }
+}
+
+// `src_first`: the source rows of this warp's first two tokens (w and w + 4), looked up before the
+// wait on the previous kernel (the index list is part of the batch, not of its output); -1: none.
 __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t* b_tiles, uint32_t b_stride, int kb_begin,
                                                     int n_kb, int w, int lane, const float4 (&gam)[LN_CHUNKS],
-                                                    const float4 (&bet)[LN_CHUNKS]) {
+                                                    const float4 (&bet)[LN_CHUNKS], const int (&src_first)[2]) {
   const int k_total = p.k_total;
   const int k_lo = kb_begin * BK, k_end = (kb_begin + n_kb) * BK, k_hi = min(k_total, k_end);
+  const float inv_k = 1.f / float(k_total);
   // Rows past the last token are left as they are: their columns of the product are never stored.
-  for (int r0 = w; r0 < p.b_total; r0 += 8) {  // two rows at a time: both rows' loads are in flight together
+  // Two rows at a time, in lockstep and free of per-row branches, so that the loads and the
+  // reductions of one row pass under those of the other.
+  for (int r0 = w; r0 < p.b_total; r0 += 8) {
     float4 v[2][LN_CHUNKS];
     bool live[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int r = r0 + 4 * u;
       live[u] = r < p.b_total;
-      const int src = live[u] ? (p.ln_rows != nullptr ? p.ln_rows[r] : r) : 0;
+      int src = 0;
+      if (live[u]) src = r0 == w ? src_first[u] : (p.ln_rows != nullptr ? p.ln_rows[r] : r);
       const float4* row = reinterpret_cast<const float4*>(p.ln_x + size_t(src) * p.ln_ldx);
 #pragma unroll
       for (int i = 0; i < LN_CHUNKS; ++i) {
@@ -216,35 +232,43 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
         v[u][i] = (live[u] && k < k_total) ? row[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
+    float sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int r = r0 + 4 * u;
-      if (!live[u]) continue;
-      float sum = 0.f;
+    for (int i = 0; i < LN_CHUNKS; ++i) {
+      sum[0] += v[0][i].x + v[0][i].y + v[0][i].z + v[0][i].w;
+      sum[1] += v[1][i].x + v[1][i].y + v[1][i].z + v[1][i].w;
+    }
+    warp_sum2(sum[0], sum[1]);
+    const float mean[2] = {sum[0] * inv_k, sum[1] * inv_k};
+    float sq[2] = {0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < LN_CHUNKS; ++i) sum += v[u][i].x + v[u][i].y + v[u][i].z + v[u][i].w;
-      const float mean = warp_sum(sum) / float(k_total);
-      float sq = 0.f;
+    for (int i = 0; i < LN_CHUNKS; ++i) {
+      int k = (lane + 32 * i) * 4;
+      if (k < k_total) {
 #pragma unroll
-      for (int i = 0; i < LN_CHUNKS; ++i) {
-        int k = (lane + 32 * i) * 4;
-        if (k < k_total) {
-          float a = v[u][i].x - mean, b = v[u][i].y - mean, c = v[u][i].z - mean, d = v[u][i].w - mean;
-          sq += a * a + b * b + c * c + d * d;
+        for (int u = 0; u < 2; ++u) {
+          float a = v[u][i].x - mean[u], b = v[u][i].y - mean[u], c = v[u][i].z - mean[u], d = v[u][i].w - mean[u];
+          sq[u] += a * a + b * b + c * c + d * d;
         }
       }
-      const float rstd = 1.f / sqrtf(warp_sum(sq) / float(k_total) + p.ln_eps);
+    }
+    warp_sum2(sq[0], sq[1]);
+    const float rstd[2] = {1.f / sqrtf(sq[0] * inv_k + p.ln_eps), 1.f / sqrtf(sq[1] * inv_k + p.ln_eps)};
 #pragma unroll
-      for (int i = 0; i < LN_CHUNKS; ++i) {
-        int k = (lane + 32 * i) * 4;
-        if (k < k_lo || k >= k_end) continue;  // another CTA's share of K, or past the tiles
+    for (int i = 0; i < LN_CHUNKS; ++i) {
+      int k = (lane + 32 * i) * 4;
+      if (k < k_lo || k >= k_end) continue;  // another CTA's share of K, or past the tiles
+      const int kb = k / BK - kb_begin, kin = k % BK;
+      uint8_t* tile = b_tiles + size_t(kb) * b_stride;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (!live[u]) continue;
+        const int r = r0 + 4 * u;
         uint32_t lo = 0u, hi = 0u;
-        if (live[u] && k < k_hi) {
-          lo = pack2((v[u][i].x - mean) * rstd * gam[i].x + bet[i].x, (v[u][i].y - mean) * rstd * gam[i].y + bet[i].y);
-          hi = pack2((v[u][i].z - mean) * rstd * gam[i].z + bet[i].z, (v[u][i].w - mean) * rstd * gam[i].w + bet[i].w);
+        if (k < k_hi) {
+          lo = pack2((v[u][i].x - mean[u]) * rstd[u] * gam[i].x + bet[i].x, (v[u][i].y - mean[u]) * rstd[u] * gam[i].y + bet[i].y);
+          hi = pack2((v[u][i].z - mean[u]) * rstd[u] * gam[i].z + bet[i].z, (v[u][i].w - mean[u]) * rstd[u] * gam[i].w + bet[i].w);
         }
-        const int kb = k / BK - kb_begin, kin = k % BK;
-        uint8_t* tile = b_tiles + size_t(kb) * b_stride;
         uint32_t off = uint32_t(r / 8) * 1024u + uint32_t(r % 8) * 128u + (uint32_t((kin / 8) ^ (r % 8)) * 16u) + uint32_t(kin % 8) * 2u;
         *reinterpret_cast<uint2*>(tile + off) = make_uint2(lo, hi);
       }
@@ -717,10 +741,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   if (warp >= 2) {
     float4 gam[fused_ln ? LN_CHUNKS : 1], bet[fused_ln ? LN_CHUNKS : 1];
-    if constexpr (fused_ln) load_norm_weights(p, kb_begin, n_kb, lane, gam, bet);
+    int src_first[2] = {-1, -1};
+    if constexpr (fused_ln) {
+      load_norm_weights(p, kb_begin, n_kb, lane, gam, bet);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r = (warp & 3) + 4 * u;
+        if (r < p.b_total) src_first[u] = p.ln_rows != nullptr ? p.ln_rows[r] : r;
+      }
+    }
     pdl_wait();  // the epilogue reads the residual stream and writes the output
     if constexpr (fused_ln) {
-      build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane, gam, bet);
+      build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane, gam, bet, src_first);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor core
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tokens_ready)) : "memory");
