@@ -57,7 +57,9 @@ template <int G>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_kernel(const DecodeParams p) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
-  pdl_wait();               // the previous kernel's writes are visible from here on
+  // The wait on the previous kernel comes further down: positions, context lengths and block
+  // tables belong to the batch, which no kernel writes, so the chain of lookups that leads to the
+  // first tile's addresses runs while the previous kernel (the product that makes q, k and v) ends.
   __shared__ float q_s[G][HD];
   __shared__ float red_o[WARPS][G][HD];
   __shared__ float red_m[WARPS][G], red_l[WARPS][G];
@@ -65,23 +67,10 @@ decode_kernel(const DecodeParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int h0 = kvh * G;
-  const int e = p.row_entry[t];
-  if (e < 0) {  // a pad row: zeros, and empty partials
-    for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
-      int g = i / HD, d = i % HD;
-      if (p.n_slices == 1 || p.counters != nullptr) {
-        if (slice == 0) p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(0.f);
-      } else {
-        p.part_o[((size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice) * HD + d] = 0.f;
-      }
-    }
-    if (p.n_slices > 1 && p.counters == nullptr && threadIdx.x < G) {
-      float* ml = p.part_ml + ((size_t(t) * p.n_heads + h0 + threadIdx.x) * p.n_slices + slice) * 2;
-      ml[0] = -INFINITY;
-      ml[1] = 0.f;
-    }
-    return;
-  }
+  // Every row is an entry of its own, in order: row t is entry t. A pad row is an entry of no keys
+  // (context length 0, position 0), which the code below turns into zeros without a branch of
+  // its own; so nothing here waits for a lookup of the row's entry before the others start.
+  const int e = t;
   const int pos = p.positions[t];
   const int seq_len = p.seq_lens[e];
   const int last = pos < seq_len - 1 ? pos : seq_len - 1;
@@ -93,12 +82,6 @@ decode_kernel(const DecodeParams p) {
   const int tile_begin = slice * tiles_per;
   const int tile_end = min(tiles, tile_begin + tiles_per);
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
-
-  for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
-    int g = i / HD, d = i % HD;
-    q_s[g][d] = __bfloat162float(p.q[size_t(t) * p.q_row_stride + size_t(h0 + g) * HD + d]) * p.scale;
-  }
-  __syncthreads();
 
   float m[G], l[G], acc[G][DPL][2];
 #pragma unroll
@@ -118,24 +101,24 @@ decode_kernel(const DecodeParams p) {
   uint8_t* my_smem = tile_smem + size_t(warp) * NBUF * 2 * 32 * ROW_BYTES;
   const int tile_of_new = (p.k_new != nullptr && pos == last) ? (pos - first) / 32 : -1;
 
-  auto issue = [&](int tile, int buf) {
-    // lane r finds row r's place once; then consecutive lanes copy consecutive 16-byte pieces of
-    // a row, then the next row: whole lines per request
-    const int j0 = first + tile * 32;
-    long long my_k, my_v;  // element offsets from k_cache / v_cache; -1 for a row past the last key
-    {
-      const int j = j0 + lane;
-      if (j > last) {
-        my_k = my_v = -1;
-      } else if (tile == tile_of_new && j == pos) {
-        my_k = (p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.k_cache;
-        my_v = (p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.v_cache;
-      } else {
-        int page = table[page_index(j, p.page_size, p.page_shift)];
-        page = (page < 0 || page >= p.n_pages) ? 0 : page;
-        my_k = my_v = (long long)(size_t(page) * p.page_stride + head_off + size_t(page_offset(j, p.page_size, p.page_shift)) * HD);
-      }
+  // lane r finds row r's place: element offsets from k_cache / v_cache; -1 for a row past the last key
+  auto lookup = [&](int tile, long long& my_k, long long& my_v) {
+    const int j = first + tile * 32 + lane;
+    if (j > last) {
+      my_k = my_v = -1;
+    } else if (tile == tile_of_new && j == pos) {
+      my_k = (p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.k_cache;
+      my_v = (p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.v_cache;
+    } else {
+      int page = table[page_index(j, p.page_size, p.page_shift)];
+      page = (page < 0 || page >= p.n_pages) ? 0 : page;
+      my_k = my_v = (long long)(size_t(page) * p.page_stride + head_off + size_t(page_offset(j, p.page_size, p.page_shift)) * HD);
     }
+  };
+  // then consecutive lanes copy consecutive 16-byte pieces of a row, then the next row: whole
+  // lines per request
+  auto copy = [&](int tile, int buf, long long my_k, long long my_v) {
+    const int j0 = first + tile * 32;
     const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
     const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES);
 #pragma unroll
@@ -153,8 +136,23 @@ decode_kernel(const DecodeParams p) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  auto issue = [&](int tile, int buf) {
+    long long my_k, my_v;
+    lookup(tile, my_k, my_v);
+    copy(tile, buf, my_k, my_v);
+  };
 
-  if (tile_begin + warp < tile_end) issue(tile_begin + warp, 0);
+  // The first tile's addresses are found before the wait; its copies (one row of which may be the
+  // new key and value, which the previous kernel made) and the query's fetch come after it.
+  long long first_k = -1, first_v = -1;
+  if (tile_begin + warp < tile_end) lookup(tile_begin + warp, first_k, first_v);
+  pdl_wait();  // the previous kernel's writes are visible from here on
+  if (tile_begin + warp < tile_end) copy(tile_begin + warp, 0, first_k, first_v);
+  for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+    int g = i / HD, d = i % HD;
+    q_s[g][d] = __bfloat162float(p.q[size_t(t) * p.q_row_stride + size_t(h0 + g) * HD + d]) * p.scale;
+  }
+  __syncthreads();
   int it = 0;
   for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS, ++it) {
     const int j0 = first + tile * 32;
