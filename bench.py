@@ -141,7 +141,10 @@ class DecodeLoop:
             self.step_fn(b)
         torch.cuda.synchronize()
         # every decode step's batch, precomputed into one pinned array
-        self.graph = self.step_fn._graph(batch, batch)  # the decode-only bucket: rows == entries
+        from research_2_b200.engine.step import StepGraph
+
+        # the decode-only graph (rows == entries) without the host copies inside: this loop feeds it on the device
+        self.graph = StepGraph(self.step_fn, batch, batch, io_inside=False)
         host = self.graph.host
         self.skip = host.section("positions")[0]  # input_ids stay on the device
         self.staged = torch.zeros(n_steps, host.buf.shape[0], dtype=torch.int32).pin_memory()

@@ -110,31 +110,13 @@ class Engine:
         plan = self.plan()
         if plan is None:
             return None
-        tokens = self.step_fn.step_and_sample(self.build_batch(plan))
-        self.commit(self._to_host(tokens))
+        batch = self.build_batch(plan)
+        tokens = self.step_fn.step_and_sample(batch)
+        self.commit(self.step_fn.tokens_to_host(batch, tokens) if hasattr(tokens, "data_ptr") else np.asarray(tokens, dtype=np.int32))
         event = self.scheduler.event()
         if self.keep_events:
             self.events.append(event)
         return event
-
-    def _to_host(self, tokens) -> np.ndarray:
-        """The step's tokens on the host: an asynchronous copy into pinned memory and one wait."""
-        if not hasattr(tokens, "is_cuda"):
-            return np.asarray(tokens, dtype=np.int32)
-        if not tokens.is_cuda:
-            return tokens.numpy()
-        n = tokens.shape[0]
-        pinned = getattr(self, "_token_buffer", None)
-        if pinned is None or pinned.shape[0] < n:
-            import torch
-
-            pinned = self._token_buffer = torch.empty(max(n, self.scheduler.config.max_batch_reqs), dtype=tokens.dtype).pin_memory()
-            self._token_view = pinned.numpy()
-        pinned[:n].copy_(tokens, non_blocking=True)
-        import torch
-
-        torch.cuda.current_stream(tokens.device).synchronize()
-        return self._token_view[:n]
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()

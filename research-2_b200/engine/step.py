@@ -87,10 +87,13 @@ def _bucket(n: int) -> int:
 
 class StepGraph:
     """Forward pass + sampling of a batch of up to `t_cap` rows in up to `r_cap` entries (one
-    logit row per entry), as one CUDA graph. t_cap == r_cap is the decode-only form."""
+    logit row per entry), as one CUDA graph. t_cap == r_cap is the decode-only form. The graph
+    begins with the copy of the pinned host batch to the device and ends with the copy of the
+    sampled tokens into pinned host memory, so that a step is one graph launch and one wait."""
 
-    def __init__(self, step_fn: "StepFunction", t_cap: int, r_cap: int):
+    def __init__(self, step_fn: "StepFunction", t_cap: int, r_cap: int, io_inside: bool = True):
         self.cap = r_cap
+        self.io_inside = io_inside  # False: the caller fills `dev` and reads `tokens` itself (a device-side loop)
         self.host = StepBatch(BatchLayout(t_cap, r_cap, r_cap, step_fn.table_widths), pinned=True)
         self.host.max_context_bound = step_fn.model.max_seq_len
         self.host.pad()
@@ -99,6 +102,9 @@ class StepGraph:
         self.dev = torch.zeros(self.host.buf.shape[0], dtype=torch.int32, device=step_fn.device)
         self.dev.copy_(self.host._pinned_tensor)
         self.ctx = StepContext(self.host, self.dev, counts=(t_cap, r_cap, r_cap))
+        self.tokens_host = torch.zeros(r_cap, dtype=torch.int32).pin_memory()
+        self.tokens_host_np = self.tokens_host.numpy()
+        self.done = torch.cuda.Event()   # recorded after every replay: the batch is consumed, the tokens are on the host
         side = torch.cuda.Stream(device=step_fn.device)
         side.wait_stream(torch.cuda.current_stream(step_fn.device))
         with torch.cuda.stream(side):  # inert warm-up: every row is a pad row
@@ -119,16 +125,24 @@ class StepGraph:
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(self.graph, pool=step_fn.graph_pool()):
+            if self.io_inside:
+                self.dev.copy_(self.host._pinned_tensor, non_blocking=True)
             self.logits = step_fn.forward(self.ctx)
             self.tokens = step_fn.sample(self.logits, self.ctx)
+            if self.io_inside:
+                self.tokens_host.copy_(self.tokens, non_blocking=True)
         self.kernels = ops.launch_count() - before
 
     def replay(self) -> None:
-        self.dev.copy_(self.host._pinned_tensor, non_blocking=True)
-        self.host.copy_done = torch.cuda.Event()
-        self.host.copy_done.record()
         self.graph.replay()
+        self.done.record()
+        self.host.copy_done = self.done
         ops.count_launches(self.kernels)
+
+    def tokens_on_host(self, n: int) -> np.ndarray:
+        """The last replay's first n tokens, once it has finished."""
+        self.done.synchronize()
+        return self.tokens_host_np[:n]
 
 
 class StepFunction:
@@ -233,6 +247,14 @@ class StepFunction:
     # ---- running ---------------------------------------------------------------------------
     def forward(self, ctx: StepContext) -> torch.Tensor:
         return self.model.forward(ctx, self.arena.members, self.state_tensors)
+
+    def tokens_to_host(self, batch: StepBatch, tokens: torch.Tensor) -> np.ndarray:
+        """The tokens that `step_and_sample(batch)` returned, on the host. A step that ran as a
+        graph has them in pinned memory already; the view holds until that graph's next replay."""
+        graph = self._graph_of(batch)
+        if graph is not None and tokens.data_ptr() == graph.tokens.data_ptr():
+            return graph.tokens_on_host(tokens.shape[0])
+        return tokens.cpu().numpy()
 
     def sample(self, logits: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         return ops.sample(logits, ctx.temperature, ctx.top_k, ctx.key0, ctx.key1, ctx.sample_pos)
