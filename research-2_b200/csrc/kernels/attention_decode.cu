@@ -53,8 +53,33 @@ struct DecodeParams {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
-template <int G>
-__global__ void __launch_bounds__(WARPS * 32)
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr bool MMA_FITS = HD <= 128;   // the tensor-core form keeps HD / 2 output floats per lane
+bool g_decode_mma = true;              // r2_attention_decode_set_mma (tests compare the two forms)
+
+// MMA: scores and outputs of a tile on the warp-level tensor cores (mma.sync m16n8k16): the G query
+// heads of the kv head are rows of a 16-row operand (the rest zeros), a tile's 32 keys its columns.
+// A tile then costs a warp 32 mma and 16 ldmatrix instead of some 500 scalar instructions, which
+// is what bounds this kernel at large batches (at batch 64 it read the cache at 0.57 of the copy
+// bandwidth with the scalar form).
+template <int G, bool MMA>
+__global__ void __launch_bounds__(WARPS * 32, (MMA && HD <= 64) ? 5 : 1)  // five CTAs to an SM is what the tiles' shared memory allows
 decode_kernel(const DecodeParams p) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   // The wait on the previous kernel comes further down: positions, context lengths and block
@@ -91,6 +116,13 @@ decode_kernel(const DecodeParams p) {
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[g][i][0] = acc[g][i][1] = 0.f;
   }
+  // tensor-core form: this lane's rows are heads gq and gq + 8 of the group (those below G exist)
+  constexpr int KS = MMA ? HD / 16 : 1, DT = MMA ? HD / 8 : 1;
+  const int gq = lane >> 2, tq = lane & 3;
+  uint32_t qf[KS][4];
+  float o[DT][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < DT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const size_t head_off = size_t(kvh) * p.page_size * HD;
 
   // Tiles of 32 keys go through shared memory: every lane copies its own key's K row and V row
@@ -148,11 +180,24 @@ decode_kernel(const DecodeParams p) {
   if (tile_begin + warp < tile_end) lookup(tile_begin + warp, first_k, first_v);
   pdl_wait();  // the previous kernel's writes are visible from here on
   if (tile_begin + warp < tile_end) copy(tile_begin + warp, 0, first_k, first_v);
-  for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
-    int g = i / HD, d = i % HD;
-    q_s[g][d] = __bfloat162float(p.q[size_t(t) * p.q_row_stride + size_t(h0 + g) * HD + d]) * p.scale;
+  if (MMA) {
+    // the query heads straight into the lane's operand registers (unscaled: the scale goes on the scores)
+    const bf16* qa = p.q + size_t(t) * p.q_row_stride + size_t(h0 + gq) * HD + 2 * tq;
+    const bf16* qb = qa + size_t(8) * HD;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qf[ks][0] = gq < G ? *reinterpret_cast<const uint32_t*>(qa + ks * 16) : 0u;
+      qf[ks][1] = gq + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + ks * 16) : 0u;
+      qf[ks][2] = gq < G ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8) : 0u;
+      qf[ks][3] = gq + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8) : 0u;
+    }
+  } else {
+    for (int i = threadIdx.x; i < G * HD; i += WARPS * 32) {
+      int g = i / HD, d = i % HD;
+      q_s[g][d] = __bfloat162float(p.q[size_t(t) * p.q_row_stride + size_t(h0 + g) * HD + d]) * p.scale;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   int it = 0;
   for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS, ++it) {
     const int j0 = first + tile * 32;
@@ -186,6 +231,89 @@ decode_kernel(const DecodeParams p) {
     __syncwarp();
     const uint8_t* k_tile = my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES;
     const uint8_t* v_tile = my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES;
+    if (MMA) {
+      const uint32_t kt = smem_u32(k_tile), vt = smem_u32(v_tile);
+      float sc[4][4];  // [8-key tile][row gq: 2 keys, row gq + 8: 2 keys]
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {  // two 8-key tiles per ldmatrix
+          uint32_t b0, b1, b2, b3;
+          const int key = np * 16 + (lane & 7) + 8 * (lane >> 4);
+          ldmatrix_x4(kt + uint32_t(key * ROW_BYTES + (ks * 2 + ((lane >> 3) & 1)) * 16), b0, b1, b2, b3);
+          mma_bf16(sc[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+          mma_bf16(sc[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+        }
+      }
+      // scale, mask keys past the last one, online softmax over the lane's two rows (in float)
+      float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const bool seen = j0 + nt * 8 + 2 * tq + c <= last;
+          sc[nt][c] = seen ? sc[nt][c] * p.scale : -INFINITY;
+          sc[nt][2 + c] = seen ? sc[nt][2 + c] * p.scale : -INFINITY;
+          mx_a = fmaxf(mx_a, sc[nt][c]);
+          mx_b = fmaxf(mx_b, sc[nt][2 + c]);
+        }
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      const float m_a = fmaxf(m_run[0], mx_a), m_b = fmaxf(m_run[1], mx_b);  // finite: a tile has a key that is seen
+      const float corr_a = __expf(m_run[0] - m_a), corr_b = __expf(m_run[1] - m_b);
+      float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          sc[nt][c] = __expf(sc[nt][c] - m_a);
+          sc[nt][2 + c] = __expf(sc[nt][2 + c] - m_b);
+          sum_a += sc[nt][c];
+          sum_b += sc[nt][2 + c];
+        }
+      }
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+      sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+      sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+      l_run[0] = l_run[0] * corr_a + sum_a;
+      l_run[1] = l_run[1] * corr_b + sum_b;
+      m_run[0] = m_a;
+      m_run[1] = m_b;
+#pragma unroll
+      for (int dt = 0; dt < DT; ++dt) {
+        o[dt][0] *= corr_a;
+        o[dt][1] *= corr_a;
+        o[dt][2] *= corr_b;
+        o[dt][3] *= corr_b;
+      }
+      // o += p . v, 16 keys at a time (rows past the last key are zeros in shared memory and p = 0)
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+        const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DT / 2; ++dp) {  // two 8-wide output tiles per ldmatrix
+          uint32_t b0, b1, b2, b3;
+          const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          ldmatrix_x4_trans(vt + uint32_t(key * ROW_BYTES + (dp * 2 + (lane >> 4)) * 16), b0, b1, b2, b3);
+          mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
+          mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      if (NBUF == 1) {
+        __syncwarp();
+        if (tile + WARPS < tile_end) issue(tile + WARPS, 0);
+      } else {
+        __syncwarp();
+      }
+      continue;
+    }
     const int j = j0 + lane;
     const bool valid = j <= last;
     float s[G];
@@ -253,8 +381,25 @@ decode_kernel(const DecodeParams p) {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // merge the four warps' states
+  if (MMA) {
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
+    for (int half = 0; half < 2; ++half) {
+      const int g = gq + 8 * half;
+      if (g < G) {
+        if (tq == 0) {
+          red_m[warp][g] = m_run[half];
+          red_l[warp][g] = l_run[half];
+        }
+#pragma unroll
+        for (int dt = 0; dt < DT; ++dt) {
+          red_o[warp][g][dt * 8 + 2 * tq] = o[dt][2 * half];
+          red_o[warp][g][dt * 8 + 2 * tq + 1] = o[dt][2 * half + 1];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G && !MMA; ++g) {
     if (lane == 0) {
       red_m[warp][g] = m[g];
       red_l[warp][g] = l[g];
@@ -348,25 +493,33 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   }
 }
 
-template <int G>
+template <int G, bool MMA>
 bool configure_smem() {
   // once per kernel instance: room for the tiles beyond the default 48 KB
   static bool done = false;
   if (!done) {
-    if (cudaFuncSetAttribute(decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(decode_kernel<G, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
     // the CTAs hide each other's waits: ask for the shared memory that lets as many as fit be resident
-    if (cudaFuncSetAttribute(decode_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(decode_kernel<G, MMA>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess) return false;
     done = true;
   }
   return true;
 }
 
+template <int G, bool MMA>
+int launch_form(const DecodeParams& p, int n_rows, cudaStream_t stream) {
+  dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
+  if (!configure_smem<G, MMA>()) return R2_UNSUPPORTED;
+  r2_launch(decode_kernel<G, MMA>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
+  return launch_status();
+}
+
 template <int G>
 int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
-  dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
-  if (!configure_smem<G>()) return R2_UNSUPPORTED;
-  r2_launch(decode_kernel<G>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
-  return launch_status();
+  if constexpr (MMA_FITS) {
+    if (g_decode_mma) return launch_form<G, true>(p, n_rows, stream);
+  }
+  return launch_form<G, false>(p, n_rows, stream);
 }
 
 }  // namespace
@@ -417,11 +570,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
 namespace {
 
 template <int G>
-int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
-  if (!configure_smem<G>()) return R2_UNSUPPORTED;
-  r2_launch(decode_kernel<G>, dim3(p.n_slices, p.n_kv_heads, n_rows), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
-  return launch_status();
-}
+int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) { return launch<G>(p, n_rows, stream); }
 
 }  // namespace
 
@@ -546,4 +695,11 @@ extern "C" int r2_attention_decode_static(const void* q, int q_row_stride, void*
   return r2_attention_decode(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, n_pages,
                              block_tables, table_width, row_entry, positions, seq_lens, n_rows, n_heads, n_kv_heads,
                              scale, window, n_slices, scratch, (long long)R2_STATIC_SCRATCH_FLOATS, stream);
+}
+
+// Tests and measurements compare the tensor-core form of a tile's arithmetic with the scalar one.
+extern "C" int r2_attention_decode_set_mma(int on) {
+  int before = g_decode_mma ? 1 : 0;
+  g_decode_mma = on != 0;
+  return before;
 }

@@ -145,6 +145,12 @@ def use_prefill_tma(on: bool, head_dim: int = 64) -> bool:
     return bool(_lib_for_head_dim("attention_prefill", head_dim).r2_attention_prefill_set_tma(int(bool(on))))
 
 
+def use_decode_mma(on: bool, head_dim: int = 64) -> bool:
+    """Switch the arithmetic of a decode-attention tile between the warp-level tensor cores
+    (mma.sync; head sizes up to 128) and scalar float instructions. Returns the previous setting."""
+    return bool(_lib_for_head_dim("attention_decode", head_dim).r2_attention_decode_set_mma(int(bool(on))))
+
+
 def use_fast_attention(on: bool) -> bool:
     """Switch bfloat16 attention between the fast kernels and the general CUDA-core one."""
     global _fast_attention

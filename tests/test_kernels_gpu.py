@@ -293,6 +293,30 @@ DECODE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in DECODE_CASES])
+@pytest.mark.parametrize("window", [0, 40])
+def test_decode_attention_tile_arithmetic_on_tensor_cores_and_scalar(case, window):
+    """A tile's scores and outputs by mma.sync (head sizes up to 128) against the scalar float
+    form of the same kernel: both within the bfloat16 budget of the plain statement, and close
+    to each other (the tensor-core form rounds p to bfloat16 before p.v, as prefill does)."""
+    contexts, h, hkv, hd, page = case
+    o = ops()
+    pc = PagedCase([(c, 1) for c in contexts], h, hkv, hd, page, torch.bfloat16, seed=hd + page + window, garbage=float("inf"))
+    scale = hd**-0.5 / 1.5
+    before = o.use_decode_mma(True, hd)
+    try:
+        by_mma = pc.run(scale, window, decode_only=True, max_context=4096).float().cpu()
+        o.use_decode_mma(False, hd)
+        by_scalar = pc.run(scale, window, decode_only=True, max_context=4096).float().cpu()
+    finally:
+        o.use_decode_mma(before, hd)
+    want = pc.plain(scale, window)
+    assert torch.isfinite(by_mma).all()
+    torch.testing.assert_close(by_mma, want, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(by_scalar, want, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(by_mma, by_scalar, atol=2e-2, rtol=2e-2)
+
+
 TMA_CASES = [
     ([(0, 200), (100, 130), (511, 1), (0, 64), (64, 65)], 4, 2, 64, 8),
     ([(3, 129), (0, 2), (300, 77)], 6, 6, 64, 32),
