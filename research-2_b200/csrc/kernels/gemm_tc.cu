@@ -24,6 +24,17 @@
 
 #include "common.cuh"
 
+// Where the key and value columns of a fused q/k/v product go (an argument of r2_gemm_tc): the
+// rows' cache slots. `col` is the first key column, `width` the keys' (and the values') width;
+// head_dim a multiple of 8.
+extern "C" struct R2KvScatter {
+  const int32_t* slots;
+  void* k_cache;
+  void* v_cache;
+  long long page_stride;
+  int page_size, n_pages, col, width, head_dim;
+};
+
 namespace {
 
 constexpr int BM = 128;          // rows of the a side = UMMA M
@@ -63,7 +74,15 @@ struct GemmParams {
   // The weight of the product that runs next: asked into L2 while this one runs, a slice per CTA.
   const uint8_t* prefetch;
   long long prefetch_bytes;
+  // Token-major bfloat16 output whose columns from kv_col on are keys, then values, of this step's
+  // tokens: those columns go straight into the rows' cache slots instead of into `out`.
+  const int32_t* kv_slots;   // [rows] slot = page * page_size + offset; null: no such columns
+  bf16* kv_k;
+  bf16* kv_v;
+  long long kv_page_stride;
+  int kv_page_size, kv_page_shift, kv_n_pages, kv_col, kv_width, kv_head_dim;
 };
+
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
@@ -401,20 +420,40 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
         }
       }
       __syncwarp();
-      if (inside && vec_ok && c0 + 64 <= c_end) {
+      // Step (2). Each lane decides for its own eight columns; the warp stays together.
+      const int col = col0 + c0 + 8 * piece;                                   // this lane's eight columns
+      const int n_cols = min(8, min(c_end - (c0 + 8 * piece), p.b_total - col));
+      if (n_cols <= 0) {
+        // nothing of this lane's lies inside the output
+      } else if (p.kv_slots != nullptr && col >= p.kv_col) {
+        // keys or values of one kv head: each row's piece goes to the row's slot in the cache
+        // ([page][kv head][offset][dim]); nothing of it goes to `out`
+        const int which = (col - p.kv_col) / p.kv_width, within = (col - p.kv_col) % p.kv_width;
+        const int head = within / p.kv_head_dim, dim = within % p.kv_head_dim;
+        bf16* base = (which == 0 ? p.kv_k : p.kv_v) + size_t(head) * p.kv_page_size * p.kv_head_dim + dim;
+        int slot[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) slot[i] = 4 * i + sub < rows ? p.kv_slots[row0 + 4 * i + sub] : -1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 w = ld_shared16(slab + uint32_t((4 * i + sub) * STAGING_ROW + 4 * piece) * 4u);
+          if (slot[i] >= 0) {
+            const int page = page_index(slot[i], p.kv_page_size, p.kv_page_shift);
+            if (page < p.kv_n_pages) {
+              *reinterpret_cast<uint4*>(base + size_t(page) * p.kv_page_stride +
+                                        size_t(page_offset(slot[i], p.kv_page_size, p.kv_page_shift)) * p.kv_head_dim) = w;
+            }
+          }
+        }
+      } else if (inside && vec_ok && n_cols == 8) {
         // the common case, free of per-element conditions
-        bf16* d = out + size_t(row0 + sub) * p.ldo + (col0 + c0 + 8 * piece);
+        bf16* d = out + size_t(row0 + sub) * p.ldo + col;
         const size_t step = size_t(4) * p.ldo;
 #pragma unroll
         for (int r4 = 0; r4 < 32; r4 += 4, d += step) {
           *reinterpret_cast<uint4*>(d) = ld_shared16(slab + uint32_t((r4 + sub) * STAGING_ROW + 4 * piece) * 4u);
         }
-        __syncwarp();
-        continue;
-      }
-      const int col = col0 + c0 + 8 * piece;                                   // this lane's eight columns
-      const int n_cols = min(8, min(c_end - (c0 + 8 * piece), p.b_total - col));
-      if (n_cols > 0) {
+      } else {
 #pragma unroll
         for (int r4 = 0; r4 < 32; r4 += 4) {
           const int r = r4 + sub;
@@ -1487,7 +1526,7 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
                           const float* residual, int ldr, void* out, int ldo, int m, int n, int k, int act,
                           int out_dtype, int* error_flag, const float* ln_x, int ln_ldx, const int32_t* ln_rows,
                           const float* ln_gamma, const float* ln_beta, float ln_eps, const void* prefetch,
-                          long long prefetch_bytes, cudaStream_t stream) {
+                          long long prefetch_bytes, const R2KvScatter* kv, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return R2_OK;
   const bool fused_ln = ln_x != nullptr;
   if (fused_ln) {
@@ -1514,6 +1553,26 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   const bool prefetch_ok = prefetch != nullptr && prefetch_bytes >= 16 && !(reinterpret_cast<uintptr_t>(prefetch) & 15);
   p.prefetch = prefetch_ok ? static_cast<const uint8_t*>(prefetch) : nullptr;
   p.prefetch_bytes = prefetch_ok ? prefetch_bytes : 0;
+  p.kv_slots = nullptr;
+  if (kv != nullptr) {
+    // keys and values straight into the cache: token-major bfloat16 output without activation or
+    // residual only, 16-byte pieces that never straddle a head or the boundary between q, k and v
+    const bool fits = m > 64 && !fused_ln && out_dtype == R2_BF16 && residual == nullptr && act == R2_ACT_NONE &&
+                      kv->head_dim % 8 == 0 && kv->width % kv->head_dim == 0 && kv->col % 8 == 0 && kv->col + 2 * kv->width == n &&
+                      kv->page_stride % 8 == 0 && kv->page_size >= 1 && !(reinterpret_cast<uintptr_t>(kv->k_cache) & 15) &&
+                      !(reinterpret_cast<uintptr_t>(kv->v_cache) & 15);
+    if (!fits) return R2_UNSUPPORTED;
+    p.kv_slots = kv->slots;
+    p.kv_k = static_cast<bf16*>(kv->k_cache);
+    p.kv_v = static_cast<bf16*>(kv->v_cache);
+    p.kv_page_stride = kv->page_stride;
+    p.kv_page_size = kv->page_size;
+    p.kv_page_shift = page_shift_of(kv->page_size);
+    p.kv_n_pages = kv->n_pages;
+    p.kv_col = kv->col;
+    p.kv_width = kv->width;
+    p.kv_head_dim = kv->head_dim;
+  }
   p.a_total = pl.a_total;
   p.b_total = pl.b_total;
   p.k_total = k;

@@ -187,6 +187,17 @@ def use_tensor_core_gemm(on: bool) -> bool:
     return before
 
 
+_kv_in_epilogue = os.environ.get("R2_KV_IN_EPILOGUE", "1") != "0"
+
+
+def use_kv_in_epilogue(on: bool) -> bool:
+    """Switch the writing of keys and values into the cache by the q/k/v product's epilogue (more
+    than 64 bfloat16 rows) on or off; off, a kernel of its own writes them. Returns the previous setting."""
+    global _kv_in_epilogue
+    before, _kv_in_epilogue = _kv_in_epilogue, bool(on)
+    return before
+
+
 def use_pair_gemm(mode):
     """The two-CTA persistent form (tcgen05.mma.cta_group::2, 256-row tiles) of the tensor-core
     product: False never, True where it is the faster form (many tiles per SM), "always" wherever
@@ -329,19 +340,48 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
     status = _lib("gemm_tc").r2_gemm_tc(
         None, 0, _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _p(a.x), a.x.stride(0), _p(a.rows), _p(a.gamma),
-        _p(a.beta), C.c_float(a.eps), *_prefetch_args(w, m), _stream())
+        _p(a.beta), C.c_float(a.eps), *_prefetch_args(w, m), None, _stream())
     if status == -4:
         return None
     _check(status, "linear (tensor cores, fused norm)")
     return out
 
 
+class KvScatter(C.Structure):
+    """Where the key and value columns of a fused q/k/v product go: the rows' cache slots.
+    `col` is the first key column, `width` the keys' (and the values') width."""
+
+    _fields_ = [("slots", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("page_stride", C.c_longlong),
+                ("page_size", C.c_int), ("n_pages", C.c_int), ("col", C.c_int), ("width", C.c_int), ("head_dim", C.c_int)]
+
+
+def kv_scatter(slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int,
+               n_pages: int, col: int, width: int, head_dim: int) -> KvScatter:
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    return KvScatter(_p(slot_mapping), _p(k_cache), _p(v_cache), page_stride, page_size, n_pages, col, width, head_dim)
+
+
 def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: bool = False,
            act: str | None = None, residual: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
+           out: torch.Tensor | None = None, kv: KvScatter | None = None):
     """act(a @ w + bias) (+ residual). `w` is [K, N], or [N, K] with w_is_nk. `a` and `w`
     share a dtype; bias and residual are float32; a float32 residual makes a float32 result.
-    `a` may be NormedRows: the LayerNorm then runs inside the product's kernel where it can."""
+    `a` may be NormedRows: the LayerNorm then runs inside the product's kernel where it can.
+
+    With `kv` (a fused q/k/v product) the result is (out, written): where the tensor-core kernel
+    takes the case (more than 64 bfloat16 rows), the key and value columns go straight into the
+    rows' cache slots, `written` is True and those columns of `out` are left undefined; else
+    `written` is False and `out` is whole."""
+    if kv is not None:
+        rows = a.shape[0]
+        if _tensor_core_gemm and _kv_in_epilogue and rows > 64 and act is None and residual is None and out_dtype in (None, torch.bfloat16):
+            tokens = a.materialize() if isinstance(a, NormedRows) else a
+            if tokens.dtype == torch.bfloat16:
+                written = _linear_kv(tokens, w, bias, w_is_nk, out, kv)
+                if written is not None:
+                    return written, True
+            a = tokens
+        return linear(a, w, bias, w_is_nk=w_is_nk, act=act, residual=residual, out_dtype=out_dtype, out=out), False
     if isinstance(a, NormedRows):
         if act not in ACTIVATIONS:
             raise KernelError(f"linear: unknown activation {act!r}; known: {sorted(k for k in ACTIVATIONS if k)}")
@@ -379,7 +419,7 @@ def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: boo
         status = _lib("gemm_tc").r2_gemm_tc(
             _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
             ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0),
-            *_prefetch_args(w, m), _stream())
+            *_prefetch_args(w, m), None, _stream())
         if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
             _check(status, "linear (tensor cores)")
             return out
@@ -387,6 +427,30 @@ def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: boo
         _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[act], dtype_code(a.dtype), dtype_code(out.dtype), _stream())
     _check(status, "linear")
+    return out
+
+
+def _linear_kv(a: torch.Tensor, w: torch.Tensor, bias, w_is_nk: bool, out, kv: KvScatter):
+    """The fused q/k/v product with keys and values written to the cache by the epilogue; None
+    where the tensor-core kernel does not take the case."""
+    _need(a, "a", torch.bfloat16, 2)
+    _need(w, "w", a.dtype, 2)
+    m, k = a.shape
+    n = w.shape[0] if w_is_nk else w.shape[1]
+    if (w.shape[1] if w_is_nk else w.shape[0]) != k:
+        raise KernelError(f"linear: a {tuple(a.shape)} does not fit w {tuple(w.shape)} (w_is_nk={w_is_nk})")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    ws = _workspace(a.device)
+    status = _lib("gemm_tc").r2_gemm_tc(
+        _p(a), _rows(a, "a"), _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), None, 0, _p(out), _rows(out, "out"), m, n, k,
+        ACTIVATIONS[None], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0),
+        *_prefetch_args(w, m), C.byref(kv), _stream())
+    if status == -4:
+        return None
+    _check(status, "linear (tensor cores, keys and values into the cache)")
     return out
 
 

@@ -56,7 +56,14 @@ class PagedAttention:
     takes_lazy_norm = True  # the input goes straight into ops.linear
 
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+        in_cache = False
+        if writes_cache and not ctx.decode_only and self.rotary is None:
+            # keys and values leave the product's epilogue for their cache slots (where that kernel takes the shape)
+            qkv, in_cache = ops.linear(h, self.w_qkv, self.b_qkv, kv=ops.kv_scatter(
+                ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages,
+                self.q_width, self.kv_width, self.head_dim))
+        else:
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv)
         q = qkv[:, : self.q_width]
         k = qkv[:, self.q_width: self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
@@ -69,7 +76,7 @@ class PagedAttention:
                 self.n_kv_heads, self.head_dim, self.scale, self.window, ctx.max_context)
             if mixed is not None:
                 return ops.linear(mixed, self.w_out, self.b_out, residual=residual)
-        if writes_cache:
+        if writes_cache and not in_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages)
         mixed = ops.paged_attention(

@@ -115,6 +115,40 @@ def test_linear_many_rows_on_a_cta_pair(m, k, n, w_is_nk):
     torch.testing.assert_close(pair[2], base, atol=2e-4, rtol=2e-4)
 
 
+@pytest.mark.parametrize("m,heads,kv_heads,hd,page", [(200, 4, 4, 64, 16), (65, 6, 2, 32, 8), (700, 5, 1, 48, 4), (2048, 12, 12, 64, 16)])
+@pytest.mark.parametrize("pair", [False, "always"])
+def test_linear_writes_keys_and_values_into_the_cache(m, heads, kv_heads, hd, page, pair):
+    """The fused q/k/v product of more than 64 rows sends its key and value columns straight to
+    the rows' cache slots: the cache then holds what the separate write kernel would have put
+    there from the whole product, the query columns are the product's, other slots are untouched."""
+    o = ops()
+    torch.manual_seed(m + hd)
+    k_in = 96
+    qw, kvw = heads * hd, kv_heads * hd
+    a = torch.randn(m, k_in).bfloat16().to(DEV)
+    w = (torch.randn(k_in, qw + 2 * kvw) * k_in**-0.5).bfloat16().to(DEV)
+    bias = torch.randn(qw + 2 * kvw).to(DEV)
+    n_pages = -(-m // page) + 3
+    stride = 2 * kv_heads * page * hd
+    slots = (torch.randperm((n_pages - 1) * page)[:m] + page).to(torch.int32).to(DEV)  # never the null page
+    pool_a = torch.full((n_pages, stride), 7.0).bfloat16().to(DEV)
+    pool_b = pool_a.clone()
+    before = o.use_pair_gemm(pair)
+    try:
+        whole = o.linear(a, w, bias)
+        ka, va = pool_a.view(-1), pool_a.view(-1)[kv_heads * page * hd:]
+        o.kv_write(whole[:, qw: qw + kvw], whole[:, qw + kvw:], ka, va, slots, kv_heads, hd, page, stride, n_pages)
+        kb, vb = pool_b.view(-1), pool_b.view(-1)[kv_heads * page * hd:]
+        got, written = o.linear(a, w, bias, kv=o.kv_scatter(slots, kb, vb, stride, page, n_pages, qw, kvw, hd))
+    finally:
+        o.use_pair_gemm(before)
+    assert written and o.device_errors() == 0
+    assert torch.equal(got[:, :qw], whole[:, :qw])
+    assert torch.equal(pool_b, pool_a)
+    few, written = o.linear(a[:40].contiguous(), w, bias, kv=o.kv_scatter(slots, kb, vb, stride, page, n_pages, qw, kvw, hd))
+    assert not written and torch.equal(few, o.linear(a[:40].contiguous(), w, bias))
+
+
 @pytest.mark.parametrize("m,k,n", [(1, 768, 2304), (8, 768, 3072), (64, 768, 2304), (5, 96, 288), (33, 1600, 4800), (17, 320, 96)])
 @pytest.mark.parametrize("w_is_nk", [False, True])
 def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
