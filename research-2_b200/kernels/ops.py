@@ -109,7 +109,7 @@ def _lib(source: str) -> C.CDLL:
 
 def build_all() -> None:
     """Compile every kernel library (what `__graft_entry__.build()` calls)."""
-    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "sampling"):
+    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling"):
         _lib(source)
     for head_dim in (16, 32, 64):  # the head sizes of the tiny test models and of GPT-2
         _lib_for_head_dim("attention_decode", head_dim)
@@ -136,6 +136,17 @@ def use_fused_norm(on: bool) -> bool:
     before, _fused_norm = _fused_norm, bool(on)
     return before
 N_SMS = 148
+
+
+_prefill_tc = os.environ.get("R2_PREFILL_TC", "1") != "0"
+
+
+def use_prefill_tc(on: bool) -> bool:
+    """Switch the tcgen05 prefill attention kernel (head size 64) on or off; off, the mma.sync
+    kernel takes every shape. Returns the previous setting."""
+    global _prefill_tc
+    before, _prefill_tc = _prefill_tc, bool(on)
+    return before
 
 
 def use_prefill_tma(on: bool, head_dim: int = 64) -> bool:
@@ -517,6 +528,17 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
+    if (q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64):
+        # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles
+        _need(q_start, "q_start", torch.int32, 1)
+        n_entries = q_start.shape[0] - 1
+        status = _lib("attention_prefill_tc").r2_attention_prefill_tc(
+            _p(q), _rows(q, "q"), n, _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
+            page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens), n_entries,
+            (n_tiles + n_entries + 1) // 2, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error), _stream())
+        if status != -4:
+            _check(status, "paged_attention (prefill, tcgen05)")
+            return out
     if (q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
             and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0):
         _need(q_start, "q_start", torch.int32, 1)

@@ -1,12 +1,13 @@
 """Runs each hot kernel once or twice at benchmark shapes (GPT-2 124M), for ncu to capture.
 
-    ncu --set full --clock-control none -k regex:'gemm_tc|decode_kernel|prefill_kernel' -c 16 \
+    ncu --set full --clock-control none -k regex:'gemm_tc|decode_kernel|prefill' -c 24 \
         -o kernels python -m research_2_b200.profiling.kernel_cases
 
 Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu: single-CTA
 tiles) and at 8,192 tokens (the same two: persistent CTA pairs), the tied logits product for 8
 and 64 rows (77 MB of weights), decode attention for 64 rows at context 640 (126 MB of cache),
-prefill attention for 2 x 1,024 tokens.
+prefill attention for 2 x 1,024 and 8 x 1,024 tokens (the tcgen05 kernel `prefill_tc_kernel`, then
+the mma.sync kernel `prefill_kernel`).
 """
 import torch
 
@@ -51,17 +52,21 @@ def main():
     for _ in range(2):
         ops.decode_attention_fused(qkv[:, :D], qkv[:, D: 2 * D], qkv[:, 2 * D:], slots, kc, vc, page_stride, PS, n_pages,
                                    tables, rows, pos, lens, H, H, HD, 0.125, 0, 1024)
-    # prefill attention, 2 x 1,024 tokens
-    batch, n = 2, 1024
-    kc, vc, tables, page_stride, n_pages = paged(batch, n)
-    q = torch.randn(batch * n, D, device=dev).bfloat16()
-    row_entry = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(n)
-    positions = torch.arange(n, dtype=torch.int32, device=dev).repeat(batch)
-    lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
-    q_start = torch.tensor([0, n, 2 * n], dtype=torch.int32, device=dev)
-    for _ in range(2):
-        ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, 0.125, 0,
-                            q_start=q_start, n_tiles=batch * n // 64)
+    # prefill attention, 2 and 8 prompts of 1,024 tokens: the tcgen05 kernel, then the mma.sync one
+    for batch in (2, 8):
+        n = 1024
+        kc, vc, tables, page_stride, n_pages = paged(batch, n)
+        q = torch.randn(batch * n, D, device=dev).bfloat16()
+        row_entry = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(n)
+        positions = torch.arange(n, dtype=torch.int32, device=dev).repeat(batch)
+        lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
+        q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * n
+        for tc in (True, False):
+            before = ops.use_prefill_tc(tc)
+            for _ in range(2):
+                ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, 0.125, 0,
+                                    q_start=q_start, n_tiles=batch * n // 64)
+            ops.use_prefill_tc(before)
     torch.cuda.synchronize()
     print("ok", ops.device_errors())
 

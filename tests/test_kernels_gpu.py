@@ -369,17 +369,72 @@ def test_prefill_attention_tiles_by_tensor_copies(case, window):
     o = ops()
     pc = PagedCase(entries, h, hkv, hd, page, torch.bfloat16, seed=page + window, garbage=float("inf"))
     scale = hd**-0.5 / 1.5
-    before = o.use_prefill_tma(True)
+    before, before_tc = o.use_prefill_tma(True), o.use_prefill_tc(False)
     try:
         by_tma = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
         o.use_prefill_tma(False)
         by_pieces = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
     finally:
         o.use_prefill_tma(before)
+        o.use_prefill_tc(before_tc)
     assert o.device_errors() == 0
     assert torch.isfinite(by_tma.float()).all(), "a slot that was never written leaked in"
     assert torch.equal(by_tma, by_pieces)
     torch.testing.assert_close(by_tma.float().cpu(), pc.plain(scale, window), atol=3e-2, rtol=3e-2)
+
+
+TC_CASES = TMA_CASES + [
+    ([(0, 1024), (0, 1024)], 12, 12, 64, 16),
+    ([(900, 1), (17, 30), (0, 3), (500, 129)], 3, 3, 64, 16),
+    ([(0, 128), (0, 127), (1, 129)], 2, 2, 64, 16),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=[f"p{c[4]}_h{c[1]}kv{c[2]}_{len(c[0])}e" for c in TC_CASES])
+@pytest.mark.parametrize("window", [0, 13, 70])
+def test_prefill_attention_on_tcgen05(case, window):
+    """Head size 64 on the 5th-generation tensor cores (128-row tiles, scores and outputs in
+    tensor memory, P handed to the second product through tensor memory, one softmax thread per row):
+    the plain statement within the bfloat16 budget,
+    close to the mma.sync kernel, nothing from slots that were never written."""
+    entries, h, hkv, hd, page = case
+    o = ops()
+    pc = PagedCase(entries, h, hkv, hd, page, torch.bfloat16, seed=page + window + 5, garbage=float("inf"))
+    scale = hd**-0.5 / 1.5
+    before = o.use_prefill_tc(True)
+    try:
+        by_tc = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
+        o.use_prefill_tc(False)
+        by_mma = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
+    finally:
+        o.use_prefill_tc(before)
+    assert o.device_errors() == 0
+    assert torch.isfinite(by_tc.float()).all(), "a slot that was never written leaked in"
+    torch.testing.assert_close(by_tc.float().cpu(), pc.plain(scale, window), atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(by_tc.float(), by_mma.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_prefill_attention_on_tcgen05_with_every_sm_shared_by_two_ctas():
+    """Eight prompts of 1,024 tokens and twelve heads: several CTAs for every SM, two of them
+    resident at a time, softmax warps of one CTA a tile apart (rows below the diagonal skip the
+    mask). What depends on the order in which warps and products finish shows here and not in
+    small cases, so the same launch runs several times and every row is compared."""
+    o = ops()
+    entries = [(0, 1024)] * 8
+    pc = PagedCase(entries, 12, 12, 64, 16, torch.bfloat16, seed=77, garbage=float("inf"))
+    scale = 0.125
+    before = o.use_prefill_tc(False)
+    try:
+        by_mma = pc.run(scale, 0, q_start=pc.q_start, n_tiles=pc.n_tiles).float()
+        o.use_prefill_tc(True)
+        for _ in range(5):
+            by_tc = pc.run(scale, 0, q_start=pc.q_start, n_tiles=pc.n_tiles).float()
+            assert torch.isfinite(by_tc).all()
+            worst = (by_tc - by_mma).abs().amax(dim=1)
+            assert worst.max().item() < 2e-2, f"rows {(worst >= 2e-2).nonzero().flatten()[:8].tolist()} differ"
+    finally:
+        o.use_prefill_tc(before)
+    assert o.device_errors() == 0
 
 
 @pytest.mark.parametrize("case", DECODE_CASES, ids=[f"hd{c[3]}_h{c[1]}kv{c[2]}_p{c[4]}" for c in DECODE_CASES])
