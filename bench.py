@@ -39,6 +39,12 @@ GPT2_124M = {
     "layer_norm_epsilon": 1e-5, "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": False,
     "tie_word_embeddings": True, "eos_token_id": None,
 }
+# The other sizes of the family that the baseline names (355M, 1.5B): the default run is 124M.
+SIZES = {
+    "gpt2-124M": GPT2_124M,
+    "gpt2-355M": dict(GPT2_124M, n_layer=24, n_embd=1024, n_head=16, n_inner=4096),
+    "gpt2-1.5B": dict(GPT2_124M, n_layer=48, n_embd=1600, n_head=25, n_inner=6400),
+}
 SEED, PAGE, PROMPT_LEN, CONTEXT = 5, 16, 512, 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -93,14 +99,14 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def build_model(n_layer: int, dtype: str = "bfloat16"):
+def build_model(n_layer: int, dtype: str = "bfloat16", size: str = "gpt2-124M"):
     import torch
     from research_2_b200.config.registry import architecture_of
     from research_2_b200.models import gpt2  # noqa: F401
     from research_2_b200.models.loading import compute_dtype
     from research_2_b200.parts import Runtime
 
-    data = dict(GPT2_124M, n_layer=n_layer)
+    data = dict(SIZES[size], n_layer=n_layer)
     arch = architecture_of(data)
     cfg = arch.parse_config(data)
     tensors = arch.random_weights(cfg, SEED, std=0.02)
@@ -274,7 +280,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=GPT2_124M["n_layer"], help="fewer layers than the model has, if memory or time needs it")
+    ap.add_argument("--model", default="gpt2-124M", choices=sorted(SIZES), help="layer sizes (the default is the baseline's benchmark configuration)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip prefill, e2e and the batch 1 / 64 points")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -284,13 +291,15 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.layers is None:
+        args.layers = SIZES[args.model]["n_layer"]
     steps = min(args.steps, CONTEXT - PROMPT_LEN - args.warmup)
 
     import torch
     from research_2_b200.kernels import ops
 
     pk, pk_source = peaks()
-    model, cfg = build_model(args.layers)
+    model, cfg = build_model(args.layers, size=args.model)
     sampler = ClockSampler()
     sampler.start()
     before = ops.launch_count()
@@ -304,12 +313,12 @@ def main() -> int:
     torch.cuda.empty_cache()
 
     line = {
-        "metric": "decode tokens/s (GPT-2 124M, batch 8, 512-token prompts)", "value": value, "unit": "tokens/s",
+        "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, 512-token prompts)", "value": value, "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random weights (seed 5)",
         "impl": "ours",
         "config": {
-            "model": "gpt2-124M", "n_layer": args.layers, "n_layer_model": GPT2_124M["n_layer"], "n_embd": cfg.n_embd,
+            "model": args.model, "n_layer": args.layers, "n_layer_model": SIZES[args.model]["n_layer"], "n_embd": cfg.n_embd,
             "n_head": cfg.n_head, "head_dim": cfg.head_dim, "n_inner": cfg.n_inner, "vocab_size": cfg.vocab_size,
             "n_positions": cfg.n_positions, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
             "page_size": PAGE, "parallelism": "none", "l2": "inputs larger than L2, no flush", "peaks": pk_source,

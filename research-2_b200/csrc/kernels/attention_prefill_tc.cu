@@ -234,11 +234,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   if (warp == 0) {
     const int left = int(gridDim.x) - 1 - int(blockIdx.x);
-    int found = -1, row0 = 0, first = 0, rows_of = 0, before = 0;
+    int found = -1, row0 = 0, first = 0, rows_of = 0, len_of = 0, before = 0;
     for (int e0 = 0; e0 < p.n_entries && found < 0; e0 += 32) {
       const int e = e0 + lane;
       const int a = e < p.n_entries ? p.q_start[e] : 0;
       const int rows = e < p.n_entries ? p.q_start[e + 1] - a : 0;
+      const int len = e < p.n_entries ? p.seq_lens[e] : 0;
       const int tiles = (rows + BM - 1) / BM;
       int upto = tiles;  // tiles of the entries up to and including this lane's
 #pragma unroll
@@ -254,6 +255,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         row0 = (left - before - __shfl_sync(0xffffffffu, upto - tiles, src_lane)) * BM;
         first = __shfl_sync(0xffffffffu, a, src_lane);
         rows_of = __shfl_sync(0xffffffffu, rows, src_lane);
+        len_of = __shfl_sync(0xffffffffu, len, src_lane);
       }
       before += __shfl_sync(0xffffffffu, upto, 31);
     }
@@ -262,7 +264,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tile_info[1] = row0;
       tile_info[2] = first;
       tile_info[3] = rows_of;
-      tile_info[4] = found >= 0 ? p.seq_lens[found] : 0;
+      tile_info[4] = len_of;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -9,6 +9,12 @@
 // The Philox counter is (position of the drawn token, 0, token id, 0) and the key is the
 // request's own, so a request draws the same numbers whatever batch it is in (the reference
 // keys the draw by the batch: kelpie-engine/kelpie_engine/sdk/plan.py:96-106).
+//
+// A row's vocabulary is split over up to 16 CTAs (the noise costs ten Philox rounds a token: one
+// CTA for 50,257 tokens took 65 us). Each CTA finds the best of its slice; the k-th largest value,
+// where there is a top-k filter, every CTA of the row selects for itself over the whole row (reads
+// that the L2 serves). The CTA that arrives last at the row's counter takes the best of the
+// slices' bests (ties to the lower token, so the split does not show) and resets the counter.
 #include <math.h>
 
 #include "common.cuh"
@@ -16,6 +22,16 @@
 namespace {
 
 constexpr int THREADS = 512;
+constexpr int MAX_SPLIT = 16;
+constexpr int MAX_SPLIT_ROWS = 1024;  // more rows than this run one CTA each
+
+struct Best {
+  float v;
+  int i;
+};
+// Scratch of the split form: launches on one stream follow one another, which is what the engine does.
+__device__ Best slice_best[MAX_SPLIT_ROWS * MAX_SPLIT];
+__device__ unsigned int slices_arrived[MAX_SPLIT_ROWS];
 
 __device__ __forceinline__ uint32_t philox_c0(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
 #pragma unroll
@@ -43,11 +59,6 @@ __device__ __forceinline__ uint32_t order_key(float v) {
   uint32_t b = __float_as_uint(v);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-
-struct Best {
-  float v;
-  int i;
-};
 
 __device__ __forceinline__ Best better(Best a, Best b) {
   if (b.i < 0) return a;
@@ -85,56 +96,149 @@ __device__ Best block_best(Best mine, Best* scratch) {
   return r;
 }
 
+// The row's token from its slices' bests: the CTA that arrives last reduces them.
+__device__ void finish_row(Best r, int row, int slice, int n_slices, int32_t* tokens, bool* last_of_row) {
+  if (n_slices == 1) {
+    if (threadIdx.x == 0) tokens[row] = r.i < 0 ? 0 : r.i;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    slice_best[row * MAX_SPLIT + slice] = r;
+    __threadfence();
+    *last_of_row = atomicAdd(&slices_arrived[row], 1u) == unsigned(n_slices - 1);
+  }
+  __syncthreads();
+  if (!*last_of_row) return;
+  if (threadIdx.x < 32) {
+    __threadfence();
+    Best b{0.f, -1};
+    if (int(threadIdx.x) < n_slices) {
+      const volatile Best* src = &slice_best[row * MAX_SPLIT + threadIdx.x];
+      b.v = src->v;
+      b.i = src->i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+      b = better(b, other);
+    }
+    if (threadIdx.x == 0) {
+      tokens[row] = b.i < 0 ? 0 : b.i;
+      slices_arrived[row] = 0u;  // for the next launch
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const uint32_t* __restrict__ key0, const uint32_t* __restrict__ key1,
-              const int32_t* __restrict__ sample_pos, int32_t* __restrict__ tokens) {
+              const int32_t* __restrict__ sample_pos, int32_t* __restrict__ tokens, int row_fits) {
+  extern __shared__ float row_s[];  // the row's logits, for the top-k selection (row_fits)
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ Best best_s[THREADS / 32];
+  // Logits crowd into the few bins of their common exponents, and shared-memory atomics on one
+  // address run one after another. So the lanes count into eight columns, lanes_hist[bin][lane % 8]:
+  // at most four lanes of a warp meet, and the columns are summed into hist afterwards.
+  __shared__ uint32_t lanes_hist[256 * 8];
   __shared__ uint32_t hist[256];
   __shared__ uint32_t sel_prefix, sel_remaining;
+  __shared__ bool last_of_row;
   const int row = blockIdx.x;
+  const int n_slices = int(gridDim.y), slice = int(blockIdx.y);
+  const int per_slice = (vocab + n_slices - 1) / n_slices;
+  const int i_begin = slice * per_slice, i_end = min(vocab, i_begin + per_slice);
   const float* lg = logits + size_t(row) * ld;
   const int k = top_k[row];
 
   if (k == 1) {
     Best mine{0.f, -1};
-    for (int i = threadIdx.x; i < vocab; i += THREADS) {
+    for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
       float v = lg[i];
       if (mine.i < 0 || v > mine.v) mine = Best{v, i};
     }
     Best r = block_best(mine, best_s);
-    if (threadIdx.x == 0) tokens[row] = r.i < 0 ? 0 : r.i;
+    finish_row(r, row, slice, n_slices, tokens, &last_of_row);
     return;
   }
 
   // The k-th largest value by radix selection over the order keys, 8 bits at a time.
+  // Each pass reads the whole row, and with a few hundred tokens a thread it is the latency of
+  // those reads that a pass costs (10 us for 50,257 tokens from the L2). Where the row fits the
+  // CTA's shared memory it is copied there once, sixteen loads in flight, and the passes read the copy.
   float kth = -INFINITY;
   if (k > 1 && k < vocab) {
+    const float* src = lg;
+    if (row_fits) {
+      for (int base = 0; base < vocab; base += 16 * THREADS) {
+        const int i0 = base + int(threadIdx.x);
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = i0 + u * THREADS < vocab ? lg[i0 + u * THREADS] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          if (i0 + u * THREADS < vocab) row_s[i0 + u * THREADS] = v[u];
+        }
+      }
+      src = row_s;  // (the first pass begins with a barrier)
+    }
     if (threadIdx.x == 0) {
       sel_prefix = 0u;
       sel_remaining = uint32_t(k);
     }
     for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0u;
+      for (int b = threadIdx.x; b < 256 * 8; b += THREADS) lanes_hist[b] = 0u;
       __syncthreads();
       uint32_t prefix = sel_prefix;
       uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
-      for (int i = threadIdx.x; i < vocab; i += THREADS) {
-        uint32_t key = order_key(lg[i]);
-        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+      for (int base = 0; base < vocab; base += 8 * THREADS) {
+        const int i0 = base + int(threadIdx.x);
+        float v[8];  // eight loads in flight
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = i0 + u * THREADS < vocab ? src[i0 + u * THREADS] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t key = order_key(v[u]);
+          if (i0 + u * THREADS < vocab && (key & mask) == prefix) atomicAdd(&lanes_hist[((key >> shift) & 0xFFu) * 8u + (threadIdx.x & 7u)], 1u);
+        }
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t remaining = sel_remaining;
-        int b = 255;
-        for (; b > 0; --b) {
-          if (hist[b] >= remaining) break;
-          remaining -= hist[b];
+      if (threadIdx.x < 256) {
+        uint32_t total = 0u;
+#pragma unroll
+        for (int l = 0; l < 8; ++l) total += lanes_hist[threadIdx.x * 8 + l];
+        hist[threadIdx.x] = total;
+      }
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        // The highest bin at which the count from the top reaches what is still wanted: lane l
+        // has bins 255 - 8l down to 248 - 8l. The elements that match the prefix are at least as
+        // many as are wanted, so there is such a bin.
+        const int lane = threadIdx.x;
+        uint32_t c[8], sum = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          c[j] = hist[255 - 8 * lane - j];
+          sum += c[j];
         }
-        sel_prefix = prefix | (uint32_t(b) << shift);
-        sel_remaining = remaining;
+        uint32_t upto = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          uint32_t other = __shfl_up_sync(0xffffffffu, upto, d);
+          if (lane >= d) upto += other;
+        }
+        const uint32_t remaining = sel_remaining;
+        uint32_t above = upto - sum;  // in bins above this lane's
+        if (above < remaining && remaining <= upto) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (above < remaining && remaining <= above + c[j]) {
+              sel_prefix = prefix | (uint32_t(255 - 8 * lane - j) << shift);
+              sel_remaining = remaining - above;
+            }
+            above += c[j];
+          }
+        }
       }
       __syncthreads();
     }
@@ -147,7 +251,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   const uint32_t k0 = key0[row], k1 = key1[row];
   const uint32_t position = uint32_t(sample_pos[row]);
   Best mine{0.f, -1};
-  for (int i = threadIdx.x; i < vocab; i += THREADS) {
+  for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
     float v = lg[i];
     bool keep = (v >= kth) && isfinite(v);
     if (!keep) continue;  // a filtered token is selected out, never added to
@@ -155,7 +259,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     if (mine.i < 0 || score > mine.v) mine = Best{score, i};
   }
   Best r = block_best(mine, best_s);
-  if (threadIdx.x == 0) tokens[row] = r.i < 0 ? 0 : r.i;
+  finish_row(r, row, slice, n_slices, tokens, &last_of_row);
 }
 
 }  // namespace
@@ -167,6 +271,21 @@ extern "C" int r2_sample(const float* logits, int ld, int n_rows, int vocab, con
                          int32_t* tokens, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (vocab < 1 || ld < vocab) return R2_BAD_SHAPE;
-  r2_launch(sample_kernel, dim3(n_rows), dim3(THREADS), size_t(0), stream, logits, ld, vocab, temperature, top_k, key0, key1, sample_pos, tokens);
+  int n_slices = (vocab + 8 * THREADS - 1) / (8 * THREADS);  // about eight tokens a thread
+  n_slices = n_rows > MAX_SPLIT_ROWS ? 1 : (n_slices < 1 ? 1 : (n_slices > MAX_SPLIT ? MAX_SPLIT : n_slices));
+  // Shared memory for a copy of the row, where a CTA can have that much (the static part is below 12 KB).
+  static int most_smem = -1;
+  if (most_smem < 0) {
+    int dev = 0, most = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&most, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most - 12 * 1024) != cudaSuccess) most = 0;
+    most_smem = most > 12 * 1024 ? most - 12 * 1024 : 0;
+    (void)cudaGetLastError();
+  }
+  const size_t row_bytes = size_t(vocab) * sizeof(float);
+  const int row_fits = row_bytes <= size_t(most_smem) ? 1 : 0;
+  r2_launch(sample_kernel, dim3(n_rows, n_slices), dim3(THREADS), row_fits ? row_bytes : size_t(0), stream, logits, ld, vocab, temperature,
+            top_k, key0, key1, sample_pos, tokens, row_fits);
   return launch_status();
 }

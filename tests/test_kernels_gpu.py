@@ -559,6 +559,29 @@ def test_sampling_draws_equal_the_plain_sampler(vocab):
     assert got == want
 
 
+@pytest.mark.parametrize("vocab", [20011, 60013])
+def test_sampling_rows_split_over_several_ctas(vocab):
+    """A large vocabulary is cut into slices, one CTA each; the draw does not show the cut (ties
+    go to the lower token across slices too), and a second launch finds the counters reset. The
+    smaller row fits a CTA's shared memory for the top-k selection, the larger does not."""
+    n = 8
+    torch.manual_seed(5)
+    logits = torch.randn(n, vocab) * 2
+    logits[0, [4100, 19000]] = 30.0          # a tie across two slices, greedy
+    temps = torch.tensor([1.0, 0.8, 1.0, 1.7, 0.3, 1.0, 0.9, 1.0])
+    top_ks = torch.tensor([1, 0, 5, 40, vocab, 1, 2, 0], dtype=torch.int32)
+    key0 = torch.arange(n, dtype=torch.int64) * 104729 % (2**31)
+    key1 = torch.arange(n, dtype=torch.int64) + 3
+    pos = torch.arange(n, dtype=torch.int32) * 5 + 2
+    want = [plain.sample_token(logits[i], float(temps[i]), int(top_ks[i]), (int(key0[i]), int(key1[i])), int(pos[i]))
+            for i in range(n)]
+    assert want[0] == 4100
+    for _ in range(2):
+        got = ops().sample(logits.to(DEV), temps.to(DEV), top_ks.to(DEV), key0.to(torch.int32).to(DEV),
+                           key1.to(torch.int32).to(DEV), pos.to(DEV)).tolist()
+        assert got == want
+
+
 def test_top_k_frequencies():
     """Draws with top_k = 3 land on the three largest logits with softmax(top3 / T) frequencies
     (the reference's sampler check: kelpie/scripts/check_build_step.py:101-140)."""
