@@ -35,3 +35,10 @@ def tiny_b_dir(tmp_path_factory):
     from tests.helpers import TINY_B, make_model_dir
 
     return make_model_dir(tmp_path_factory.mktemp("tiny_b"), TINY_B)
+
+
+@pytest.fixture(scope="session")
+def tiny_c_dir(tmp_path_factory):
+    from tests.helpers import TINY_C, make_model_dir
+
+    return make_model_dir(tmp_path_factory.mktemp("tiny_c"), TINY_C)

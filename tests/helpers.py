@@ -30,7 +30,18 @@ TINY_B = {
     },
     "seed": 2, "std": 0.05, "store_dtype": "bfloat16", "page_size": 8,
 }
-TINY = {"a": TINY_A, "b": TINY_B}
+# Head size 64 (what the tcgen05 prefill attention and the 4-D tensor copies are built for) at a
+# width, a hidden size and a vocabulary that are no power of two.
+TINY_C = {
+    "config": {
+        "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+        "n_layer": 2, "n_embd": 192, "n_head": 3, "n_inner": 448, "vocab_size": 777, "n_positions": 512,
+        "activation_function": "gelu_new", "layer_norm_epsilon": 3e-6, "scale_attn_weights": True,
+        "scale_attn_by_inverse_layer_idx": True, "tie_word_embeddings": True, "eos_token_id": None,
+    },
+    "seed": 9, "std": 0.04, "store_dtype": "bfloat16", "page_size": 16,
+}
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
 
 
 def make_model_dir(folder: Path, tiny: dict, std: float | None = None) -> Path:

@@ -1,6 +1,7 @@
 """Replay on the GPU against the plain implementation: the same requests whole, with the last
 32 tokens decoded one by one, in portions of changing size, and mixed with other requests in
-so few pages that pages are used again; in float32 and in bfloat16, for both tiny configurations."""
+so few pages that pages are used again; in float32 and in bfloat16, for the two tiny configurations
+and for a third of head size 64 with prompts of several 128-row tiles (the tensor-core attention)."""
 
 from __future__ import annotations
 
@@ -18,7 +19,7 @@ from tests.helpers import TINY, assert_within_budget, random_tokens
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
-LENGTHS = {"a": (70, 45, 128, 33, 2, 97), "b": (130, 64, 9, 100, 40, 3, 256)}
+LENGTHS = {"a": (70, 45, 128, 33, 2, 97), "b": (130, 64, 9, 100, 40, 3, 256), "c": (300, 130, 64, 200, 17, 2, 129, 512)}
 
 
 def requests_for(name: str) -> dict[str, list[int]]:
@@ -63,12 +64,12 @@ def compare(folder, requests, tb, outputs, dtype, what):
 
 
 @pytest.fixture(scope="module")
-def folders(tiny_a_dir, tiny_b_dir):
-    return {"a": tiny_a_dir, "b": tiny_b_dir}
+def folders(tiny_a_dir, tiny_b_dir, tiny_c_dir):
+    return {"a": tiny_a_dir, "b": tiny_b_dir, "c": tiny_c_dir}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
 @pytest.mark.parametrize("mode", ["whole", "decode32", "portions", "mixed"])
 def test_replay_modes(folders, name, dtype, mode):
     folder, requests = folders[name], requests_for(name)
