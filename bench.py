@@ -253,9 +253,12 @@ def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
     t0 = time.perf_counter()
     n_tokens = 0
     for _ in range(steps):
-        engine.step()
+        engine.step(wait=False)   # launched; the polls below run while the GPU works and see the step before
         for r in rids:
             n_tokens += len(engine.poll(r).new_tokens)
+    engine.finish()
+    for r in rids:
+        n_tokens += len(engine.poll(r).new_tokens)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     h2d = (engine.step_fn.h2d_bytes - h0) / steps

@@ -31,7 +31,7 @@ def generate(  # noqa: PLR0913
         return generate_with(engine, prompts, max_new_tokens, temperature, top_k, seed, stop_token_ids)
 
 
-def generate_with(engine: Engine, prompts, max_new_tokens, temperature=0.0, top_k=0, seed=0, stop_token_ids=()):
+def generate_with(engine: Engine, prompts, max_new_tokens, temperature=0.0, top_k=0, seed=0, stop_token_ids=(), wait=True):
     from .scheduler import Full
 
     out: list[list[int]] = [[] for _ in prompts]
@@ -46,7 +46,7 @@ def generate_with(engine: Engine, prompts, max_new_tokens, temperature=0.0, top_
                 break
             live[rid] = nxt
             nxt += 1
-        engine.step()
+        engine.step(wait=wait)  # (wait=False: the polls below run while the GPU works, and see the step before)
         for rid in list(live):
             p = engine.poll(rid)
             out[live[rid]] += p.new_tokens

@@ -3,7 +3,9 @@
 `submit / poll / wait / cancel / plan / commit` carry the names and meanings of the reference's
 Engine (kelpie-engine/kelpie_engine/sdk/engine.py:240-753). The reference runs its step loop
 on a thread of its own; here `step()` is a plain call and `wait()` steps until the request is
-finished, so nothing happens behind the caller's back.
+finished, so nothing happens behind the caller's back. `step(wait=False)` returns as soon as the
+step's graph has been launched: what the caller does next (polling the tokens of earlier steps,
+submitting) runs while the GPU works, and the step is completed by the next call that needs it.
 """
 
 from __future__ import annotations
@@ -25,6 +27,7 @@ class Engine:
         self._plan: Plan | None = None
         self.events: list[StepEvent] = []
         self.keep_events = False
+        self._launched = None   # (graph, number of entries) of a step that runs and is not committed yet
 
     @classmethod
     def for_model(cls, model, options: EngineOptions | None = None) -> "Engine":
@@ -59,6 +62,7 @@ class Engine:
         return rid
 
     def cancel(self, rid: int) -> None:
+        self.finish()
         self.scheduler.cancel(rid)
         self._pending.pop(rid, None)
 
@@ -83,6 +87,7 @@ class Engine:
     def plan(self) -> Plan | None:
         """The next step's entries, or None when there is nothing to run (the by-hand rung:
         kelpie_engine/sdk/engine.py:585-601). Follow with `commit`."""
+        self.finish()
         plan = self.scheduler.plan()
         if plan.n_entries == 0:
             self.scheduler.commit([])
@@ -105,12 +110,19 @@ class Engine:
         batch.set_sampling(plan.temperature, plan.top_k, plan.key0, plan.key1, plan.sample_pos)
         return batch
 
-    def step(self) -> StepEvent | None:
-        """One plan, one forward pass, one sampling call, one commit."""
+    def step(self, wait: bool = True) -> StepEvent | None:
+        """One plan, one forward pass, one sampling call, one commit. With `wait=False` a step
+        that runs as a CUDA graph is only launched: `finish()`, or the next `step`, `plan`, `wait`,
+        `cancel` or `close`, waits for its tokens and commits them (`poll` before that returns
+        what earlier steps produced); the return value is then None."""
         plan = self.plan()
         if plan is None:
             return None
         batch = self.build_batch(plan)
+        graph = self.step_fn.launch_graph(batch)
+        if graph is not None:
+            self._launched = (graph, plan.n_entries)
+            return self.finish() if wait else None
         tokens = self.step_fn.step_and_sample(batch)
         self.commit(self.step_fn.tokens_to_host(batch, tokens) if hasattr(tokens, "data_ptr") else np.asarray(tokens, dtype=np.int32))
         event = self.scheduler.event()
@@ -118,13 +130,26 @@ class Engine:
             self.events.append(event)
         return event
 
+    def finish(self) -> StepEvent | None:
+        """Completes a step that `step(wait=False)` launched: waits for its tokens, commits them."""
+        if self._launched is None:
+            return None
+        graph, n = self._launched
+        self._launched = None
+        self.commit(graph.tokens_on_host(n))
+        event = self.scheduler.event()
+        if self.keep_events:
+            self.events.append(event)
+        return event
+
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._launched is not None or self.scheduler.has_work()
 
     def set(self, **knobs) -> None:  # noqa: A003
         self.scheduler.set(**knobs)
 
     def close(self) -> None:
+        self.finish()
         self.scheduler.close()
 
     def __enter__(self) -> "Engine":

@@ -149,6 +149,7 @@ class StepFunction:
     def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False):
         self.model = model
         self.device = model.rt.device
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device() if torch.cuda.is_available() else 0
         self.groups, self.member_group = derive_groups(model.cache_members, page_size, num_pages)
         self.arena = KVArena(model.cache_members, self.groups, self.member_group, model.rt.dtype, self.device)
         self.state_tensors = [
@@ -274,6 +275,24 @@ class StepFunction:
                 self.h2d_bytes += batch.buf.nbytes
                 return graph.logits[: batch.n_logit_rows]
             return self.forward(self.upload(batch))
+
+    def launch_graph(self, batch: StepBatch) -> StepGraph | None:
+        """Launches the step as its CUDA graph, if the batch is one that the scheduler filled and
+        has a graph: upload, forward pass, sampling and the copy of the tokens to pinned memory are
+        all inside. Returns the graph (`tokens_on_host` waits for it), or None: run
+        `step_and_sample` then."""
+        if not batch.trusted:
+            return None
+        graph = self._graph_of(batch)
+        if graph is None or not graph.io_inside:
+            return None
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self.device):
+                graph.replay()
+        else:
+            graph.replay()
+        self.h2d_bytes += batch.buf.nbytes
+        return graph
 
     @torch.no_grad()
     def step_and_sample(self, batch: StepBatch) -> torch.Tensor:

@@ -92,6 +92,25 @@ def test_prompt_portions_run_as_graphs_when_a_shape_repeats(wide_b):
     assert got == want
 
 
+def test_steps_that_are_only_launched_give_the_same_tokens(wide_b):
+    """`step(wait=False)` returns when the step's graph has been launched; polls in between see
+    the tokens of earlier steps, and the step is completed by the next call that needs it. Prompts
+    of several lengths, so that admissions, portions, decoding and finishing all pass through."""
+    import research_2_b200 as r2
+    from research_2_b200.engine.api import generate_with
+
+    prompts = [random_tokens(80 + i, n, 1031) for i, n in enumerate((40, 9, 100, 3, 64))]
+    want = plain_generate(wide_b, prompts, 14)
+    with r2.run(wide_b, dtype="float32", block_size=8, max_requests=3, max_batch_tokens=64, capture=True) as engine:
+        launched = []
+        launch_graph = engine.step_fn.launch_graph
+        engine.step_fn.launch_graph = lambda batch: launched.append(launch_graph(batch)) or launched[-1]
+        got = generate_with(engine, prompts, 14, wait=False)
+        assert engine.finish() is None and not engine.has_work()
+        assert sum(g is not None for g in launched) > 10, "no step ran as a launched-only graph"
+    assert got == want
+
+
 def test_few_pages_preempt_and_recompute(wide_a):
     """So few pages that running requests are preempted: the tokens stay the same."""
     import research_2_b200 as r2
