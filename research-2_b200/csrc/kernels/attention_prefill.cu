@@ -21,10 +21,10 @@
 #include <math.h>
 
 #include <cstring>
-#include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tensor_maps.cuh"
 
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
@@ -59,10 +59,8 @@ struct PrefillParams {
 
 bool g_prefill_tma = true;                    // r2_attention_prefill_set_tma
 constexpr int TMA_TILE_BYTES = BN * 128;       // TMA form (head size 64): unpadded 128-byte rows
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+using namespace r2ptx;
 #define R2_ERR_TIMEOUT_KV_TILE 5
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
   int bytes = pred ? 16 : 0;  // 0 source bytes: the 16 destination bytes are filled with zeros
@@ -84,47 +82,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// 2^x by the hardware's approximation (2 ulp; 2^-inf = 0).
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Waits for the phase with the given parity; false after SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (spin > 1024) __nanosleep(64);
-  }
-  return false;
-}
-// One page's rows of one kv head: coordinates (dim, offset in page, kv head, page).
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // Threads: four warps that compute; the TMA form adds a fifth that only issues the tensor copies
 // (a tile's two or more copies cost the issuing thread several hundred cycles, which would
@@ -186,7 +143,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     int row = id / (HD / 8), c = id % (HD / 8);
     bool ok = row < rows_here;
     const bf16* src = p.q + size_t(t0 + r0 + (ok ? row : 0)) * p.q_row_stride + size_t(h) * HD + c * 8;
-    cp_async16(smem_addr(q_s + row * ROW_BYTES + c * 16), src, ok);
+    cp_async16(smem_u32(q_s + row * ROW_BYTES + c * 16), src, ok);
   }
 
   // Key and value tiles are copied in 16-byte pieces, consecutive threads taking consecutive
@@ -214,8 +171,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       int page = (pages[i] < 0 || pages[i] >= p.n_pages) ? 0 : pages[i];  // a bad entry reads the null page
       size_t off = ok ? size_t(page) * p.page_stride + (size_t(kvh) * p.page_size + page_offset(j, p.page_size, p.page_shift)) * HD + c * 8 : 0;
       uint32_t dst = uint32_t(stage * TILE_BYTES + row * ROW_BYTES + c * 16);
-      cp_async16(smem_addr(k_s) + dst, p.k_cache + off, ok);
-      cp_async16(smem_addr(v_s) + dst, p.v_cache + off, ok);
+      cp_async16(smem_u32(k_s) + dst, p.k_cache + off, ok);
+      cp_async16(smem_u32(v_s) + dst, p.v_cache + off, ok);
     }
   };
 
@@ -226,7 +183,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   // TMA form: lane b of the producer warp brings box b of a tile (box_rows key rows of one page,
   // keys and values); a box no row of which any query row may see is left out. The page of a box
   // is looked up one tile before its copies are issued.
-  const uint32_t full_base = smem_addr(full), empty_base = smem_addr(empty);
+  const uint32_t full_base = smem_u32(full), empty_base = smem_u32(empty);
   const int n_boxes = TMA ? BN / p.box_rows : 0;
   int box_page = INT_MIN;  // lane's page for the tile whose copies are issued next
   auto box_lookup = [&](int j0) {
@@ -248,8 +205,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       const int page = (box_page < 0 || box_page >= p.n_pages) ? 0 : box_page;  // a bad entry reads the null page
       const int off = page_offset(jb, p.page_size, p.page_shift);
       const uint32_t dst = uint32_t(stage * TMA_TILE_BYTES) + uint32_t(lane) * box_bytes;
-      tma_load_4d(smem_addr(k_s) + dst, &map_k, 0, off, kvh, page, bar);
-      tma_load_4d(smem_addr(v_s) + dst, &map_v, 0, off, kvh, page, bar);
+      tma_load_4d(smem_u32(k_s) + dst, &map_k, 0, off, kvh, page, bar);
+      tma_load_4d(smem_u32(v_s) + dst, &map_v, 0, off, kvh, page, bar);
     }
   };
   if (TMA) {
@@ -323,7 +280,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         for (int row = tid; row < BN; row += WARPS * 32) {
           const int j = j0 + row;
           if (j < lo || j > pmax) {
-            const uint32_t dst = smem_addr(v_s) + uint32_t(stage * TMA_TILE_BYTES + row * 128);
+            const uint32_t dst = smem_u32(v_s) + uint32_t(stage * TMA_TILE_BYTES + row * 128);
 #pragma unroll
             for (int c = 0; c < 8; ++c) asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + c * 16), "r"(0u) : "memory");
           }
@@ -343,15 +300,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     if (it == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
-        uint32_t addr = smem_addr(q_s + (warp * 16 + (lane & 15)) * ROW_BYTES + (ks * 16 + 8 * (lane >> 4)) * 2);
+        uint32_t addr = smem_u32(q_s + (warp * 16 + (lane & 15)) * ROW_BYTES + (ks * 16 + 8 * (lane >> 4)) * 2);
         ldmatrix_x4(addr, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
       }
     }
     // a warp whose 16 rows all lie past the entry's rows, or before every key of this tile, rests
     const bool warp_active = warp * 16 < rows_here && j0 <= pmin + min(warp * 16 + 15, rows_here - 1);
     if (warp_active) {
-      const uint32_t kt = smem_addr(k_s) + uint32_t(stage * KV_TILE);
-      const uint32_t vt = smem_addr(v_s) + uint32_t(stage * KV_TILE);
+      const uint32_t kt = smem_u32(k_s) + uint32_t(stage * KV_TILE);
+      const uint32_t vt = smem_u32(v_s) + uint32_t(stage * KV_TILE);
       // a row's 16-byte piece `c`: padded rows, or 128-byte rows swizzled by the row index
       auto piece = [&](uint32_t tile, int row, int c) -> uint32_t {
         return TMA ? tile + uint32_t(row * 128 + ((c ^ (row & 7)) << 4)) : tile + uint32_t(row * ROW_BYTES + c * 16);
@@ -482,72 +439,6 @@ extern "C" int r2_attention_prefill_head_dim(void) { return HD; }
 
 namespace {
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-  });
-  return fn;
-}
-
-// One layer's keys (or values) in the page pool as a 4-D tensor [page][kv head][offset][dim] of
-// bfloat16, copied in boxes of `box_rows` offsets of one head of one page, 128-byte swizzle.
-// Maps are kept per (base, geometry): a model asks for the same few again every step.
-struct MapKey {
-  const void* base;
-  long long page_stride;
-  int page_size, n_kv_heads, n_pages, box_rows;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && page_stride == o.page_stride && page_size == o.page_size && n_kv_heads == o.n_kv_heads &&
-           n_pages == o.n_pages && box_rows == o.box_rows;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = std::hash<const void*>()(k.base);
-    h = h * 1315423911u + std::hash<long long>()(k.page_stride);
-    h = h * 1315423911u + size_t(k.page_size) * 131u + size_t(k.n_kv_heads) * 31u + size_t(k.n_pages) * 7u + size_t(k.box_rows);
-    return h;
-  }
-};
-
-bool page_map(CUtensorMap* out, const void* base, long long page_stride, int page_size, int n_kv_heads, int n_pages, int box_rows) {
-  static std::mutex lock;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-  const MapKey key{base, page_stride, page_size, n_kv_heads, n_pages, box_rows};
-  std::lock_guard<std::mutex> guard(lock);
-  auto it = maps.find(key);
-  if (it != maps.end()) {
-    *out = it->second;
-    return true;
-  }
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(page_size), cuuint64_t(n_kv_heads), cuuint64_t(n_pages)};
-  cuuint64_t strides[3] = {cuuint64_t(HD) * 2, cuuint64_t(page_size) * HD * 2, cuuint64_t(page_stride) * 2};
-  cuuint32_t box[4] = {cuuint32_t(HD), cuuint32_t(box_rows), 1, 1};
-  cuuint32_t elem[4] = {1, 1, 1, 1};
-  CUtensorMap map;
-  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-    return false;
-  }
-  if (maps.size() > 4096) maps.clear();  // pools that came and went
-  maps.emplace(key, map);
-  *out = map;
-  return true;
-}
-
 template <bool TMA>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_tiles, cudaStream_t stream) {
   const size_t smem = TMA ? size_t(TILE_BYTES) + 1024 + 2 * STAGES * size_t(TMA_TILE_BYTES) : (1 + 2 * STAGES) * size_t(TILE_BYTES);
@@ -596,8 +487,8 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   const bool page_fits = page_size == 8 || page_size == 16 || page_size == 32 || page_size % 64 == 0;
   if (HD == 64 && page_fits && error_flag != nullptr && g_prefill_tma) {
     p.box_rows = page_size < 64 ? page_size : 64;
-    if (page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows) &&
-        page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows)) {
+    if (r2::page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD) &&
+        r2::page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD)) {
       return launch<true>(mk, mv, p, n_tiles, stream);
     }
     p.box_rows = 0;

@@ -31,10 +31,10 @@
 #include <math.h>
 
 #include <cstring>
-#include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tensor_maps.cuh"
 
 namespace {
 
@@ -44,7 +44,6 @@ constexpr int THREADS = 192;
 constexpr int SOFTMAX_WARPS = 4;
 constexpr int Q_BYTES = BM * 128, KV_BYTES = BN * 128;
 constexpr float RESCALE_STEP = 8.f;  // log2 of how far a tile's maximum may exceed the one in use
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
 #define R2_ERR_TIMEOUT_ATTN 6
 
 struct Params {
@@ -58,122 +57,7 @@ struct Params {
   int* error_flag;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-// Waits for the phase with the given parity to complete; false after SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 1024) __nanosleep(64);
-  }
-  return false;
-}
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-// Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= uint64_t((addr >> 4) & 0x3FFF);
-  d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= uint64_t(1) << 46;   // descriptor version
-  d |= uint64_t(2) << 61;   // SWIZZLE_128B
-  return d;
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The same with the A operand in tensor memory (row = lane, two bfloat16 to a column).
-__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float y;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-#define R2_REGS32(r) \
-  "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), \
-  "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), \
-  "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-// 32 consecutive columns of the thread's tensor-memory lane (no wait: several may be in flight).
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, "
-      "%21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : R2_REGS32(r)
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, "
-      "%21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+using namespace r2ptx;
 
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -539,77 +423,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 // ---- host side ------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* base;
-  long long a, b;
-  int c, d, e, f;
-  bool operator==(const MapKey& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d && e == o.e && f == o.f; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = std::hash<const void*>()(k.base);
-    h = h * 1315423911u + std::hash<long long>()(k.a);
-    h = h * 1315423911u + std::hash<long long>()(k.b);
-    return h * 1315423911u + size_t(k.c) * 131u + size_t(k.d) * 31u + size_t(k.e) * 7u + size_t(k.f);
-  }
-};
-
-// Tensor maps are kept per (base, geometry): a model asks for the same few again every step.
-bool cached_map(CUtensorMap* out, const MapKey& key, cuuint32_t rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
-  static std::mutex lock;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
-  std::lock_guard<std::mutex> guard(lock);
-  auto it = maps.find(key);
-  if (it != maps.end()) {
-    *out = it->second;
-    return true;
-  }
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint32_t elem[4] = {1, 1, 1, 1};
-  CUtensorMap map;
-  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(key.base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-    return false;
-  }
-  if (maps.size() > 4096) maps.clear();  // pools that came and went
-  maps.emplace(key, map);
-  *out = map;
-  return true;
-}
-
-// One layer's keys (or values) in the page pool as [page][kv head][offset][dim], boxes of `box_rows` offsets.
-bool page_map(CUtensorMap* out, const void* base, long long page_stride, int page_size, int n_kv_heads, int n_pages, int box_rows) {
-  cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(page_size), cuuint64_t(n_kv_heads), cuuint64_t(n_pages)};
-  cuuint64_t strides[3] = {cuuint64_t(HD) * 2, cuuint64_t(page_size) * HD * 2, cuuint64_t(page_stride) * 2};
-  cuuint32_t box[4] = {cuuint32_t(HD), cuuint32_t(box_rows), 1, 1};
-  return cached_map(out, MapKey{base, page_stride, 0, page_size, n_kv_heads, n_pages, box_rows}, 4, dims, strides, box);
-}
-
 // The queries [rows][heads * 64] (row stride in elements), boxes of 128 rows of one head.
 bool query_map(CUtensorMap* out, const void* base, long long rows, long long row_stride, int n_heads) {
   cuuint64_t dims[2] = {cuuint64_t(n_heads) * HD, cuuint64_t(rows)};
   cuuint64_t strides[1] = {cuuint64_t(row_stride) * 2};
   cuuint32_t box[2] = {cuuint32_t(HD), cuuint32_t(BM)};
-  return cached_map(out, MapKey{base, rows, row_stride, n_heads, -1, 0, 0}, 2, dims, strides, box);
+  return r2::cached_bf16_map(out, r2::MapKey{base, rows, row_stride, n_heads, -1, 0, 0}, 2, dims, strides, box);
 }
 
 }  // namespace
@@ -642,8 +461,8 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
   p.error_flag = error_flag;
   CUtensorMap mq, mk, mv;
   if (!query_map(&mq, q, n_rows, q_row_stride, n_heads) ||
-      !page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows) ||
-      !page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows)) {
+      !r2::page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD) ||
+      !r2::page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD)) {
     return R2_UNSUPPORTED;
   }
   const size_t smem = 1024 + Q_BYTES + 2 * STAGES * size_t(KV_BYTES) + 16 * 8 + 16;
