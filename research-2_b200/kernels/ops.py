@@ -37,6 +37,18 @@ def dtype_code(dtype: torch.dtype) -> int:
 _launches = 0
 
 
+_uses: dict[str, int] = {}
+
+
+def kernel_uses() -> dict[str, int]:
+    """How often each attention kernel has been chosen (tests check the choice by it)."""
+    return dict(_uses)
+
+
+def _used(name: str) -> None:
+    _uses[name] = _uses.get(name, 0) + 1
+
+
 def launch_count() -> int:
     """How many kernels of this package have been launched (graph replays count their kernels)."""
     return _launches
@@ -138,14 +150,15 @@ def use_fused_norm(on: bool) -> bool:
 N_SMS = 148
 
 
-_prefill_tc = os.environ.get("R2_PREFILL_TC", "1") != "0"
+_prefill_tc = {"0": False, "always": "always"}.get(os.environ.get("R2_PREFILL_TC", "1"), True)
 
 
-def use_prefill_tc(on: bool) -> bool:
-    """Switch the tcgen05 prefill attention kernel (head size 64) on or off; off, the mma.sync
-    kernel takes every shape. Returns the previous setting."""
+def use_prefill_tc(on):
+    """The tcgen05 prefill attention kernel (head size 64): False, the mma.sync kernel takes
+    every shape; True, the tcgen05 kernel takes batches whose 128-row tiles are at least half
+    full; "always", every batch that it can take (tests). Returns the previous setting."""
     global _prefill_tc
-    before, _prefill_tc = _prefill_tc, bool(on)
+    before, _prefill_tc = _prefill_tc, ("always" if on == "always" else bool(on))
     return before
 
 
@@ -528,8 +541,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
-    if (q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64):
-        # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles
+    if (q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64
+            and (_prefill_tc == "always" or 2 * n >= 64 * n_tiles)):
+        # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles, one entry to a
+        # tile. Where most tiles would be mostly empty (single decoded tokens beside a portion: 64 such rows
+        # and 448 of a prompt took 77 us against 39), the mma.sync kernel with its 64-row tiles goes on.
         _need(q_start, "q_start", torch.int32, 1)
         n_entries = q_start.shape[0] - 1
         status = _lib("attention_prefill_tc").r2_attention_prefill_tc(
@@ -538,6 +554,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             (n_tiles + n_entries + 1) // 2, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error), _stream())
         if status != -4:
             _check(status, "paged_attention (prefill, tcgen05)")
+            _used("attention_prefill_tc")
             return out
     if (q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
             and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0):
@@ -549,6 +566,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error),
             _stream())
         _check(status, "paged_attention (prefill)")
+        _used("attention_prefill")
         return out
     status = _lib("attention_simt").r2_attention_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),

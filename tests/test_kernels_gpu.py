@@ -401,7 +401,7 @@ def test_prefill_attention_on_tcgen05(case, window):
     o = ops()
     pc = PagedCase(entries, h, hkv, hd, page, torch.bfloat16, seed=page + window + 5, garbage=float("inf"))
     scale = hd**-0.5 / 1.5
-    before = o.use_prefill_tc(True)
+    before = o.use_prefill_tc("always")
     try:
         by_tc = pc.run(scale, window, q_start=pc.q_start, n_tiles=pc.n_tiles)
         o.use_prefill_tc(False)
@@ -426,7 +426,7 @@ def test_prefill_attention_on_tcgen05_with_every_sm_shared_by_two_ctas():
     before = o.use_prefill_tc(False)
     try:
         by_mma = pc.run(scale, 0, q_start=pc.q_start, n_tiles=pc.n_tiles).float()
-        o.use_prefill_tc(True)
+        o.use_prefill_tc("always")
         for _ in range(5):
             by_tc = pc.run(scale, 0, q_start=pc.q_start, n_tiles=pc.n_tiles).float()
             assert torch.isfinite(by_tc).all()
@@ -528,6 +528,26 @@ def test_pad_rows_are_zero():
     pc.row_entry[1] = -1
     out = pc.run(0.25)
     assert torch.count_nonzero(out[1]) == 0 and torch.count_nonzero(out[0]) > 0
+
+
+def test_prefill_attention_kernel_is_chosen_by_how_full_its_tiles_are():
+    """Whole prompts go to the tcgen05 kernel (128-row tiles, one entry to a tile); a batch of
+    single decoded tokens beside one portion, whose tiles would be mostly empty, stays with the
+    64-row tiles of the mma.sync kernel. Both give the plain statement's numbers."""
+    o = ops()
+    scale = 0.125
+    for entries, want in (([(0, 300), (40, 200)], "attention_prefill_tc"),
+                          ([(200 + i, 1) for i in range(24)] + [(0, 150)], "attention_prefill")):
+        pc = PagedCase(entries, 3, 3, 64, 16, torch.bfloat16, seed=len(entries), garbage=float("inf"))
+        before, uses = o.use_prefill_tc(True), o.kernel_uses()
+        try:
+            got = pc.run(scale, 0, q_start=pc.q_start, n_tiles=pc.n_tiles)
+        finally:
+            o.use_prefill_tc(before)
+        after = o.kernel_uses()
+        assert after.get(want, 0) == uses.get(want, 0) + 1, (want, uses, after)
+        torch.testing.assert_close(got.float().cpu(), pc.plain(scale, 0), atol=3e-2, rtol=3e-2)
+    assert o.device_errors() == 0
 
 
 def test_sampling_greedy_first_index_on_ties():
