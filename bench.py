@@ -267,6 +267,37 @@ def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
             "d2h_bytes_per_step": 4 * batch, "polled_tokens": n_tokens}
 
 
+def mixed_point(model, n_requests: int = 64, new_tokens: int = 256) -> dict:
+    """A continuous batch through the Python entry point: prompts of 16 to 768 tokens, portions
+    of 512 tokens a step beside the decoded tokens of the others (the workload that the baseline
+    names for the 355M size, here at the benchmark's own). The first pass captures the graphs of
+    the shapes that come; the second is timed by the host's clock."""
+    import random
+
+    import torch
+    from research_2_b200.config.engine_options import EngineOptions
+    from research_2_b200.engine.api import generate_with
+    from research_2_b200.engine.engine import Engine
+
+    opts = EngineOptions(dtype="bfloat16", max_requests=n_requests, block_size=PAGE, max_batch_tokens=512 + n_requests, capture=True)
+    engine = Engine.for_model(model, opts)
+    rng = random.Random(SEED + 300)
+    gen = torch.Generator().manual_seed(SEED + 300)
+    prompts = [torch.randint(0, model.vocab_size, (rng.randint(16, 768),), generator=gen).tolist() for _ in range(n_requests)]
+    generate_with(engine, prompts, new_tokens, wait=False)
+    engine.keep_events = True
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = generate_with(engine, prompts, new_tokens, wait=False)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    steps = len(engine.events)
+    engine.close()
+    n_out, n_in = sum(len(o) for o in out), sum(len(p) for p in prompts)
+    return {"generated_per_s": n_out / dt, "tokens_per_s": (n_in + n_out) / dt, "requests": n_requests,
+            "prompt_tokens": n_in, "generated_tokens": n_out, "steps": steps, "ms": dt * 1e3}
+
+
 def reference_arm() -> int:
     print(json.dumps({
         "impl": "reference",
@@ -342,6 +373,7 @@ def main() -> int:
             del lp
             torch.cuda.empty_cache()
         line["points"] = points
+        line["mixed"] = mixed_point(model)
     print(json.dumps(line))
     return 0
 
