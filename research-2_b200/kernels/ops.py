@@ -121,7 +121,7 @@ def _lib(source: str) -> C.CDLL:
 
 def build_all() -> None:
     """Compile every kernel library (what `__graft_entry__.build()` calls)."""
-    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling"):
+    for source in ("rowwise", "gemm_simt", "gemm_tc", "mlp_fused", "attention_simt", "attention_prefill_tc", "sampling"):
         _lib(source)
     for head_dim in (16, 32, 64):  # the head sizes of the tiny test models and of GPT-2
         _lib_for_head_dim("attention_decode", head_dim)
@@ -139,6 +139,18 @@ def use_fused_decode_attention(on: bool) -> bool:
     """Switch the one-launch decode attention (cache write and slice merge inside) on or off."""
     global _fused_decode
     before, _fused_decode = _fused_decode, bool(on)
+    return before
+
+
+_fused_mlp = os.environ.get("R2_FUSED_MLP", "0") == "1"
+
+
+def use_fused_mlp(on: bool) -> bool:
+    """Switch the one-kernel feed-forward for a few rows (bfloat16) on or off; off (the default:
+    it measured slower, 17.3 against 6.9 + 4.9 us at 8 x 768 x 3,072 x 768), its two products run
+    as kernels of their own. Returns the previous setting."""
+    global _fused_mlp
+    before, _fused_mlp = _fused_mlp, bool(on)
     return before
 
 
@@ -247,6 +259,7 @@ class _Workspace:
     def __init__(self, device):
         self.floats = torch.empty(self.FLOATS, dtype=torch.float32, device=device)
         self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
+        self.mlp_counters = torch.zeros(16, dtype=torch.int32, device=device)  # the fused feed-forward's, zero between launches
         self.error = torch.zeros(4, dtype=torch.int32, device=device)
 
 
@@ -369,6 +382,43 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
         return None
     _check(status, "linear (tensor cores, fused norm)")
     return out
+
+
+def mlp(h, w_in: torch.Tensor, b_in: torch.Tensor, act: str, w_out: torch.Tensor, b_out: torch.Tensor | None,
+        residual: torch.Tensor | None = None) -> torch.Tensor:
+    """act(h @ w_in + b_in) @ w_out + b_out (+ residual), both matrices stored [in, out]. `h` may be
+    NormedRows. A few bfloat16 rows of a width that fits run as ONE kernel (LayerNorm, both
+    products, the sum over the hidden features: csrc/kernels/mlp_fused.cu); everything else as two
+    `linear` calls."""
+    if (_fused_mlp and _tensor_core_gemm and _fused_norm and isinstance(h, NormedRows) and h.dtype == torch.bfloat16
+            and w_in.dtype == torch.bfloat16 and w_out.dtype == torch.bfloat16 and residual is not None
+            and residual.dtype == torch.float32 and h.shape[0] <= 16 and h.x.is_contiguous()):
+        m, k = h.shape
+        hidden, n_out = w_in.shape[1], w_out.shape[1]
+        if w_in.shape[0] != k or w_out.shape[0] != hidden:
+            raise KernelError(f"mlp: rows {h.shape}, w_in {tuple(w_in.shape)} and w_out {tuple(w_out.shape)} do not fit")
+        if act not in ACTIVATIONS:
+            raise KernelError(f"unknown activation {act!r}")
+        _need(h.x, "x", torch.float32, 2)
+        _need(residual, "residual", torch.float32, 2)
+        if tuple(residual.shape) != (m, n_out):
+            raise KernelError(f"mlp: residual {tuple(residual.shape)} is not [{m}, {n_out}]")
+        for name, t, n in (("b_in", b_in, hidden), ("b_out", b_out, n_out), ("gamma", h.gamma, k), ("beta", h.beta, k)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_cuda):
+                raise KernelError(f"mlp: {name} must be {n} float32 values on the device")
+        out = torch.empty(m, n_out, dtype=torch.float32, device=h.device)
+        ws = _workspace(h.device)
+        status = _lib("mlp_fused").r2_mlp_fused(
+            _p(h.x), h.x.stride(0), _p(h.rows), _p(h.gamma), _p(h.beta), C.c_float(h.eps), m, k, _p(w_in), _rows(w_in, "w_in"),
+            _p(b_in), hidden, _p(w_out), _rows(w_out, "w_out"), _p(b_out), n_out, _p(residual), _rows(residual, "residual"),
+            _p(out), _rows(out, "out"), ACTIVATIONS[act], _p(ws.floats), C.c_longlong(ws.floats.numel()), _p(ws.mlp_counters),
+            _p(ws.error), _stream())
+        if status != -4:
+            _check(status, "mlp (one kernel)")
+            _used("mlp_fused")
+            return out
+    inner = linear(h, w_in, b_in, act=act)
+    return linear(inner, w_out, b_out, residual=residual)
 
 
 class KvScatter(C.Structure):

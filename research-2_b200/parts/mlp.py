@@ -31,5 +31,4 @@ class DenseMLP:
         return [self.w_in, self.w_out]
 
     def forward(self, h, residual, ctx):
-        inner = ops.linear(h, self.w_in, self.b_in, act=self.activation)
-        return ops.linear(inner, self.w_out, self.b_out, residual=residual)
+        return ops.mlp(h, self.w_in, self.b_in, self.activation, self.w_out, self.b_out, residual=residual)

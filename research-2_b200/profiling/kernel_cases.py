@@ -1,6 +1,6 @@
 """Runs each hot kernel twice at benchmark shapes (GPT-2 124M), for ncu to capture:
 
-    ncu --set full --clock-control none -k regex:'gemm_tc|decode_kernel|prefill' -c 36 \
+    ncu --set full --clock-control none -k regex:'gemm_tc|mlp_fused|decode_kernel|prefill' -c 40 \
         -o kernels python -m research_2_b200.profiling.kernel_cases
 
 With `--time` it instead times each case inside a CUDA graph of 20 launches (CUDA events around
@@ -66,6 +66,8 @@ def cases():
         ("decode: LayerNorm + fc product with gelu, 8 x 768 x 3,072", lambda: ops.linear(normed(), wfc, bias, act="gelu_new")),
         ("decode: mlp output product + residual, 8 x 3,072 x 768", lambda: ops.linear(f8, wproj2, bd, residual=h8)),
     ]
+    out.append(("decode: feed-forward in one kernel (off by default), 8 x 768 x 3,072 x 768",
+                lambda: (ops.use_fused_mlp(True), ops.mlp(normed(), wfc, bias, "gelu_new", wproj2, bd, residual=h8), ops.use_fused_mlp(False))))
     logits8 = torch.randn(8, V, device=dev)
     zeros_i = torch.zeros(8, dtype=torch.int32, device=dev)
     ones_i, temp = torch.ones(8, dtype=torch.int32, device=dev), torch.full((8,), 0.8, device=dev)

@@ -178,6 +178,61 @@ def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
     assert o.device_errors() == 0
 
 
+@pytest.mark.parametrize("m,k,hidden,n_out,act", [(8, 768, 3072, 768, "gelu_new"), (1, 768, 3072, 768, "gelu"),
+                                                  (16, 768, 3072, 768, "gelu_new"), (5, 512, 1024, 512, "gelu_new"),
+                                                  (13, 1024, 512, 256, "gelu"), (3, 640, 1536, 384, "gelu_new")])
+def test_feed_forward_in_one_kernel(m, k, hidden, n_out, act):
+    """LayerNorm, both products of the feed-forward and the sum over the hidden features in one
+    kernel (a few bfloat16 rows): the same as the two products apart, and as a plain float32
+    statement; the same bits at every launch; rows picked by an index list."""
+    o = ops()
+    torch.manual_seed(m + k + hidden)
+    x = (torch.randn(m + 3, k) * 2 + 0.5).to(DEV)
+    g, b = (1 + 0.1 * torch.randn(k)).to(DEV), (0.1 * torch.randn(k)).to(DEV)
+    w1 = (torch.randn(k, hidden) * k**-0.5).bfloat16().to(DEV)
+    w2 = (torch.randn(hidden, n_out) * hidden**-0.5).bfloat16().to(DEV)
+    b1, b2 = torch.randn(hidden).to(DEV), torch.randn(n_out).to(DEV)
+    res = torch.randn(m, n_out).to(DEV)
+    rows = torch.randperm(m + 3)[:m].to(torch.int32).to(DEV)
+    for pick in (None, rows):
+        lazy = o.NormedRows(x if pick is not None else x[:m], g, b, 1e-5, torch.bfloat16, rows=pick)
+        before, uses = o.use_fused_mlp(True), o.kernel_uses().get("mlp_fused", 0)
+        try:
+            fused = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
+            again = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
+            assert o.kernel_uses().get("mlp_fused", 0) == uses + 2, "the one-kernel form did not take the shape"
+            o.use_fused_mlp(False)
+            apart = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
+        finally:
+            o.use_fused_mlp(before)
+        assert o.device_errors() == 0
+        assert torch.equal(fused, again)
+        src = x[:m] if pick is None else x[pick.long()]
+        h = F.layer_norm(src, (k,), g, b, 1e-5).bfloat16().float()
+        inner = F.gelu(h @ w1.float() + b1, approximate="tanh" if act == "gelu_new" else "none").bfloat16().float()
+        want = inner @ w2.float() + b2 + res
+        torch.testing.assert_close(fused, want, atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(fused, apart, atol=2e-2, rtol=2e-2)
+
+
+def test_feed_forward_shapes_that_the_one_kernel_form_does_not_take():
+    """A hidden width that is no multiple of 512, or more than 16 rows: two products as before."""
+    o = ops()
+    torch.manual_seed(3)
+    for m, k, hidden, n_out in ((4, 96, 320, 96), (40, 768, 3072, 768)):
+        x = torch.randn(m, k).to(DEV)
+        g, b = torch.ones(k).to(DEV), torch.zeros(k).to(DEV)
+        w1 = (torch.randn(k, hidden) * k**-0.5).bfloat16().to(DEV)
+        w2 = (torch.randn(hidden, n_out) * hidden**-0.5).bfloat16().to(DEV)
+        b1, b2, res = torch.randn(hidden).to(DEV), torch.randn(n_out).to(DEV), torch.randn(m, n_out).to(DEV)
+        uses = o.kernel_uses().get("mlp_fused", 0)
+        got = o.mlp(o.NormedRows(x, g, b, 1e-5, torch.bfloat16), w1, b1, "gelu_new", w2, b2, residual=res)
+        assert o.kernel_uses().get("mlp_fused", 0) == uses
+        h = F.layer_norm(x, (k,), g, b, 1e-5).bfloat16().float()
+        want = F.gelu(h @ w1.float() + b1, approximate="tanh").bfloat16().float() @ w2.float() + b2 + res
+        torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     """In float32 a row's result is the same bits alone and among other rows."""
     torch.manual_seed(0)
