@@ -31,7 +31,10 @@ def generate(  # noqa: PLR0913
         return generate_with(engine, prompts, max_new_tokens, temperature, top_k, seed, stop_token_ids)
 
 
-def generate_with(engine: Engine, prompts, max_new_tokens, temperature=0.0, top_k=0, seed=0, stop_token_ids=(), wait=True):
+def generate_with(engine: Engine, prompts, max_new_tokens, temperature=0.0, top_k=0, seed=0, stop_token_ids=(), wait=False):
+    """Continuations of all prompts through one engine, as many at a time as it has request slots. With
+    `wait=False` (the default) a step is only launched before the requests are polled, so the host's share
+    of a step runs while the GPU works; the tokens are the same."""
     from .scheduler import Full
 
     out: list[list[int]] = [[] for _ in prompts]

@@ -106,6 +106,7 @@ def test_steps_that_are_only_launched_give_the_same_tokens(wide_b):
         launch_graph = engine.step_fn.launch_graph
         engine.step_fn.launch_graph = lambda batch: launched.append(launch_graph(batch)) or launched[-1]
         got = generate_with(engine, prompts, 14, wait=False)
+        assert generate_with(engine, prompts, 14, wait=True) == got
         assert engine.finish() is None and not engine.has_work()
         assert sum(g is not None for g in launched) > 10, "no step ran as a launched-only graph"
     assert got == want
