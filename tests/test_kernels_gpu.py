@@ -532,7 +532,8 @@ def test_decode_attention_in_one_launch(case, window, max_context):
 def test_decode_slices_choice():
     o = ops()
     assert o.decode_slices(64, 12, 1024) == 1
-    assert o.decode_slices(8, 12, 1024) == 7
+    assert o.decode_slices(8, 12, 1024) == 6    # 576 CTAs: one wave of four to an SM
+    assert o.decode_slices(16, 12, 1024) == 3
     assert o.decode_slices(1, 12, 1024) == 8
     assert o.decode_slices(1, 12, 100) == 1
 
