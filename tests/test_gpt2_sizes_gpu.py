@@ -1,8 +1,10 @@
 """The benchmark's own size (GPT-2 124M: 12 layers, width 768, 12 heads of 64, vocabulary
-50,257) with random weights: logits in float32 and in bfloat16 against the plain implementation
-in all four cuttings (whole, the last 32 tokens one by one, portions, mixed in few pages). At
-this size the products run as CTA pairs or cluster split-K, attention on tcgen05, and the
-logits over a vocabulary that is no multiple of anything."""
+50,257) with random weights, and the layer sizes of the 355M and 1.5B models (two layers each:
+width 1,024 with 16 heads; width 1,600 with 25 heads, which is no multiple of 128): logits in
+float32 and in bfloat16 against the plain implementation in all four cuttings (whole, the last
+32 tokens one by one, portions, mixed in few pages). At these sizes the products run as
+cluster split-K or whole tiles, attention on tcgen05, and the logits over a vocabulary that is
+no multiple of anything."""
 
 from __future__ import annotations
 
@@ -22,17 +24,34 @@ GPT2_124M = {
 }
 
 
+SIZES = {
+    "124M": GPT2_124M,
+    "355M_two_layers": dict(GPT2_124M, n_layer=2, n_embd=1024, n_head=16, n_inner=4096),
+    "1.5B_two_layers": dict(GPT2_124M, n_layer=2, n_embd=1600, n_head=25, n_inner=6400),
+}
+
+
 @pytest.fixture(scope="module")
-def folder_124m(tmp_path_factory):
-    return make_model_dir(tmp_path_factory.mktemp("gpt2_124m"), {"config": GPT2_124M, "seed": 5, "std": 0.02, "store_dtype": "float32"})
+def folders(tmp_path_factory):
+    made = {}
+
+    def folder(size):
+        if size not in made:
+            made[size] = make_model_dir(tmp_path_factory.mktemp("gpt2_" + size.replace(".", "_")),
+                                        {"config": SIZES[size], "seed": 5, "std": 0.02, "store_dtype": "float32"})
+        return made[size]
+
+    return folder
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_gpt2_124m_in_all_four_cuttings(folder_124m, dtype):
+@pytest.mark.parametrize("size", sorted(SIZES))
+def test_gpt2_sizes_in_all_four_cuttings(folders, size, dtype):
+    folder_124m = folders(size)
     requests = {f"r{i}": random_tokens(500 + i, n, GPT2_124M["vocab_size"]) for i, n in enumerate((130, 40, 9, 200))}
     cuttings = {"whole": (traces.whole(requests), 1), "decode32": (traces.prefill_then_decode(requests, 32), 1),
                 "portions": (traces.portions(requests), 1), "mixed": (traces.mixed(requests, max_live=4), 4)}
     for mode, (tb, live) in cuttings.items():
         biggest = sorted((round64(len(v)) for v in requests.values()), reverse=True)[:live]
         outputs = run_trace(folder_124m, tb, dtype, sum(biggest), 16)
-        compare(folder_124m, requests, tb, outputs, dtype, f"124M/{dtype}/{mode}")
+        compare(folder_124m, requests, tb, outputs, dtype, f"{size}/{dtype}/{mode}")
