@@ -149,7 +149,8 @@ class StepFunction:
     def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False):
         self.model = model
         self.device = model.rt.device
-        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device() if torch.cuda.is_available() else 0
+        # the device's number, for the launch path that skips torch's device guard when it is the current one
+        self._device_index = self.device.index if self.device.index is not None else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
         self.groups, self.member_group = derive_groups(model.cache_members, page_size, num_pages)
         self.arena = KVArena(model.cache_members, self.groups, self.member_group, model.rt.dtype, self.device)
         self.state_tensors = [
