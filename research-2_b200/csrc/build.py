@@ -130,7 +130,11 @@ def host_library() -> ctypes.CDLL:
     folder = CSRC / "host"
     sources = sorted(folder.glob("*.cc"))
     gxx = shutil.which("g++") or "g++"
-    return _build_and_load("r2host", sources, _headers(folder), [gxx], GXX_FLAGS, [], gxx)
+    flags = list(GXX_FLAGS)
+    if os.environ.get("R2_HOST_SANITIZE") == "1":
+        # for the CPU tests: run python with LD_PRELOAD set to g++'s libasan.so and libubsan.so
+        flags = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined"] + [f for f in flags if f != "-O2"]
+    return _build_and_load("r2host", sources, _headers(folder), [gxx], flags, [], gxx)
 
 
 def kernel_library(source: str, defines: dict[str, int | str] | None = None) -> ctypes.CDLL:
