@@ -274,17 +274,20 @@ extern "C" int r2_sample(const float* logits, int ld, int n_rows, int vocab, con
   int n_slices = (vocab + 8 * THREADS - 1) / (8 * THREADS);  // about eight tokens a thread
   n_slices = n_rows > MAX_SPLIT_ROWS ? 1 : (n_slices < 1 ? 1 : (n_slices > MAX_SPLIT ? MAX_SPLIT : n_slices));
   // Shared memory for a copy of the row, where a CTA can have that much (the static part is below 12 KB).
-  static int most_smem = -1;
+  static int most_smem = -1, n_sms = 1;
   if (most_smem < 0) {
     int dev = 0, most = 0;
     cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&most, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most - 12 * 1024) != cudaSuccess) most = 0;
     most_smem = most > 12 * 1024 ? most - 12 * 1024 : 0;
     (void)cudaGetLastError();
   }
   const size_t row_bytes = size_t(vocab) * sizeof(float);
-  const int row_fits = row_bytes <= size_t(most_smem) ? 1 : 0;
+  // (a CTA with the row in shared memory has an SM to itself: with more CTAs than SMs, as at 64
+  // rows, greedy and plain temperature rows would queue behind that, so the copy is left out there)
+  const int row_fits = (row_bytes <= size_t(most_smem) && n_rows * n_slices <= n_sms) ? 1 : 0;
   r2_launch(sample_kernel, dim3(n_rows, n_slices), dim3(THREADS), row_fits ? row_bytes : size_t(0), stream, logits, ld, vocab, temperature,
             top_k, key0, key1, sample_pos, tokens, row_fits);
   return launch_status();
