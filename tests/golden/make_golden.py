@@ -3,7 +3,7 @@ random model, for comparison with the plain implementation (tests/plain/gpt2_pla
 
 Run once, on the CPU, where the reference tree is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py PATH_OF_THE_REFERENCE_TREE
 
 It imports `kelpie_models.models.torch.gpt2` and `kelpie_models.kernels.ops.sample` from the
 reference's source tree (no native library is needed: the ops run their torch bodies), builds
@@ -89,4 +89,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py PATH_OF_THE_REFERENCE_TREE")
+    main(sys.argv[1])
