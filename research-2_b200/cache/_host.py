@@ -6,7 +6,7 @@ import ctypes as C
 
 from ..csrc.build import host_library
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 I32P = C.POINTER(C.c_int32)
 
 
@@ -18,7 +18,7 @@ class SchedulerConfigC(C.Structure):
     _fields_ = [
         ("max_requests", C.c_int32), ("max_seq_len", C.c_int32), ("max_batch_tokens", C.c_int32),
         ("max_batch_reqs", C.c_int32), ("order", C.c_int32), ("reserve_ratio", C.c_float),
-        ("eos_token", C.c_int32), ("vocab_size", C.c_int32),
+        ("eos_token", C.c_int32), ("vocab_size", C.c_int32), ("chunk_size", C.c_int32),
     ]
 
 
@@ -46,7 +46,16 @@ class StepBatchC(C.Structure):
 
 class StallC(C.Structure):
     _fields_ = [("stalled", C.c_int32), ("req_id", C.c_int32), ("n_work", C.c_int32),
-                ("need_pages", C.c_int32), ("free_pages", C.c_int32)]
+                ("need_pages", C.c_int32), ("free_pages", C.c_int32), ("group", C.c_int32)]
+
+
+class RequestEventC(C.Structure):
+    _fields_ = [
+        ("t_arrival_ns", C.c_int64), ("t_first_sched_ns", C.c_int64), ("t_first_token_ns", C.c_int64),
+        ("t_last_token_ns", C.c_int64), ("t_finish_ns", C.c_int64), ("first_step", C.c_int64), ("last_step", C.c_int64),
+        ("request_id", C.c_int32), ("n_prompt", C.c_int32), ("n_generated", C.c_int32), ("max_new", C.c_int32),
+        ("n_preempted", C.c_int32), ("n_chunks", C.c_int32), ("state", C.c_int32), ("peak_pages", C.c_int32),
+    ]
 
 
 class StepEventC(C.Structure):
@@ -103,6 +112,9 @@ def lib() -> C.CDLL:
         "r2_sched_event": (i32, [vp, C.POINTER(StepEventC)]),
         "r2_sched_counts": (i32, [vp, I32P, I32P]),
         "r2_sched_request_info": (i32, [vp, i32] + [I32P] * 5),
+        "r2_sched_request_event": (i32, [vp, i32, C.POINTER(RequestEventC)]),
+        "r2_sched_drain_request_events": (i32, [vp, C.POINTER(RequestEventC), i32]),
+        "r2_sched_grain": (i32, [vp]),
         "r2_sched_set": (i32, [vp, i32, C.c_double]),
     }
     for name, (res, args) in sig.items():
@@ -111,7 +123,7 @@ def lib() -> C.CDLL:
         fn.argtypes = args
     if h.r2_abi_version() != ABI_VERSION:
         raise RuntimeError(f"host library ABI {h.r2_abi_version()} != expected {ABI_VERSION}")
-    for which, struct in enumerate((GroupSpecC, SchedulerConfigC, PlanC, StallC, StepEventC, StepBatchC)):
+    for which, struct in enumerate((GroupSpecC, SchedulerConfigC, PlanC, StallC, StepEventC, StepBatchC, RequestEventC)):
         if h.r2_sizeof(which) != C.sizeof(struct):
             raise RuntimeError(f"host library struct {struct.__name__}: size {h.r2_sizeof(which)} != {C.sizeof(struct)}")
     _lib = h

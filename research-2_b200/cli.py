@@ -31,6 +31,8 @@ def _engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-seq-len", type=int, default=0, help="0 = the model's own maximum")
     p.add_argument("--max-batch-tokens", type=int, default=1024)
     p.add_argument("--max-batch-reqs", type=int, default=0)
+    p.add_argument("--chunk-size", type=int, default=0,
+                   help="most tokens of a prompt portion that does not finish its prompt; 0 = the token budget decides")
     p.add_argument("--reserve-ratio", type=float, default=0.0)
     p.add_argument("--order", default="running_first", choices=("running_first", "waiting_first"))
 
@@ -58,7 +60,7 @@ def cmd_generate(args) -> int:
         args.model, prompts, args.max_new_tokens, temperature=args.temperature, top_k=args.top_k, seed=args.seed,
         stop_token_ids=_ints(args.stop_token_ids), device=args.device, dtype=args.dtype, capture=args.capture,
         max_requests=args.max_requests, num_slabs=args.num_slabs, block_size=args.block_size, max_seq_len=args.max_seq_len,
-        max_batch_tokens=args.max_batch_tokens, max_batch_reqs=args.max_batch_reqs, reserve_ratio=args.reserve_ratio,
+        max_batch_tokens=args.max_batch_tokens, max_batch_reqs=args.max_batch_reqs, chunk_size=args.chunk_size, reserve_ratio=args.reserve_ratio,
         order=args.order)
     for prompt, out in zip(prompts, outs):
         print(json.dumps({"prompt": prompt, "tokens": out}))

@@ -27,6 +27,7 @@ class EngineOptions:
     num_slabs: int = 0  # pages per cache group; 0 = enough for max_requests full sequences
     max_batch_tokens: int = 1024
     max_batch_reqs: int = 0  # 0 = min(256, max_requests)
+    chunk_size: int = 0  # most rows of a prompt portion that does not finish its prompt; 0 = the token budget decides
     reserve_ratio: float = 0.0
     order: str = "running_first"
     capture: bool | None = None  # CUDA graphs for decode-only steps; None = on for bfloat16
@@ -51,6 +52,12 @@ class EngineOptions:
         reqs = self.max_batch_reqs or min(256, self.max_requests)
         if not 1 <= reqs <= MAX_BUDGET:
             raise ConfigError(f"max_batch_reqs must be in [1, {MAX_BUDGET}], got {reqs}")
+        if not 0 <= self.chunk_size <= self.max_batch_tokens:
+            raise ConfigError(f"chunk_size must be 0 or in [1, max_batch_tokens = {self.max_batch_tokens}], got {self.chunk_size}")
+        if (self.chunk_size or self.max_batch_tokens) < self.block_size:
+            raise ConfigError(
+                f"max_batch_tokens and chunk_size must be at least block_size ({self.block_size}): a portion that does "
+                f"not finish its prompt ends on a page boundary, so a smaller budget could never run a longer prompt")
         if not 0.0 <= self.reserve_ratio <= 1.0:
             raise ConfigError(f"reserve_ratio must be in [0, 1], got {self.reserve_ratio}")
         pages_per_seq = -(-max_seq // self.block_size)
@@ -61,6 +68,6 @@ class EngineOptions:
         return EngineOptions(
             dtype=self.dtype, max_requests=self.max_requests, max_seq_len=max_seq,
             block_size=self.block_size, num_slabs=slabs, max_batch_tokens=self.max_batch_tokens,
-            max_batch_reqs=reqs, reserve_ratio=self.reserve_ratio, order=self.order,
+            max_batch_reqs=reqs, chunk_size=self.chunk_size, reserve_ratio=self.reserve_ratio, order=self.order,
             capture=capture, seed=self.seed,
         )

@@ -15,6 +15,7 @@ static_assert(sizeof(R2GroupSpec) == sizeof(r2::GroupSpec), "group spec layouts 
 static_assert(sizeof(R2SchedulerConfig) == sizeof(r2::SchedulerConfig), "config layouts must agree");
 static_assert(sizeof(R2Stall) == sizeof(r2::Stall), "stall layouts must agree");
 static_assert(sizeof(R2StepEvent) == sizeof(r2::StepEvent), "event layouts must agree");
+static_assert(sizeof(R2RequestEvent) == sizeof(r2::RequestEvent), "request event layouts must agree");
 
 static bool groups_ok(const R2GroupSpec* groups, int32_t n_groups, int32_t max_requests, int32_t max_seq_len) {
   if (groups == nullptr || n_groups < 1) { g_error = "at least one cache group is needed"; return false; }
@@ -46,6 +47,7 @@ int32_t r2_sizeof(int32_t which) {
     case 3: return sizeof(R2Stall);
     case 4: return sizeof(R2StepEvent);
     case 5: return sizeof(R2StepBatch);
+    case 6: return sizeof(R2RequestEvent);
     default: return -1;
   }
 }
@@ -122,9 +124,20 @@ void* r2_sched_create(const R2SchedulerConfig* cfg, const R2GroupSpec* groups, i
   if (!(cfg->reserve_ratio >= 0.f && cfg->reserve_ratio <= 1.f)) { g_error = "reserve_ratio must be in [0, 1]"; return nullptr; }
   if (cfg->vocab_size < 1) { g_error = "vocab_size must be >= 1"; return nullptr; }
   if (cfg->eos_token < -1 || cfg->eos_token >= cfg->vocab_size) { g_error = "eos_token must be -1 or a token id"; return nullptr; }
+  if (cfg->chunk_size < 0 || cfg->chunk_size > cfg->max_batch_tokens) { g_error = "chunk_size must be 0 or in [1, max_batch_tokens]"; return nullptr; }
   r2::SchedulerConfig c{cfg->max_requests, cfg->max_seq_len, cfg->max_batch_tokens, cfg->max_batch_reqs,
-                        cfg->order, cfg->reserve_ratio, cfg->eos_token, cfg->vocab_size};
-  return new Scheduler(c, to_groups(groups, n_groups));
+                        cfg->order, cfg->reserve_ratio, cfg->eos_token, cfg->vocab_size, cfg->chunk_size};
+  Scheduler* s = new Scheduler(c, to_groups(groups, n_groups));
+  // A portion that does not finish a history ends on a page boundary of every group; a budget below
+  // that grain could never run a prompt longer than itself.
+  int32_t least = cfg->chunk_size > 0 ? cfg->chunk_size : cfg->max_batch_tokens;
+  if (least < s->grain()) {
+    g_error = "max_batch_tokens and chunk_size must be at least " + std::to_string(s->grain()) +
+              " (a portion ends on a page boundary of every cache group)";
+    delete s;
+    return nullptr;
+  }
+  return s;
 }
 
 void r2_sched_destroy(void* sched) { delete static_cast<Scheduler*>(sched); }
@@ -189,12 +202,21 @@ int32_t r2_sched_request_info(const void* sched, int32_t id, int32_t* state, int
   *n_preempted = r->n_preempted;
   return 0;
 }
+int32_t r2_sched_request_event(const void* sched, int32_t id, R2RequestEvent* out) {
+  static_assert(sizeof(R2RequestEvent) == sizeof(r2::RequestEvent), "layout");
+  return CSC(sched)->request_event(id, reinterpret_cast<r2::RequestEvent*>(out));
+}
+int32_t r2_sched_drain_request_events(void* sched, R2RequestEvent* out, int32_t cap) {
+  return SC(sched)->drain_request_events(reinterpret_cast<r2::RequestEvent*>(out), cap);
+}
+int32_t r2_sched_grain(const void* sched) { return CSC(sched)->grain(); }
 int32_t r2_sched_set(void* sched, int32_t knob, double value) {
   switch (knob) {
     case 0: return SC(sched)->set_max_batch_tokens(int32_t(value));
     case 1: return SC(sched)->set_max_batch_reqs(int32_t(value));
     case 2: return SC(sched)->set_order(int32_t(value));
     case 3: return SC(sched)->set_reserve_ratio(float(value));
+    case 4: return SC(sched)->set_chunk_size(int32_t(value));
     default: return r2::SCHED_BAD_ARGS;
   }
 }

@@ -74,10 +74,11 @@ int32_t CacheManager::pages_to_take(int32_t req, int32_t g, int32_t n_computed, 
   return need;
 }
 
-bool CacheManager::can_reserve(int32_t req, int32_t n_computed, int32_t n_total, int32_t spare_pages) const {
+bool CacheManager::can_reserve(int32_t req, int32_t n_computed, int32_t n_total, int32_t spare_tokens) const {
   if (!is_open(req) || n_total > max_seq_len_ || n_computed < 0 || n_total < n_computed) return false;
   for (int32_t g = 0; g < n_groups(); ++g) {
-    if (pages_to_take(req, g, n_computed, n_total) + spare_pages > pools_[g].n_free()) return false;
+    int32_t spare = ceil_div(std::max(0, spare_tokens), groups_[g].page_size);
+    if (pages_to_take(req, g, n_computed, n_total) + spare > pools_[g].n_free()) return false;
   }
   return true;
 }

@@ -70,7 +70,8 @@ class CacheManager {
   // Pages that group g must take so that the request holds positions up to n_total (exclusive),
   // given that its next row is at n_computed.
   int32_t pages_to_take(int32_t req, int32_t g, int32_t n_computed, int32_t n_total) const;
-  bool can_reserve(int32_t req, int32_t n_computed, int32_t n_total, int32_t spare_pages) const;
+  // `spare_tokens` more positions' worth of pages must stay free in every group besides.
+  bool can_reserve(int32_t req, int32_t n_computed, int32_t n_total, int32_t spare_tokens) const;
   // All groups or nothing.
   int32_t reserve(int32_t req, int32_t n_computed, int32_t n_total);
   // Window groups give back the pages that no later row can read.

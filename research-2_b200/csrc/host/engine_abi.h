@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define R2_ABI_VERSION 2
+#define R2_ABI_VERSION 3
 
 typedef struct {
   int32_t page_size;
@@ -30,6 +30,7 @@ typedef struct {
   float reserve_ratio;
   int32_t eos_token;
   int32_t vocab_size;
+  int32_t chunk_size; /* 0: none; else the most rows of a portion that does not finish its history */
 } R2SchedulerConfig;
 
 /* Pointers into arrays that the scheduler owns; valid until the next r2_sched_plan. */
@@ -78,9 +79,18 @@ typedef struct {
   int32_t stalled;
   int32_t req_id;
   int32_t n_work;
-  int32_t need_pages;
+  int32_t need_pages; /* of the group that is shortest of pages */
   int32_t free_pages;
+  int32_t group;
 } R2Stall;
+
+/* One request's life; times in nanoseconds of a monotonic clock, 0 = not yet. */
+typedef struct {
+  int64_t t_arrival_ns, t_first_sched_ns, t_first_token_ns, t_last_token_ns, t_finish_ns;
+  int64_t first_step, last_step;
+  int32_t request_id, n_prompt, n_generated, max_new;
+  int32_t n_preempted, n_chunks, state, peak_pages;
+} R2RequestEvent;
 
 typedef struct {
   int64_t step;
@@ -91,7 +101,7 @@ typedef struct {
 } R2StepEvent;
 
 int32_t r2_abi_version(void);
-int32_t r2_sizeof(int32_t which); /* 0 group spec, 1 scheduler config, 2 plan, 3 stall, 4 step event */
+int32_t r2_sizeof(int32_t which); /* 0 group spec, 1 scheduler config, 2 plan, 3 stall, 4 step event, 5 step batch, 6 request event */
 const char* r2_last_error(void);
 
 /* ---- cache manager ---- */
@@ -135,7 +145,12 @@ int32_t r2_sched_event(const void* sched, R2StepEvent* out);
 int32_t r2_sched_counts(const void* sched, int32_t* n_running, int32_t* n_waiting);
 int32_t r2_sched_request_info(const void* sched, int32_t id, int32_t* state, int32_t* n_prompt, int32_t* n_tokens,
                               int32_t* n_computed, int32_t* n_preempted);
-int32_t r2_sched_set(void* sched, int32_t knob, double value); /* 0 tokens, 1 reqs, 2 order, 3 reserve */
+/* The record of a request that is queued, running, or finished and not yet polled to its end. */
+int32_t r2_sched_request_event(const void* sched, int32_t id, R2RequestEvent* out);
+/* Records of requests whose slots were released since the last call, oldest first; returns the count copied. */
+int32_t r2_sched_drain_request_events(void* sched, R2RequestEvent* out, int32_t cap);
+int32_t r2_sched_grain(const void* sched);
+int32_t r2_sched_set(void* sched, int32_t knob, double value); /* 0 tokens, 1 reqs, 2 order, 3 reserve, 4 chunk size */
 
 #ifdef __cplusplus
 }

@@ -13,6 +13,7 @@ static int64_t now_ns() {
 }
 
 static inline int32_t ceil_div(int32_t a, int32_t b) { return (a + b - 1) / b; }
+static int32_t gcd(int32_t a, int32_t b) { return b == 0 ? a : gcd(b, a % b); }
 
 void Plan::clear() {
   req.clear(); start.clear(); rows.clear(); emits.clear(); kind.clear();
@@ -25,6 +26,44 @@ Scheduler::Scheduler(const SchedulerConfig& cfg, std::vector<GroupSpec> groups)
     : cfg_(cfg), create_max_batch_tokens_(cfg.max_batch_tokens), create_max_batch_reqs_(cfg.max_batch_reqs),
       cache_(std::move(groups), cfg.max_requests, cfg.max_seq_len), reqs_(size_t(cfg.max_requests)) {
   for (int32_t i = 0; i < cfg.max_requests; ++i) reqs_[i].id = i;
+  for (int32_t g = 0; g < cache_.n_groups(); ++g) {
+    int32_t ps = cache_.group(g).page_size;
+    grain_ = grain_ / gcd(grain_, ps) * ps;
+  }
+}
+
+int32_t Scheduler::min_free() const {
+  int32_t least = cache_.n_free(0);
+  for (int32_t g = 1; g < cache_.n_groups(); ++g) least = std::min(least, cache_.n_free(g));
+  return least;
+}
+
+void Scheduler::note_pages(Request& r) {
+  int32_t held = 0;
+  for (int32_t g = 0; g < cache_.n_groups(); ++g) held += cache_.pages_held(r.id, g);
+  r.peak_pages = std::max(r.peak_pages, held);
+}
+
+int32_t Scheduler::request_event(int32_t id, RequestEvent* out) const {
+  const Request* r = request(id);
+  if (r == nullptr) return SCHED_BAD_ID;
+  *out = RequestEvent();
+  out->t_arrival_ns = r->t_arrival_ns;
+  out->t_first_sched_ns = r->t_first_sched_ns;
+  out->t_first_token_ns = r->t_first_token_ns;
+  out->t_last_token_ns = r->t_last_token_ns;
+  out->t_finish_ns = r->t_finish_ns;
+  out->first_step = r->first_step;
+  out->last_step = r->last_step;
+  out->request_id = r->id;
+  out->n_prompt = r->n_prompt;
+  out->n_generated = r->n_generated();
+  out->max_new = r->max_new;
+  out->n_preempted = r->n_preempted;
+  out->n_chunks = r->n_chunks;
+  out->state = r->state;
+  out->peak_pages = r->peak_pages;
+  return SCHED_OK;
 }
 
 const Request* Scheduler::request(int32_t id) const {
@@ -43,7 +82,11 @@ int32_t Scheduler::submit(const int32_t* prompt, int32_t n, int32_t max_new, flo
   const int32_t n_new = std::max(1, max_new);  // max_new_tokens 0 still yields one token
   if (int64_t(n) + n_new > cfg_.max_seq_len) return SCHED_TOO_LONG;
   for (int32_t g = 0; g < cache_.n_groups(); ++g) {
-    if (cache_.worst_pages(g, n + n_new - 1, cfg_.max_batch_tokens, grain()) > cache_.group(g).num_pages) {
+    // the largest portion under the knobs as they stand; one that is raised after this check can lead a
+    // window group into a stall, which plan() then reports (kelpie-core/src/scheduler.zig:1040-1044)
+    int32_t most = cfg_.max_batch_tokens;
+    if (cfg_.chunk_size > 0) most = std::min(most, cfg_.chunk_size);
+    if (cache_.worst_pages(g, n + n_new - 1, most, grain()) > cache_.group(g).num_pages) {
       return SCHED_EXCEEDS_KV_POOL;
     }
   }
@@ -71,6 +114,10 @@ int32_t Scheduler::submit(const int32_t* prompt, int32_t n, int32_t max_new, flo
   r.n_polled = 0;
   r.n_preempted = 0;
   r.n_chunks = 0;
+  r.peak_pages = 0;
+  r.t_arrival_ns = now_ns();
+  r.t_first_sched_ns = r.t_first_token_ns = r.t_last_token_ns = r.t_finish_ns = 0;
+  r.first_step = r.last_step = 0;
   r.in_plan = false;
   r.cancel_pending = false;
   r.state = REQ_WAITING;
@@ -78,7 +125,25 @@ int32_t Scheduler::submit(const int32_t* prompt, int32_t n, int32_t max_new, flo
   return r.id;
 }
 
+int32_t Scheduler::drain_request_events(RequestEvent* out, int32_t cap) {
+  int32_t n = 0;
+  while (n < cap && !done_events_.empty()) {
+    out[n++] = done_events_.front();
+    done_events_.pop_front();
+  }
+  return n;
+}
+
 void Scheduler::release_slot(Request& r) {
+  RequestEvent e;
+  if (request_event(r.id, &e) == SCHED_OK) {
+    if (e.t_finish_ns == 0) {  // cancelled: it ends now
+      e.t_finish_ns = now_ns();
+      e.state = REQ_CANCELLED;
+    }
+    if (done_events_.size() >= 4096) done_events_.pop_front();
+    done_events_.push_back(e);
+  }
   r.state = REQ_FREE;
   r.tokens.clear();
   r.in_plan = false;
@@ -113,6 +178,7 @@ int32_t Scheduler::cancel(int32_t id) {
 int32_t Scheduler::chunk_for(const Request& r, int32_t budget) const {
   int32_t remaining = int32_t(r.tokens.size()) - r.n_computed;
   int32_t n_work = std::min(remaining, budget);
+  if (cfg_.chunk_size > 0 && remaining > 1) n_work = std::min(n_work, cfg_.chunk_size);
   if (n_work < remaining) {  // does not finish the history: end on a page boundary
     int32_t g = grain();
     int32_t end = (r.n_computed + n_work) / g * g;
@@ -123,8 +189,7 @@ int32_t Scheduler::chunk_for(const Request& r, int32_t budget) const {
 
 int32_t Scheduler::reserve_pages(const Request& r) const {
   if (cfg_.reserve_ratio <= 0.f) return 0;
-  int32_t tokens = int32_t(std::ceil(double(cfg_.reserve_ratio) * std::max(1, r.max_new)));
-  return ceil_div(tokens, grain());
+  return int32_t(std::ceil(double(cfg_.reserve_ratio) * std::max(1, r.max_new)));  // in tokens; pages group by group
 }
 
 void Scheduler::schedule(Request& r, int32_t n_work) {
@@ -139,6 +204,12 @@ void Scheduler::schedule(Request& r, int32_t n_work) {
   sched_.push_back(e);
   r.in_plan = true;
   r.n_chunks += 1;
+  r.last_step = step_;
+  if (r.t_first_sched_ns == 0) {
+    r.t_first_sched_ns = now_ns();
+    r.first_step = step_;
+  }
+  note_pages(r);
 }
 
 void Scheduler::preempt(int32_t id) {
@@ -188,7 +259,7 @@ void Scheduler::plan_waiting(int32_t& budget) {
     int32_t n_work = chunk_for(r, budget);
     // The reserve keeps room for the runners' decoding; with nobody running there is no one
     // to keep it for, and submit has checked that the request fits alone.
-    int32_t reserve = running_.empty() ? 0 : reserve_pages(r);
+    int32_t reserve = running_.empty() ? 0 : reserve_pages(r);  // tokens
     cache_.open(r.id);
     if (n_work == 0 || !cache_.can_reserve(r.id, 0, n_work, reserve)) {
       cache_.close(r.id);
@@ -236,10 +307,21 @@ void Scheduler::detect_stall(bool preempted) {
   stall_.stalled = 1;
   stall_.req_id = id;
   stall_.n_work = chunk_for(r, cfg_.max_batch_tokens);
-  int32_t need = ceil_div(r.n_computed + stall_.n_work, grain());
-  if (cache_.is_open(id)) need = cache_.pages_to_take(id, 0, r.n_computed, r.n_computed + stall_.n_work);
-  stall_.need_pages = stall_.n_work == 0 ? 0 : need;
-  stall_.free_pages = cache_.n_free(0);
+  // the group that is shortest of pages for this portion
+  int32_t worst = 0, worst_gap = 0;
+  for (int32_t g = 0; g < cache_.n_groups(); ++g) {
+    int32_t need = ceil_div(r.n_computed + stall_.n_work, cache_.group(g).page_size) - cache_.first_needed_page(g, r.n_computed);
+    if (cache_.is_open(id)) need = cache_.pages_to_take(id, g, r.n_computed, r.n_computed + stall_.n_work);
+    if (stall_.n_work == 0) need = 0;
+    int32_t gap = need - cache_.n_free(g);
+    if (g == 0 || gap > worst_gap) {
+      worst = g;
+      worst_gap = gap;
+      stall_.need_pages = need;
+    }
+  }
+  stall_.group = worst;
+  stall_.free_pages = cache_.n_free(worst);
 }
 
 int32_t Scheduler::plan() {
@@ -266,7 +348,7 @@ int32_t Scheduler::plan() {
   event_.n_tokens = plan_.n_tokens;
   event_.n_running = n_running();
   event_.n_waiting = n_waiting();
-  event_.kv_free = cache_.n_free(0);
+  event_.kv_free = min_free();
   event_.t_plan_ns = now_ns() - t0;
   outstanding_ = true;
   return SCHED_OK;
@@ -276,6 +358,7 @@ void Scheduler::finish(Request& r, int32_t state) {
   cache_.close(r.id);
   running_.erase(std::find(running_.begin(), running_.end(), r.id));
   r.state = state;
+  r.t_finish_ns = now_ns();
   event_.n_finished += 1;
 }
 
@@ -299,6 +382,8 @@ int32_t Scheduler::commit(const int32_t* tokens, int32_t n) {
     if (!plan_.emits[i]) continue;  // a portion inside the history: its token is dropped
     int32_t token = tokens[i];
     r.tokens.push_back(token);
+    r.t_last_token_ns = t0;
+    if (r.t_first_token_ns == 0) r.t_first_token_ns = t0;
     bool stop = token == cfg_.eos_token && cfg_.eos_token >= 0;
     for (int32_t s = 0; s < r.n_stops; ++s) stop = stop || token == r.stops[s];
     if (stop) {
@@ -310,7 +395,7 @@ int32_t Scheduler::commit(const int32_t* tokens, int32_t n) {
   outstanding_ = false;
   event_.n_running = n_running();
   event_.n_waiting = n_waiting();
-  event_.kv_free = cache_.n_free(0);
+  event_.kv_free = min_free();
   event_.t_commit_ns = now_ns() - t0;
   return SCHED_OK;
 }
@@ -332,6 +417,12 @@ int32_t Scheduler::poll(int32_t id, int32_t* out, int32_t cap, int32_t* finished
 int32_t Scheduler::set_max_batch_tokens(int32_t v) {
   if (v < 1 || v > create_max_batch_tokens_) return SCHED_BAD_ARGS;
   cfg_.max_batch_tokens = v;
+  return SCHED_OK;
+}
+
+int32_t Scheduler::set_chunk_size(int32_t v) {
+  if (v < 0 || v > create_max_batch_tokens_) return SCHED_BAD_ARGS;
+  cfg_.chunk_size = v;
   return SCHED_OK;
 }
 

@@ -15,6 +15,11 @@
 //                                                                              :785-794,1304-1313
 //   * a plan that schedules nothing, preempts nobody and still has work is a stall :454-467
 //   * only an entry that reaches the end of its history keeps its sampled token :609-626
+//   * `chunk_size` caps a portion that does not finish a history, whatever the token budget
+//     has left (0: the budget alone decides); the reference reaches this only through its
+//     token budget, which also caps the decoded tokens that share the step
+//   * with several cache groups every count of pages is made group by group (each group has a
+//     pool of its own), and portions end on a multiple of every group's page size
 #pragma once
 
 #include <cstdint>
@@ -63,6 +68,7 @@ struct SchedulerConfig {
   float reserve_ratio;
   int32_t eos_token;  // -1: none
   int32_t vocab_size;
+  int32_t chunk_size;  // 0: none; else the most rows of a portion that does not finish its history
 };
 
 struct Request {
@@ -80,6 +86,9 @@ struct Request {
   int32_t n_polled = 0;
   int32_t n_preempted = 0;
   int32_t n_chunks = 0;
+  int32_t peak_pages = 0;  // the most pages it held at one time, summed over groups
+  int64_t t_arrival_ns = 0, t_first_sched_ns = 0, t_first_token_ns = 0, t_last_token_ns = 0, t_finish_ns = 0;
+  int64_t first_step = 0, last_step = 0;
   bool in_plan = false;
   bool cancel_pending = false;
   int32_t n_generated() const { return int32_t(tokens.size()) - n_prompt; }
@@ -89,8 +98,18 @@ struct Stall {
   int32_t stalled = 0;
   int32_t req_id = -1;
   int32_t n_work = 0;
-  int32_t need_pages = 0;
+  int32_t need_pages = 0;  // of the group that is shortest of pages
   int32_t free_pages = 0;
+  int32_t group = 0;
+};
+
+// A request's life in numbers, complete once it has finished or was cancelled; times in
+// nanoseconds of a monotonic clock (kelpie-core/src/events.zig:39-55).
+struct RequestEvent {
+  int64_t t_arrival_ns = 0, t_first_sched_ns = 0, t_first_token_ns = 0, t_last_token_ns = 0, t_finish_ns = 0;
+  int64_t first_step = 0, last_step = 0;
+  int32_t request_id = 0, n_prompt = 0, n_generated = 0, max_new = 0;
+  int32_t n_preempted = 0, n_chunks = 0, state = 0, peak_pages = 0;
 };
 
 struct StepEvent {
@@ -140,11 +159,20 @@ class Scheduler {
   int32_t n_waiting() const { return int32_t(waiting_.size()); }
   bool has_work() const { return !running_.empty() || !waiting_.empty(); }
   const Request* request(int32_t id) const;
+  // SCHED_OK and the record of a request that is queued, running, or finished and not yet polled away.
+  int32_t request_event(int32_t id, RequestEvent* out) const;
+  // Records of requests whose slots have been released (finished and polled to the end, or
+  // cancelled), oldest first; at most the last 4096 are kept. Returns how many were copied out.
+  int32_t drain_request_events(RequestEvent* out, int32_t cap);
 
   int32_t set_max_batch_tokens(int32_t v);
   int32_t set_max_batch_reqs(int32_t v);
   int32_t set_order(int32_t v);
   int32_t set_reserve_ratio(float v);
+  int32_t set_chunk_size(int32_t v);
+  // Portions end on multiples of this: the least common multiple of the groups' page sizes.
+  int32_t grain() const { return grain_; }
+  int32_t min_free() const;  // the free pages of the group that has fewest
 
  private:
   int32_t chunk_for(const Request& r, int32_t budget) const;
@@ -157,11 +185,12 @@ class Scheduler {
   void emit_plan();
   void detect_stall(bool preempted);
   void release_slot(Request& r);
-  int32_t grain() const { return cache_.group(0).page_size; }
+  void note_pages(Request& r);
 
   SchedulerConfig cfg_;
   int32_t create_max_batch_tokens_, create_max_batch_reqs_;
   CacheManager cache_;
+  int32_t grain_ = 1;
   std::vector<Request> reqs_;
   std::vector<int32_t> running_;
   std::deque<int32_t> waiting_;
@@ -170,6 +199,7 @@ class Scheduler {
   bool outstanding_ = false;
   Stall stall_;
   StepEvent event_;
+  std::deque<RequestEvent> done_events_;
   int64_t step_ = 0;
   size_t rr_ = 0;
 };

@@ -13,7 +13,7 @@ from .engine import Engine
 def run(model, *, device: str = "cuda:0", dtype: str = "bfloat16", **options) -> Engine:
     """`model` is a model folder (config.json + model.safetensors) or an already loaded model.
     Keyword options are EngineOptions fields (max_requests, num_slabs, block_size,
-    max_batch_tokens, max_batch_reqs, max_seq_len, reserve_ratio, order, capture, seed)."""
+    max_batch_tokens, max_batch_reqs, chunk_size, max_seq_len, reserve_ratio, order, capture, seed)."""
     opts = EngineOptions(dtype=dtype, **options)
     if isinstance(model, (str, bytes)) or hasattr(model, "__fspath__"):
         model = load_model(model, dtype=dtype, device=device)

@@ -15,7 +15,7 @@ import time
 import numpy as np
 
 from ..config.engine_options import EngineOptions
-from .scheduler import Plan, Poll, Scheduler, SchedulerConfig, StepEvent
+from .scheduler import Plan, Poll, RequestEvent, Scheduler, SchedulerConfig, StepEvent  # noqa: F401
 
 
 class Engine:
@@ -40,7 +40,7 @@ class Engine:
             SchedulerConfig(
                 max_requests=opts.max_requests, max_seq_len=opts.max_seq_len, max_batch_tokens=opts.max_batch_tokens,
                 max_batch_reqs=opts.max_batch_reqs, vocab_size=model.vocab_size, eos_token=model.eos_token,
-                order=opts.order, reserve_ratio=opts.reserve_ratio),
+                order=opts.order, reserve_ratio=opts.reserve_ratio, chunk_size=opts.chunk_size),
             step_fn.cache_groups())
         engine = cls(step_fn, Sampler(model.rt.device), scheduler, seed=opts.seed)
         engine.options = opts
@@ -141,6 +141,11 @@ class Engine:
         if self.keep_events:
             self.events.append(event)
         return event
+
+    def request_events(self):
+        """Per-request records (arrival, first token, finish, portions, preemptions, peak pages) of the
+        requests that ended since the last call (kelpie-core/src/events.zig:39-55)."""
+        return self.scheduler.finished_request_events()
 
     def has_work(self) -> bool:
         return self._launched is not None or self.scheduler.has_work()

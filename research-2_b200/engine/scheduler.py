@@ -36,12 +36,12 @@ class ExceedsKvPool(ValueError):
 class Stalled(RuntimeError):
     """A plan scheduled nothing, preempted nobody, and work is pending."""
 
-    def __init__(self, req_id: int, n_work: int, need_pages: int, free_pages: int):
+    def __init__(self, req_id: int, n_work: int, need_pages: int, free_pages: int, group: int = 0):
         super().__init__(
-            f"stalled: request {req_id} needs {need_pages} pages for its next {n_work} tokens, "
+            f"stalled: request {req_id} needs {need_pages} pages of cache group {group} for its next {n_work} tokens, "
             f"{free_pages} are free and nothing else can make progress"
         )
-        self.req_id, self.n_work, self.need_pages, self.free_pages = req_id, n_work, need_pages, free_pages
+        self.req_id, self.n_work, self.need_pages, self.free_pages, self.group = req_id, n_work, need_pages, free_pages, group
 
 
 class CommitError(RuntimeError):
@@ -58,6 +58,7 @@ class SchedulerConfig:
     eos_token: int | None = None
     order: str = "running_first"
     reserve_ratio: float = 0.0
+    chunk_size: int = 0  # 0 = the token budget alone cuts prompts; else the most rows of a portion inside a history
 
 
 class Plan:
@@ -101,6 +102,32 @@ class Poll:
     new_tokens: list[int]
     finished: bool
     reason: str  # the request's state: running, waiting, finished_eos, finished_length
+
+
+@dataclass(frozen=True)
+class RequestEvent:
+    """One request's life in numbers (kelpie-core/src/events.zig:39-55); times are nanoseconds of a
+    monotonic clock and 0 while the moment has not come."""
+
+    t_arrival_ns: int
+    t_first_sched_ns: int
+    t_first_token_ns: int
+    t_last_token_ns: int
+    t_finish_ns: int
+    first_step: int
+    last_step: int
+    request_id: int
+    n_prompt: int
+    n_generated: int
+    max_new: int
+    n_preempted: int
+    n_chunks: int
+    state: str
+    peak_pages: int
+
+    @property
+    def time_to_first_token_ms(self) -> float | None:
+        return (self.t_first_token_ns - self.t_arrival_ns) / 1e6 if self.t_first_token_ns else None
 
 
 @dataclass(frozen=True)
@@ -153,7 +180,7 @@ class Scheduler:
         c = _host.SchedulerConfigC(
             config.max_requests, config.max_seq_len, config.max_batch_tokens, config.max_batch_reqs,
             ORDERS[config.order], config.reserve_ratio,
-            -1 if config.eos_token is None else config.eos_token, config.vocab_size,
+            -1 if config.eos_token is None else config.eos_token, config.vocab_size, config.chunk_size,
         )
         handle = self._lib.r2_sched_create(C.byref(c), group_array(self.groups), len(self.groups))
         if not handle:
@@ -237,6 +264,35 @@ class Scheduler:
         return {"state": STATE_NAMES[state], "n_prompt": n_prompt, "n_tokens": n_tokens,
                 "n_computed": n_computed, "n_preempted": n_preempted}
 
+    def request_event(self, rid: int) -> RequestEvent:
+        """The request's record so far; complete once it has finished. It goes away with the
+        request's slot, that is with the poll that reports `finished`: read it before that poll."""
+        e = _host.RequestEventC()
+        if self._lib.r2_sched_request_event(self._h, rid, C.byref(e)) != 0:
+            raise KeyError(f"no request {rid}")
+        values = {name: getattr(e, name) for name, _ in _host.RequestEventC._fields_}
+        values["state"] = STATE_NAMES[values["state"]]
+        return RequestEvent(**values)
+
+    def finished_request_events(self) -> list[RequestEvent]:
+        """Records of the requests whose slots were released since the last call (finished and polled
+        to the end, or cancelled), oldest first."""
+        buf = (_host.RequestEventC * 64)()
+        out = []
+        while True:
+            n = self._lib.r2_sched_drain_request_events(self._h, buf, 64)
+            for e in buf[:n]:
+                values = {name: getattr(e, name) for name, _ in _host.RequestEventC._fields_}
+                values["state"] = STATE_NAMES[values["state"]]
+                out.append(RequestEvent(**values))
+            if n < 64:
+                return out
+
+    @property
+    def grain(self) -> int:
+        """Portions that do not finish a history end on multiples of this (every group's page size divides it)."""
+        return self._lib.r2_sched_grain(self._h)
+
     # ---- steps -----------------------------------------------------------------------------
     def plan(self) -> Plan:
         """The next step's entries (possibly none). Raises Stalled when nothing can run."""
@@ -249,7 +305,7 @@ class Scheduler:
             stall = _host.StallC()
             if self._lib.r2_sched_stall(self._h, C.byref(stall)):
                 self._lib.r2_sched_commit(self._h, None, 0)  # the empty plan is closed so that the caller can go on
-                raise Stalled(stall.req_id, stall.n_work, stall.need_pages, stall.free_pages)
+                raise Stalled(stall.req_id, stall.n_work, stall.need_pages, stall.free_pages, stall.group)
         return plan
 
     def fill(self, batch) -> None:
@@ -288,7 +344,7 @@ class Scheduler:
 
     def set(self, **knobs) -> None:  # noqa: A003
         """Live knobs, applied at the next plan (kelpie-core/src/scheduler.zig:36-52)."""
-        ids = {"max_batch_tokens": 0, "max_batch_reqs": 1, "order": 2, "reserve_ratio": 3}
+        ids = {"max_batch_tokens": 0, "max_batch_reqs": 1, "order": 2, "reserve_ratio": 3, "chunk_size": 4}
         for name, value in knobs.items():
             if name not in ids:
                 raise KeyError(f"unknown knob {name!r}; known: {sorted(ids)}")

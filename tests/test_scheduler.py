@@ -57,15 +57,18 @@ class TraceRunner:
 
     def do_config(self, rest: str) -> None:
         kv = _kv(rest)
-        groups = kv.get("groups", "all")
-        window = int(groups[len("window"):]) if groups.startswith("window") else 0
+        # groups=all | window8 | all+window8 (one cache group each); num_blocks=6 or 6,2 (per group)
+        windows = [int(g[len("window"):]) if g.startswith("window") else 0 for g in kv.get("groups", "all").split("+")]
+        blocks = [int(b) for b in kv["num_blocks"].split(",")]
+        blocks = blocks * len(windows) if len(blocks) == 1 else blocks
         eos = int(kv.get("eos", -1))
         cfg = SchedulerConfig(
             max_requests=int(kv.get("max_requests", 8)), max_seq_len=int(kv.get("max_seq_len", 64)),
             max_batch_tokens=int(kv["max_batch_tokens"]), max_batch_reqs=int(kv["max_batch_reqs"]),
             vocab_size=10000, eos_token=None if eos < 0 else eos, order=kv.get("order", "running_first"),
-            reserve_ratio=float(kv.get("reserve_ratio", 0)))
-        self.sched = Scheduler(cfg, [GroupSpec(int(kv["block_size"]), window, int(kv["num_blocks"]))])
+            reserve_ratio=float(kv.get("reserve_ratio", 0)), chunk_size=int(kv.get("chunk_size", 0)))
+        self.sched = Scheduler(cfg, [GroupSpec(int(kv["block_size"]), w, n) for w, n in zip(windows, blocks)])
+        self.ids, self.polled, self.final = {}, {}, {}
 
     def _submit(self, rest: str) -> int:
         name, _, opts = rest.partition(" ")
@@ -125,8 +128,14 @@ class TraceRunner:
         elif what == "kinds":
             got = self.last_kinds
             assert got == arg.split(), f"kinds are {' '.join(got)}"
-        elif what == "free":
-            assert self.sched.cache.n_free(0) == int(arg), f"free is {self.sched.cache.n_free(0)}"
+        elif what in ("free", "free1"):
+            g = 1 if what == "free1" else 0
+            assert self.sched.cache.n_free(g) == int(arg), f"{what} is {self.sched.cache.n_free(g)}"
+        elif what == "request":
+            name, _, opts = arg.partition(" ")
+            event = self.sched.request_event(self.ids[name])
+            for k, v in _kv(opts).items():
+                assert str(getattr(event, k)) == v, f"request {name}: {k} is {getattr(event, k)}"
         elif what in ("running", "waiting"):
             got = sorted(n for n, rid in self.ids.items() if self.sched.request_info(rid)["state"] == what)
             assert got == sorted(arg.split()), f"{what} is {got}"
@@ -146,8 +155,8 @@ class TraceRunner:
                 kv = _kv(opts)
                 s = self.stall
                 assert s is not None, "no stall was reported"
-                got = (self.name_of(s.req_id), s.n_work, s.need_pages, s.free_pages)
-                assert got == (name, int(kv["n_work"]), int(kv["need"]), int(kv["free"])), f"stall is {got}"
+                got = (self.name_of(s.req_id), s.n_work, s.need_pages, s.free_pages, s.group)
+                assert got == (name, int(kv["n_work"]), int(kv["need"]), int(kv["free"]), int(kv.get("group", 0))), f"stall is {got}"
         elif what == "event":
             event = self.sched.event()
             for k, v in _kv(arg).items():
@@ -337,3 +346,34 @@ def test_random_caller_against_the_token_oracle(seed):
             if sched.poll(rid).finished:
                 del histories[rid]
     assert sched.cache.n_free(0) == groups[0].num_pages
+
+
+def test_budget_below_a_page_is_refused_at_creation():
+    with pytest.raises(ValueError, match="at least 8"):
+        Scheduler(SchedulerConfig(4, 64, 4, 4, 100), [GroupSpec(8, 0, 8)])
+    with pytest.raises(ValueError, match="at least 8"):
+        Scheduler(SchedulerConfig(4, 64, 16, 4, 100, chunk_size=4), [GroupSpec(8, 0, 8)])
+    with pytest.raises(ValueError, match="at least 24"):  # two groups: a portion ends on a page boundary of both
+        Scheduler(SchedulerConfig(4, 64, 16, 4, 100), [GroupSpec(8, 0, 8), GroupSpec(12, 4, 8)])
+    assert Scheduler(SchedulerConfig(4, 64, 24, 4, 100), [GroupSpec(8, 0, 8), GroupSpec(12, 4, 8)]).grain == 24
+
+
+def test_request_events_outlive_their_slots():
+    """Arrival, first token and finish of every request, read after its slot was given back."""
+    s = Scheduler(SchedulerConfig(2, 32, 16, 2, 100), [GroupSpec(4, 0, 8)])
+    a = s.submit([1, 2, 3, 4, 5], 2)
+    b = s.submit([7], 3)
+    s.cancel(b)
+    while s.has_work():
+        plan = s.plan()
+        s.commit([9] * plan.n_entries)
+        during = s.request_event(a) if s.request_info(a)["state"] != "free" else None
+        s.poll(a)
+    assert during is not None and during.n_generated == 2 and during.state == "finished_length"
+    events = s.finished_request_events()
+    assert [e.request_id for e in events] == [b, a] and s.finished_request_events() == []
+    cancelled, done = events
+    assert cancelled.state == "cancelled" and cancelled.t_first_token_ns == 0 and cancelled.time_to_first_token_ms is None
+    assert done.n_prompt == 5 and done.n_generated == 2 and done.n_chunks == 2 and done.peak_pages == 2
+    assert done.t_arrival_ns <= done.t_first_sched_ns <= done.t_first_token_ns <= done.t_last_token_ns <= done.t_finish_ns
+    assert done.first_step == 1 and done.last_step == 2 and done.time_to_first_token_ms >= 0
