@@ -114,6 +114,41 @@ def build_model(n_layer: int, dtype: str = "bfloat16", size: str = "gpt2-124M"):
     return arch.build(cfg, tensors, Runtime(torch.device("cuda:0"), compute_dtype(dtype))), cfg
 
 
+class DeviceLoopGraph:
+    """Forward pass and sampling of a decode-only batch as one CUDA graph WITHOUT the host copies: the
+    device-only loop below writes each step's index arrays into `dev` and feeds the sampled tokens back
+    as the next step's input ids on the device. It is put together here from the step function's public
+    pieces (`forward`, `sample`, a StepContext over a device buffer); the product's own StepGraph, which
+    the end-to-end number runs through, copies the batch in and the tokens out inside the graph."""
+
+    def __init__(self, step_fn, batch: int):
+        import torch
+        from research_2_b200.engine.batch import BatchLayout, StepBatch
+        from research_2_b200.engine.step import StepContext
+        from research_2_b200.kernels import ops
+
+        self.host = StepBatch(BatchLayout(batch, batch, batch, step_fn.table_widths), pinned=True)
+        self.host.max_context_bound = step_fn.model.max_seq_len
+        self.host.pad()
+        self.host.set_logit_rows([])
+        self.host.set_sampling([], [], [], [], [])
+        self.dev = torch.zeros(self.host.buf.shape[0], dtype=torch.int32, device=step_fn.device)
+        self.dev.copy_(self.host._pinned_tensor)
+        ctx = StepContext(self.host, self.dev, counts=(batch, batch, batch))
+        side = torch.cuda.Stream(device=step_fn.device)
+        side.wait_stream(torch.cuda.current_stream(step_fn.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step_fn.sample(step_fn.forward(ctx), ctx)
+        torch.cuda.current_stream(step_fn.device).wait_stream(side)
+        torch.cuda.synchronize(step_fn.device)
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self.graph, pool=step_fn.graph_pool()):
+            self.tokens = step_fn.sample(step_fn.forward(ctx), ctx)
+        self.kernels = ops.launch_count() - before
+
+
 class DecodeLoop:
     """B requests with PROMPT_LEN-token prompts, prefilled through the step function, then
     decoded with the decode graph; the sampled tokens feed the next step on the device."""
@@ -147,10 +182,7 @@ class DecodeLoop:
             self.step_fn(b)
         torch.cuda.synchronize()
         # every decode step's batch, precomputed into one pinned array
-        from research_2_b200.engine.step import StepGraph
-
-        # the decode-only graph (rows == entries) without the host copies inside: this loop feeds it on the device
-        self.graph = StepGraph(self.step_fn, batch, batch, io_inside=False)
+        self.graph = DeviceLoopGraph(self.step_fn, batch)
         host = self.graph.host
         self.skip = host.section("positions")[0]  # input_ids stay on the device
         self.staged = torch.zeros(n_steps, host.buf.shape[0], dtype=torch.int32).pin_memory()
@@ -298,15 +330,6 @@ def mixed_point(model, n_requests: int = 64, new_tokens: int = 256) -> dict:
             "prompt_tokens": n_in, "generated_tokens": n_out, "steps": steps, "ms": dt * 1e3}
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "the offline install of the reference holds only its `observe` package; its engine "
-                       "(kelpie) runs through libkelpie, a Zig library, and no zig toolchain is in the image",
-    }))
-    return 0
-
-
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -318,8 +341,6 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip prefill, e2e and the batch 1 / 64 points")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -328,6 +349,21 @@ def main() -> int:
     if args.layers is None:
         args.layers = SIZES[args.model]["n_layer"]
     steps = min(args.steps, CONTEXT - PROMPT_LEN - args.warmup)
+    if args.impl == "reference":
+        from baseline import reference_arm
+
+        cfg_data = SIZES[args.model]
+        skeleton = {
+            "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, 512-token prompts)", "value": None, "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random weights (seed 5)", "impl": "reference",
+            "config": {"model": args.model, "n_layer": cfg_data["n_layer"], "n_layer_model": cfg_data["n_layer"], "n_embd": cfg_data["n_embd"],
+                       "n_head": cfg_data["n_head"], "head_dim": cfg_data["n_embd"] // cfg_data["n_head"], "n_inner": cfg_data["n_inner"],
+                       "vocab_size": cfg_data["vocab_size"], "n_positions": cfg_data["n_positions"], "global_batch": args.batch,
+                       "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE, "parallelism": "none",
+                       "l2": "inputs larger than L2, no flush"},
+        }
+        return reference_arm.main(args, cfg_data, SEED, PAGE, PROMPT_LEN, CONTEXT, skeleton)
 
     import torch
     from research_2_b200.kernels import ops

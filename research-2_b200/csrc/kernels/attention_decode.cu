@@ -495,8 +495,12 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
 
 template <int G, bool MMA>
 bool configure_smem() {
-  // once per kernel instance: room for the tiles beyond the default 48 KB
-  static bool done = false;
+  // once per kernel instance and device (function attributes belong to a device's context): room for
+  // the tiles beyond the default 48 KB
+  static bool done_on[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return false;
+  bool& done = done_on[device];
   if (!done) {
     if (cudaFuncSetAttribute(decode_kernel<G, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
     // the CTAs hide each other's waits: ask for the shared memory that lets as many as fit be resident
@@ -692,6 +696,13 @@ extern "C" int r2_attention_decode_static(const void* q, int q_row_stride, void*
   }
   // Every (row, head, slice) word of the scratch that the merge reads is written by this call's
   // own slices first (empty slices write zeros and a -inf maximum), so nothing needs clearing.
+  // The kernels of this entry point take plain stream order: the engine's own launches let a kernel
+  // read its index arrays while its predecessor still runs (nothing in the engine writes them on the
+  // device), which a caller who fills them with a kernel of its own must not be exposed to.
+  struct PlainOrder {
+    PlainOrder() { t_r2_plain_order = 1; }
+    ~PlainOrder() { t_r2_plain_order = 0; }
+  } plain_order;
   return r2_attention_decode(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, n_pages,
                              block_tables, table_width, row_entry, positions, seq_lens, n_rows, n_heads, n_kv_heads,
                              scale, window, n_slices, scratch, (long long)R2_STATIC_SCRATCH_FLOATS, stream);

@@ -26,6 +26,14 @@
  *     overlap on the GPU (different streams, or concurrent graph branches) race on it. Keep
  *     calls into this entry point ordered on one stream per device.
  *   - No cudaMalloc, cudaFree or allocating library routine is called, on any path.
+ *   - Row t of `q` is entry t: `seq_lens[t]` is its context length (the new token included),
+ *     `positions[t]` its position, row t of `block_tables` its pages. `row_entry` is not read (pass
+ *     NULL); a batch whose rows are not its entries in order is not what this kernel computes.
+ *   - The kernels of this entry point are launched in plain stream order, so every array may be
+ *     produced by the caller's kernel just before the call in the same stream. (`r2_attention_decode`
+ *     itself is launched with programmatic stream serialization when that is switched on, and reads
+ *     positions, seq_lens and block_tables before it waits for its predecessor: its index arrays must
+ *     be complete before the kernel ahead of it in the stream has started.)
  */
 #pragma once
 

@@ -95,6 +95,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 static int g_r2_pdl = 1;
+// Set by an entry point (on the calling thread, around its launches) whose callers may produce the
+// kernel's index arrays with the kernel just before it in the stream: such launches take plain
+// stream order, so that nothing is read before that predecessor has completed.
+static thread_local int t_r2_plain_order = 0;
 // Every kernel library exports this switch (1 = launch with programmatic stream serialization).
 extern "C" void r2_set_pdl(int on) { g_r2_pdl = on ? 1 : 0; }
 
@@ -109,7 +113,7 @@ static inline void r2_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = g_r2_pdl ? 1 : 0;
+  config.numAttrs = (g_r2_pdl && !t_r2_plain_order) ? 1 : 0;
   cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);  // a failure shows in launch_status()
 }
 

@@ -43,13 +43,29 @@ constexpr int BK = 64;           // one 128-byte swizzle span of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr int MAX_STAGES = 8;
-constexpr int N_SMS = 148;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 #define R2_ERR_TIMEOUT_FULL 1
 #define R2_ERR_TIMEOUT_EMPTY 2
 #define R2_ERR_TIMEOUT_ACC 3
 #define R2_ERR_TIMEOUT_TOKENS 4
+
+// The current device's number of multiprocessors: the plans below spread tiles and K-splits over it.
+static int n_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 1;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 struct GemmParams {
   int a_total, b_total, k_total;  // extents of the a side, the b side and K
@@ -1292,7 +1308,7 @@ int max_resident_clusters(int size) {
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) != cudaSuccess || n < 1) {
       cudaGetLastError();
-      n = N_SMS / size / 2;  // a cautious guess
+      n = n_sms() / size / 2;  // a cautious guess
     }
     cached[size] = n;
   }
@@ -1308,7 +1324,7 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
     pl.bn = ((pl.b_total + 15) / 16) * 16;               // tokens, K-major: any multiple of 16
     // more than 32 tokens and few feature tiles: two token tiles double the CTAs that stream the
     // weights (the second pass over a weight tile comes from L2) and halve the leader's reduce buffer
-    if (pl.b_total > 32 && ((pl.a_total + BM - 1) / BM) * 8 < N_SMS) pl.bn = 32;
+    if (pl.b_total > 32 && ((pl.a_total + BM - 1) / BM) * 8 < n_sms()) pl.bn = 32;
   } else if (w_is_nk) {
     pl.bn = pl.b_total >= 128 ? 128 : ((pl.b_total + 15) / 16) * 16;
   } else {
@@ -1320,8 +1336,8 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   // of a cluster (at most 8) on one tile, each with a share of K; the leader's shared memory
   // must hold the others' partial tiles.
   pl.splits = 1;
-  if (pl.swapped && tiles * 2 <= N_SMS) {
-    int s = N_SMS / tiles;
+  if (pl.swapped && tiles * 2 <= n_sms()) {
+    int s = n_sms() / tiles;
     if (s > 8) s = 8;
     if (s > pl.n_kb) s = pl.n_kb;
     for (; s > 1; --s) {
@@ -1339,7 +1355,7 @@ Plan make_plan(int m, int n, int k, int w_is_nk, bool fused_ln = false) {
   const size_t fixed = 1024 + (2 * MAX_STAGES + 3) * 8 + 32 +
                        (pl.swapped ? size_t(pl.splits - 1) * (pl.bn + 4) * BM * 4 : size_t(BIAS_SLOTS) * 4);  // partial sums, or the bias
   // with more tiles than SMs, leave room for two CTAs on an SM: one's epilogue under the other's loads
-  const size_t budget = (tiles * pl.splits > N_SMS ? 113 * 1024 : 227 * 1024) - fixed;
+  const size_t budget = (tiles * pl.splits > n_sms() ? 113 * 1024 : 227 * 1024) - fixed;
   if (fused_ln) {
     // the normalised token tiles of the CTA's whole K share stay resident; the ring holds weights only
     const size_t tokens = size_t(pl.kb_per_split) * b_stride;
@@ -1389,7 +1405,7 @@ int max_resident_pairs() {
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &config) != cudaSuccess || n < 1) {
       cudaGetLastError();
-      n = N_SMS / 2 - 2;  // a cautious guess
+      n = n_sms() / 2 - 2;  // a cautious guess
     }
     cached = n;
   }
@@ -1406,7 +1422,7 @@ PairPlan make_pair_plan(int m, int n, int k, int w_is_nk, bool always) {
   // set-up and an epilogue that nothing hides; with fewer than about 2.5 single-CTA tiles per SM
   // the single-CTA form (two CTAs to an SM) is the faster one.
   const int single_tiles = ((m + BM - 1) / BM) * ((n + 127) / 128);
-  if (!always && 2 * single_tiles < 5 * N_SMS) return pl;
+  if (!always && 2 * single_tiles < 5 * n_sms()) return pl;
   const int row_pairs = (m + 2 * BM - 1) / (2 * BM);
   const int pairs = max_resident_pairs();
   pl.n_kb = (k + BK - 1) / BK;

@@ -228,6 +228,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
           if (lane >= d) upto += other;
         }
         const uint32_t remaining = sel_remaining;
+        __syncwarp();  // every lane has read the count before the selecting lane overwrites it
         uint32_t above = upto - sum;  // in bins above this lane's
         if (above < remaining && remaining <= upto) {
 #pragma unroll

@@ -19,8 +19,8 @@ from .scheduler import Plan, Poll, RequestEvent, Scheduler, SchedulerConfig, Ste
 
 
 class Engine:
-    def __init__(self, step_fn, sampler, scheduler: Scheduler, seed: int = 0):
-        self.step_fn, self.sampler, self.scheduler = step_fn, sampler, scheduler
+    def __init__(self, step_fn, scheduler: Scheduler, seed: int = 0):
+        self.step_fn, self.scheduler = step_fn, scheduler
         self.seed = seed
         self._ordinal = 0
         self._pending: dict[int, list[int]] = {}
@@ -31,7 +31,6 @@ class Engine:
 
     @classmethod
     def for_model(cls, model, options: EngineOptions | None = None) -> "Engine":
-        from ..sampling.sampler import Sampler
         from .step import StepFunction
 
         opts = (options or EngineOptions()).validated(model.max_seq_len)
@@ -42,7 +41,7 @@ class Engine:
                 max_batch_reqs=opts.max_batch_reqs, vocab_size=model.vocab_size, eos_token=model.eos_token,
                 order=opts.order, reserve_ratio=opts.reserve_ratio, chunk_size=opts.chunk_size),
             step_fn.cache_groups())
-        engine = cls(step_fn, Sampler(model.rt.device), scheduler, seed=opts.seed)
+        engine = cls(step_fn, scheduler, seed=opts.seed)
         engine.options = opts
         engine.model = model
         return engine

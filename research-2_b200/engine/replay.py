@@ -18,27 +18,32 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
+from ..kernels import ops
 from ..models.loading import load_model
 from .step import StepFunction
 
-MAX_LIVE = 4
-ROUND_TO = 64
-
 
 class Replay:
+    """`max_tokens` is the most tokens that live requests hold at any time, each request's count
+    rounded up to a multiple of `round_to`; the pool gets the pages for that many (a request whose
+    rounded count is no multiple of the page size may need one page more, so with such a page
+    size the pool gets one extra page per live request). `capture` runs the steps as CUDA graphs
+    where the step function has one for the shape, as generation does."""
+
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, device: str = "cuda:0",
-                 max_live: int = MAX_LIVE):
+                 max_live: int = 4, round_to: int = 64, capture: bool = False):
         if max_tokens < 1:
             raise ValueError(f"--max-tokens must be >= 1, got {max_tokens}")
-        if ROUND_TO % block_size != 0:
-            raise ValueError(f"the page size must divide {ROUND_TO}, got {block_size}")
+        if block_size < 1 or max_live < 1 or round_to < 1:
+            raise ValueError("block size, live requests and rounding must be >= 1")
         self.model = load_model(model_dir, dtype=dtype, device=device)
-        num_pages = -(-max_tokens // block_size)
-        self.step_fn = StepFunction(self.model, block_size, num_pages, max_live)
+        num_pages = -(-max_tokens // block_size) + (max_live if round_to % block_size else 0)
+        self.step_fn = StepFunction(self.model, block_size, num_pages, max_live, capture=capture, capture_after=0)
         self.cache = CacheManager(self.step_fn.cache_groups(), max_live, self.model.max_seq_len)
         self.slots: dict[str, int] = {}
         self.fed: dict[str, int] = {}
         self.max_live = max_live
+        self.pages_of_last_step: dict[str, list[list[int]]] = {}  # request -> per cache group, the pages it held in the last step
 
     def _slot(self, rid: str) -> int:
         if rid in self.slots:
@@ -54,6 +59,7 @@ class Replay:
         """Run one step; returns the wanted logits [n, vocab] (None when nothing is wanted)."""
         entries = record.get("entries", [])
         reqs, starts, token_lists, wants = [], [], [], []
+        self.pages_of_last_step = {}
         for entry in entries:
             rid, tokens = str(entry["id"]), [int(t) for t in entry["tokens"]]
             if not tokens:
@@ -62,6 +68,7 @@ class Replay:
             start = self.fed[rid]
             self.cache.slide(slot, start)
             self.cache.reserve(slot, start, start + len(tokens))
+            self.pages_of_last_step[rid] = [[int(p) for p in self.cache.table(slot, g) if p] for g in range(len(self.cache.groups))]
             want = [int(w) for w in entry.get("want", [])]
             if any(not 0 <= w < len(tokens) for w in want):
                 raise ValueError(f"request {rid!r}: want {want} lies outside its {len(tokens)} tokens")
@@ -72,7 +79,8 @@ class Replay:
         result = None
         if reqs:
             n_want = sum(len(w) for w in wants)
-            batch = self.step_fn.new_batch(sum(len(t) for t in token_lists), len(reqs), n_want)
+            batch = self.step_fn.new_batch(sum(len(t) for t in token_lists), len(reqs), n_want,
+                                           decode_only=all(len(t) == 1 for t in token_lists))
             batch.set_entries(reqs, starts, token_lists)
             self.cache.fill(batch)
             rows = [int(batch.q_start[e]) + w for e, want in enumerate(wants) for w in want]
@@ -84,6 +92,7 @@ class Replay:
                 result = logits.to(torch.float32).cpu().numpy()
             else:
                 torch.cuda.synchronize(self.step_fn.device)
+            ops.raise_on_device_error(self.step_fn.device)  # a kernel that gave up a bounded wait: the step is void
         for rid in record.get("end", []):
             rid = str(rid)
             if rid in self.slots:
@@ -103,10 +112,14 @@ def main(argv=None) -> int:
                     help="the most tokens that live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--max-live", type=int, default=4, help="the most requests that are live at a time")
+    ap.add_argument("--round-to", type=int, default=64, help="each request's token count is rounded up to a multiple of this")
+    ap.add_argument("--capture", action="store_true", help="run steps as CUDA graphs where generation would")
     args = ap.parse_args(argv)
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    replay = Replay(args.model, args.dtype, args.max_tokens, args.block_size, args.device)
+    replay = Replay(args.model, args.dtype, args.max_tokens, args.block_size, args.device, max_live=args.max_live,
+                    round_to=args.round_to, capture=args.capture)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -91,9 +91,9 @@ class StepGraph:
     begins with the copy of the pinned host batch to the device and ends with the copy of the
     sampled tokens into pinned host memory, so that a step is one graph launch and one wait."""
 
-    def __init__(self, step_fn: "StepFunction", t_cap: int, r_cap: int, io_inside: bool = True):
+    def __init__(self, step_fn: "StepFunction", t_cap: int, r_cap: int):
         self.cap = r_cap
-        self.io_inside = io_inside  # False: the caller fills `dev` and reads `tokens` itself (a device-side loop)
+        self.device = step_fn.device
         self.host = StepBatch(BatchLayout(t_cap, r_cap, r_cap, step_fn.table_widths), pinned=True)
         self.host.max_context_bound = step_fn.model.max_seq_len
         self.host.pad()
@@ -104,6 +104,10 @@ class StepGraph:
         self.ctx = StepContext(self.host, self.dev, counts=(t_cap, r_cap, r_cap))
         self.tokens_host = torch.zeros(r_cap, dtype=torch.int32).pin_memory()
         self.tokens_host_np = self.tokens_host.numpy()
+        # the device's error word travels to the host with the tokens: a kernel's time-out is seen at no extra cost
+        self.error_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.error_host_np = self.error_host.numpy()
+        self.error_word = ops.error_word(self.device)
         self.done = torch.cuda.Event()   # recorded after every replay: the batch is consumed, the tokens are on the host
         side = torch.cuda.Stream(device=step_fn.device)
         side.wait_stream(torch.cuda.current_stream(step_fn.device))
@@ -125,12 +129,11 @@ class StepGraph:
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(self.graph, pool=step_fn.graph_pool()):
-            if self.io_inside:
-                self.dev.copy_(self.host._pinned_tensor, non_blocking=True)
+            self.dev.copy_(self.host._pinned_tensor, non_blocking=True)
             self.logits = step_fn.forward(self.ctx)
             self.tokens = step_fn.sample(self.logits, self.ctx)
-            if self.io_inside:
-                self.tokens_host.copy_(self.tokens, non_blocking=True)
+            self.tokens_host.copy_(self.tokens, non_blocking=True)
+            self.error_host.copy_(self.error_word, non_blocking=True)
         self.kernels = ops.launch_count() - before
 
     def replay(self) -> None:
@@ -140,13 +143,24 @@ class StepGraph:
         ops.count_launches(self.kernels)
 
     def tokens_on_host(self, n: int) -> np.ndarray:
-        """The last replay's first n tokens, once it has finished."""
+        """The last replay's first n tokens, once it has finished. Raises `ops.KernelTimeout` if a
+        kernel of the step recorded that one of its bounded waits ran out."""
         self.done.synchronize()
+        self.check()
         return self.tokens_host_np[:n]
+
+    def check(self) -> None:
+        if self.error_host_np[0]:
+            code, self.error_host_np[0] = int(self.error_host_np[0]), 0
+            ops.raise_on_device_error(self.device, code)
 
 
 class StepFunction:
-    def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False):
+    def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False,
+                 capture_after: int = 1):
+        """`capture`: steps run as CUDA graphs per shape bucket. A decode-only bucket is captured at
+        first use; a bucket with prompt portions once its shape has come `capture_after` times
+        before (0: at first use)."""
         self.model = model
         self.device = model.rt.device
         # the device's number, for the launch path that skips torch's device guard when it is the current one
@@ -163,7 +177,8 @@ class StepFunction:
         # only models whose mixers all say `capturable` may run inside a CUDA graph.
         self.capture = capture and all(getattr(b.mixer, "capturable", False) for b in model.blocks)
         self._graphs: dict[tuple[int, int], StepGraph] = {}
-        self._seen: set[tuple[int, int]] = set()   # shapes with prompt portions that came once
+        self.capture_after = capture_after
+        self._seen: dict[tuple[int, int], int] = {}   # how often a shape with prompt portions has come
         self._pool = None
         self._batches: dict[tuple[int, int, int], StepBatch] = {}
         self.h2d_bytes = 0
@@ -188,10 +203,10 @@ class StepFunction:
         if self.capture and decode_only:
             graph = self._graph(r_cap, r_cap)
         elif self.capture and n_logit_rows <= n_entries and t_cap > r_cap:  # (t_cap == r_cap is the decode-only graph)
-            if (t_cap, r_cap) in self._graphs or (t_cap, r_cap) in self._seen:
+            if (t_cap, r_cap) in self._graphs or self._seen.get((t_cap, r_cap), 0) >= self.capture_after:
                 graph = self._graph(t_cap, r_cap)
             else:
-                self._seen.add((t_cap, r_cap))
+                self._seen[(t_cap, r_cap)] = self._seen.get((t_cap, r_cap), 0) + 1
         if graph is not None:
             batch = graph.host
         else:
@@ -256,7 +271,9 @@ class StepFunction:
         graph = self._graph_of(batch)
         if graph is not None and tokens.data_ptr() == graph.tokens.data_ptr():
             return graph.tokens_on_host(tokens.shape[0])
-        return tokens.cpu().numpy()
+        out = tokens.cpu().numpy()
+        ops.raise_on_device_error(self.device)
+        return out
 
     def sample(self, logits: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         return ops.sample(logits, ctx.temperature, ctx.top_k, ctx.key0, ctx.key1, ctx.sample_pos)
@@ -285,7 +302,7 @@ class StepFunction:
         if not batch.trusted:
             return None
         graph = self._graph_of(batch)
-        if graph is None or not graph.io_inside:
+        if graph is None:
             return None
         if torch.cuda.current_device() != self._device_index:
             with torch.cuda.device(self.device):

@@ -26,6 +26,27 @@ class KernelError(RuntimeError):
     pass
 
 
+class KernelTimeout(KernelError):
+    """A bounded wait inside a kernel ran out: the kernel recorded a code and returned instead of
+    spinning on. What it computed is not to be trusted. `code` is the recorded number."""
+
+    CODES = {
+        1: "a product's operand tile did not arrive (tensor copy)",
+        2: "a product's operand stage was not released (tensor-core commit)",
+        3: "a product's accumulator was not completed",
+        4: "a product's normalised token tile was not built",
+        5: "a key/value tile of prefill attention did not arrive (tensor copy)",
+        6: "a stage of the tensor-core prefill attention did not complete",
+        7: "a step of the resident decode kernel did not reach its grid barrier",
+        99: "a wait that a test let run out",
+    }
+
+    def __init__(self, code: int):
+        super().__init__(f"a kernel gave up a bounded wait (code {code}: {self.CODES.get(code, 'unknown')}); "
+                         f"the step's results are not valid")
+        self.code = code
+
+
 def dtype_code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return F32
@@ -119,38 +140,27 @@ def _lib(source: str) -> C.CDLL:
     return lib
 
 
-def build_all() -> None:
-    """Compile every kernel library (what `__graft_entry__.build()` calls)."""
-    for source in ("rowwise", "gemm_simt", "gemm_tc", "mlp_fused", "attention_simt", "attention_prefill_tc", "sampling"):
+def build_all(head_dims=()) -> None:
+    """Compile every kernel library that does not depend on a model, and the attention kernels
+    for the given head sizes (a model compiles its own head size at first use otherwise)."""
+    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling", "wait_selftest"):
         _lib(source)
-    for head_dim in (16, 32, 64):  # the head sizes of the tiny test models and of GPT-2
+    for head_dim in head_dims:
         _lib_for_head_dim("attention_decode", head_dim)
-        _lib_for_head_dim("attention_prefill", head_dim)
+        if head_dim <= 128:
+            _lib_for_head_dim("attention_prefill", head_dim)
 
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"
 _fast_attention = os.environ.get("R2_ATTENTION", "fast") != "simt"
 _fused_norm = os.environ.get("R2_FUSED_NORM", "1") != "0"
 _fused_decode = os.environ.get("R2_FUSED_DECODE", "1") != "0"
-_weight_prefetch = os.environ.get("R2_WEIGHT_PREFETCH", "0") != "0"  # measured: no gain at batch 8, so off
 
 
 def use_fused_decode_attention(on: bool) -> bool:
     """Switch the one-launch decode attention (cache write and slice merge inside) on or off."""
     global _fused_decode
     before, _fused_decode = _fused_decode, bool(on)
-    return before
-
-
-_fused_mlp = os.environ.get("R2_FUSED_MLP", "0") == "1"
-
-
-def use_fused_mlp(on: bool) -> bool:
-    """Switch the one-kernel feed-forward for a few rows (bfloat16) on or off; off (the default:
-    it measured slower, 17.3 against 6.9 + 4.9 us at 8 x 768 x 3,072 x 768), its two products run
-    as kernels of their own. Returns the previous setting."""
-    global _fused_mlp
-    before, _fused_mlp = _fused_mlp, bool(on)
     return before
 
 
@@ -161,7 +171,16 @@ def use_fused_norm(on: bool) -> bool:
     return before
 
 
-N_SMS = 148
+_sm_counts: dict = {}
+
+
+def sm_count(device) -> int:
+    """The device's number of multiprocessors (asked once per device)."""
+    device = torch.device(device)
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = int(torch.cuda.get_device_properties(device).multi_processor_count)
+    return n
 
 
 _prefill_tc = {"0": False, "always": "always"}.get(os.environ.get("R2_PREFILL_TC", "1"), True)
@@ -196,13 +215,13 @@ def use_fast_attention(on: bool) -> bool:
     return before
 
 
-def decode_slices(n_rows: int, n_kv_heads: int, max_context: int) -> int:
+def decode_slices(n_rows: int, n_kv_heads: int, max_context: int, device="cuda:0") -> int:
     """Slices of the keys per (row, kv head) in decode attention: as many as keep every CTA
     resident at once (four to an SM is what every head size's kernel reaches; a second wave of
     CTAs costs more than the slices gain: 8 rows x 12 heads took 8.4 us with 6 slices, 10.3 us with
     8), never less than 128 keys a slice."""
     ctas = max(1, n_rows * n_kv_heads)
-    want = max(1, 4 * N_SMS // ctas)
+    want = max(1, 4 * sm_count(device) // ctas)
     most = max(1, max_context // 128)
     return max(1, min(want, most, 32))
 
@@ -263,7 +282,6 @@ class _Workspace:
     def __init__(self, device):
         self.floats = torch.empty(self.FLOATS, dtype=torch.float32, device=device)
         self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
-        self.mlp_counters = torch.zeros(16, dtype=torch.int32, device=device)  # the fused feed-forward's, zero between launches
         self.error = torch.zeros(4, dtype=torch.int32, device=device)
 
 
@@ -281,6 +299,33 @@ def device_errors(device="cuda:0") -> int:
     """0, or the code that a kernel left when one of its bounded waits ran out (synchronises)."""
     ws = _workspaces.get(torch.device(device))
     return 0 if ws is None else int(ws.error[0].item())
+
+
+def error_word(device) -> torch.Tensor:
+    """The device's error word (int32 [4]; element 0 holds the code): a step's graph copies it to the
+    host beside its tokens, so that a time-out is seen without a transfer of its own."""
+    return _workspace(torch.device(device)).error
+
+
+def raise_on_device_error(device="cuda:0", code: int | None = None) -> None:
+    """Raises KernelTimeout if a kernel on `device` has recorded that a bounded wait ran out, and
+    clears the word so that later steps are judged on their own. `code` is the word's value when the
+    caller has read it already (a graph's pinned copy); else it is read here (synchronises)."""
+    if code is None:
+        code = device_errors(device)
+    if code:
+        ws = _workspaces.get(torch.device(device))
+        if ws is not None:
+            ws.error.zero_()
+        raise KernelTimeout(int(code))
+
+
+def wait_selftest(device="cuda:0", polls: int = 64, code: int = 99) -> None:
+    """Launches the kernel that waits `polls` polls on a barrier nothing arrives on and then records
+    `code` in the device's error word (csrc/kernels/wait_selftest.cu). For tests of the error path."""
+    ws = _workspace(torch.device(device))
+    with torch.cuda.device(device):
+        _check(_lib("wait_selftest").r2_wait_selftest(_p(ws.error), int(polls), int(code), _stream()), "wait_selftest")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -329,24 +374,6 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: fl
     return out
 
 
-_next_weight: dict[int, tuple[int, int]] = {}
-
-
-def set_weight_order(weights: list[torch.Tensor]) -> None:
-    """Tell the products in which order their weights are used during a step: with few tokens a
-    product then asks the following product's weight into L2 while it runs (decode steps wait on
-    DRAM latency, not bandwidth). The last weight's successor is the first. Optional."""
-    _next_weight.clear()
-    for i, w in enumerate(weights):
-        nxt = weights[(i + 1) % len(weights)]
-        _next_weight[w.data_ptr()] = (nxt.data_ptr(), nxt.numel() * nxt.element_size())
-
-
-def _prefetch_args(w: torch.Tensor, m: int):
-    hint = _next_weight.get(w.data_ptr()) if m <= 64 and _weight_prefetch else None
-    return (C.c_void_p(hint[0]), C.c_longlong(hint[1])) if hint else (None, C.c_longlong(0))
-
-
 class NormedRows:
     """LayerNorm of float32 rows that has not been computed yet: `linear` may compute it inside
     its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel."""
@@ -381,7 +408,7 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
     status = _lib("gemm_tc").r2_gemm_tc(
         None, 0, _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), _p(a.x), a.x.stride(0), _p(a.rows), _p(a.gamma),
-        _p(a.beta), C.c_float(a.eps), *_prefetch_args(w, m), None, _stream())
+        _p(a.beta), C.c_float(a.eps), None, C.c_longlong(0), None, _stream())
     if status == -4:
         return None
     _check(status, "linear (tensor cores, fused norm)")
@@ -391,36 +418,7 @@ def _linear_of_normed(a: NormedRows, w, bias, w_is_nk, act, residual, out_dtype,
 def mlp(h, w_in: torch.Tensor, b_in: torch.Tensor, act: str, w_out: torch.Tensor, b_out: torch.Tensor | None,
         residual: torch.Tensor | None = None) -> torch.Tensor:
     """act(h @ w_in + b_in) @ w_out + b_out (+ residual), both matrices stored [in, out]. `h` may be
-    NormedRows. A few bfloat16 rows of a width that fits run as ONE kernel (LayerNorm, both
-    products, the sum over the hidden features: csrc/kernels/mlp_fused.cu); everything else as two
-    `linear` calls."""
-    if (_fused_mlp and _tensor_core_gemm and _fused_norm and isinstance(h, NormedRows) and h.dtype == torch.bfloat16
-            and w_in.dtype == torch.bfloat16 and w_out.dtype == torch.bfloat16 and residual is not None
-            and residual.dtype == torch.float32 and h.shape[0] <= 16 and h.x.is_contiguous()):
-        m, k = h.shape
-        hidden, n_out = w_in.shape[1], w_out.shape[1]
-        if w_in.shape[0] != k or w_out.shape[0] != hidden:
-            raise KernelError(f"mlp: rows {h.shape}, w_in {tuple(w_in.shape)} and w_out {tuple(w_out.shape)} do not fit")
-        if act not in ACTIVATIONS:
-            raise KernelError(f"unknown activation {act!r}")
-        _need(h.x, "x", torch.float32, 2)
-        _need(residual, "residual", torch.float32, 2)
-        if tuple(residual.shape) != (m, n_out):
-            raise KernelError(f"mlp: residual {tuple(residual.shape)} is not [{m}, {n_out}]")
-        for name, t, n in (("b_in", b_in, hidden), ("b_out", b_out, n_out), ("gamma", h.gamma, k), ("beta", h.beta, k)):
-            if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_cuda):
-                raise KernelError(f"mlp: {name} must be {n} float32 values on the device")
-        out = torch.empty(m, n_out, dtype=torch.float32, device=h.device)
-        ws = _workspace(h.device)
-        status = _lib("mlp_fused").r2_mlp_fused(
-            _p(h.x), h.x.stride(0), _p(h.rows), _p(h.gamma), _p(h.beta), C.c_float(h.eps), m, k, _p(w_in), _rows(w_in, "w_in"),
-            _p(b_in), hidden, _p(w_out), _rows(w_out, "w_out"), _p(b_out), n_out, _p(residual), _rows(residual, "residual"),
-            _p(out), _rows(out, "out"), ACTIVATIONS[act], _p(ws.floats), C.c_longlong(ws.floats.numel()), _p(ws.mlp_counters),
-            _p(ws.error), _stream())
-        if status != -4:
-            _check(status, "mlp (one kernel)")
-            _used("mlp_fused")
-            return out
+    NormedRows (the LayerNorm then runs inside the first product's kernel where it can)."""
     inner = linear(h, w_in, b_in, act=act)
     return linear(inner, w_out, b_out, residual=residual)
 
@@ -497,7 +495,7 @@ def linear(a, w: torch.Tensor, bias: torch.Tensor | None = None, *, w_is_nk: boo
         status = _lib("gemm_tc").r2_gemm_tc(
             _p(a), lda, _p(w), ldw, int(w_is_nk), _p(bias), _p(residual), ldr, _p(out), _rows(out, "out"), m, n, k,
             ACTIVATIONS[act], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0),
-            *_prefetch_args(w, m), None, _stream())
+            None, C.c_longlong(0), None, _stream())
         if status != -4:  # -4: a shape the tensor-core kernel does not take; the CUDA-core kernel does
             _check(status, "linear (tensor cores)")
             return out
@@ -525,7 +523,7 @@ def _linear_kv(a: torch.Tensor, w: torch.Tensor, bias, w_is_nk: bool, out, kv: K
     status = _lib("gemm_tc").r2_gemm_tc(
         _p(a), _rows(a, "a"), _p(w), _rows(w, "w"), int(w_is_nk), _p(bias), None, 0, _p(out), _rows(out, "out"), m, n, k,
         ACTIVATIONS[None], dtype_code(out.dtype), _p(ws.error), None, 0, None, None, None, C.c_float(0.0),
-        *_prefetch_args(w, m), C.byref(kv), _stream())
+        None, C.c_longlong(0), C.byref(kv), _stream())
     if status == -4:
         return None
     _check(status, "linear (tensor cores, keys and values into the cache)")
@@ -581,7 +579,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     group = n_heads // max(n_kv_heads, 1)
     if q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
-        n_slices = decode_slices(n, n_kv_heads, max_context)
+        n_slices = decode_slices(n, n_kv_heads, max_context, q.device)
         ws = _workspace(q.device)
         need = lib.r2_attention_decode_scratch_floats(n, n_heads, n_slices)
         if need > ws.floats.numel():
@@ -652,7 +650,7 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     stride = _rows(k_new, "k_new")
     if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
         raise KernelError("decode attention: the new keys and values do not fit the rows")
-    slices = decode_slices(n, n_kv_heads, max_context)
+    slices = decode_slices(n, n_kv_heads, max_context, q.device)
     lib = _lib_for_head_dim("attention_decode", head_dim)
     ws = _workspace(q.device)
     if (lib.r2_attention_decode_scratch_floats(n, n_heads, slices) > ws.floats.numel()

@@ -77,20 +77,6 @@ class DecoderModel:
         head_table = self.embedding.table if spec.head == spec.embedding else tensors[spec.head].to(rt.device, rt.dtype)
         self.head = Head(build_part("norm", spec.final_norm, tensors, rt), head_table, rt.dtype)
         self.cache_members, self.state_members = self._members(mixers)
-        self._announce_weight_order()
-
-    def _announce_weight_order(self) -> None:
-        """The matrices in the order in which a step uses them, for the products' L2 prefetch."""
-        from ..kernels import ops
-
-        order = []
-        for entry in self.schedule:
-            block = self.blocks[entry.layer]
-            for part in (block.mixer, block.feed_forward):
-                order += [t for t in getattr(part, "matrices", lambda: [])()]
-        order.append(self.head.table)
-        if len(order) > 1:
-            ops.set_weight_order(order)
 
     def _members(self, mixers) -> tuple[list[MemberSpec], list]:
         cache: dict[int, MemberSpec] = {}

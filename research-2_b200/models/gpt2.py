@@ -4,7 +4,8 @@ Tensor names and the `[in, out]` (Conv1D) layout of the four matrices per layer 
 GPT-2 checkpoints (kelpie-models/kelpie_models/models/torch/gpt2.py:157-188): `wte.weight`,
 `wpe.weight`, `h.{i}.ln_1`, `h.{i}.attn.c_attn`, `h.{i}.attn.c_proj`, `h.{i}.ln_2`,
 `h.{i}.mlp.c_fc`, `h.{i}.mlp.c_proj`, `ln_f`; each may carry a `transformer.` prefix. The
-head is the token table (gpt2.py:70,101); a stored `lm_head.weight` and the causal-mask
+head is the token table (gpt2.py:70,101): a stored `lm_head.weight` is not read but must equal
+`wte.weight` (the reference's tripwire is its shape assert, gpt2.py:186-187); the causal-mask
 buffers `attn.bias` / `attn.masked_bias` are not read.
 """
 
@@ -38,7 +39,8 @@ def weight_spec(cfg: GPT2Config) -> WeightSpec:
     return WeightSpec(
         tensors=tuple(tensors),
         prefixes=("", "transformer."),
-        ignorable=(r"lm_head\.weight", r"(transformer\.)?h\.\d+\.attn\.(bias|masked_bias)"),
+        ignorable=(r"(transformer\.)?h\.\d+\.attn\.(bias|masked_bias)",),
+        tied=(("lm_head.weight", "wte.weight"),),
     )
 
 

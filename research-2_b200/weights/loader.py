@@ -44,6 +44,9 @@ class WeightSpec:
     tensors: tuple[TensorSpec, ...]
     prefixes: tuple[str, ...] = ("",)  # spellings tried in order, e.g. ("", "transformer.")
     ignorable: tuple[str, ...] = field(default=())  # regexes of names that may be present and are not read
+    # (stored name, spec name): a tensor that may be stored beside the one it is tied to; it is
+    # not read, but it must hold the same values, else the checkpoint is not the tied model it claims to be
+    tied: tuple[tuple[str, str], ...] = field(default=())
 
 
 def check_and_select(found: dict[str, torch.Tensor], spec: WeightSpec, where: str = "checkpoint") -> dict[str, torch.Tensor]:
@@ -75,6 +78,19 @@ def check_and_select(found: dict[str, torch.Tensor], spec: WeightSpec, where: st
             if tensor.dtype == torch.float16:
                 tensor = tensor.to(torch.bfloat16)
         out[ts.name] = tensor
+    for alias, target in spec.tied:
+        if alias not in found:
+            continue
+        used.add(alias)
+        if target not in out:
+            continue  # already reported as missing or wrong
+        copy, kept = found[alias], out[target]
+        if tuple(copy.shape) != tuple(kept.shape):
+            wrong.append(f"{alias}: tied to {target} of shape {tuple(kept.shape)}, got {tuple(copy.shape)}")
+        elif not torch.equal(copy.to(torch.float32), kept.to(torch.float32)):
+            gap = float((copy.to(torch.float32) - kept.to(torch.float32)).abs().max())
+            wrong.append(f"{alias}: tied to {target} but its values differ (max |difference| {gap:.3g}); "
+                         f"an untied head is not supported")
     ignorable = [re.compile(p) for p in spec.ignorable]
     unexpected = sorted(
         name for name in found

@@ -155,3 +155,24 @@ def test_random_orders_keep_every_invariant(seed):
     for r in list(fed):
         cm.close(r)
     assert [cm.n_free(g) for g in range(2)] == [groups[0].num_pages, groups[1].num_pages]
+
+
+def test_the_replay_tests_mixed_traces_use_pages_again():
+    """The GPU tests replay their mixed traces in a pool of the trace's own peak demand plus one page.
+    Over the cache manager alone (no GPU) that pool is enough, and at least a third of its pages
+    pass from one request to another, at every configuration that those tests use."""
+    from tests import traces
+    from tests.helpers import TINY, random_tokens
+    from tests.test_odd_shapes_gpu import ODD
+    from tests.test_replay_gpu import LENGTHS
+
+    cases = [(name, TINY[name]["page_size"], 4, [(100 + i, n) for i, n in enumerate(LENGTHS[name])]) for name in LENGTHS]
+    cases += [(name, t["page_size"], 2, [(300 + i, n) for i, n in enumerate(t["lengths"])]) for name, t in ODD.items()]
+    cases.append(("124M", 16, 3, [(500 + i, n) for i, n in enumerate((130, 40, 9, 200, 70, 25))]))
+    for name, page, live, lengths in cases:
+        requests = {f"r{i}": random_tokens(seed, n, 50) for i, (seed, n) in enumerate(lengths)}
+        tb = traces.mixed(requests, max_live=live)
+        pool = traces.peak_pages(tb, page) + 1
+        owners = traces.page_traffic(tb, page, pool)   # raises OutOfPages if the pool were too small
+        reused = sum(len(seen) >= 2 for seen in owners.values())
+        assert 3 * reused >= pool, f"{name}: {reused} of {pool} pages are used again"

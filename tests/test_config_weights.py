@@ -132,6 +132,21 @@ def test_transformer_prefix_and_ignorable_buffers(tmp_path):
     assert "wte.weight" in got and len(got) == 2 + 12 * cfg.n_layer + 2
 
 
+def test_a_stored_head_that_differs_from_the_token_table_is_an_error():
+    """GPT-2 ties its head to wte: a checkpoint whose lm_head.weight holds other values is not that model."""
+    arch = architecture("GPT2LMHeadModel")
+    cfg = arch.parse_config(TINY_A["config"])
+    tensors = arch.random_weights(cfg, 0)
+    tensors["lm_head.weight"] = tensors["wte.weight"].clone()
+    tensors["lm_head.weight"][3, 5] += 0.25
+    with pytest.raises(WeightError, match=r"lm_head\.weight: tied to wte\.weight but its values differ") as err:
+        check_and_select(tensors, arch.weight_spec(cfg))
+    assert len(err.value.wrong) == 1 and not err.value.missing and not err.value.unexpected
+    tensors["lm_head.weight"] = tensors["wte.weight"][:-1]
+    with pytest.raises(WeightError, match="tied to wte.weight of shape"):
+        check_and_select(tensors, arch.weight_spec(cfg))
+
+
 def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
     arch = architecture("GPT2LMHeadModel")
     cfg = arch.parse_config(TINY_A["config"])

@@ -67,7 +67,7 @@ def make_engine(max_requests=3, pages=64, page_size=4, max_seq_len=96, budget=16
         SchedulerConfig(max_requests=max_requests, max_seq_len=max_seq_len, max_batch_tokens=budget, max_batch_reqs=max_requests,
                         vocab_size=VOCAB, eos_token=None, order="running_first", reserve_ratio=0.0),
         step_fn.cache_groups())
-    return Engine(step_fn, None, scheduler)
+    return Engine(step_fn, scheduler)
 
 
 def continuation(prompt: list[int], n: int, stop=()) -> list[int]:

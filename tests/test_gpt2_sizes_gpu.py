@@ -2,7 +2,7 @@
 50,257) with random weights, and the layer sizes of the 355M and 1.5B models (two layers each:
 width 1,024 with 16 heads; width 1,600 with 25 heads, which is no multiple of 128): logits in
 float32 and in bfloat16 against the plain implementation in all four cuttings (whole, the last
-32 tokens one by one, portions, mixed in few pages). At these sizes the products run as
+32 tokens one by one, portions, mixed in a pool of the trace's peak demand plus one page, where pages are used again). At these sizes the products run as
 cluster split-K or whole tiles, attention on tcgen05, and the logits over a vocabulary that is
 no multiple of anything."""
 
@@ -12,7 +12,7 @@ import pytest
 
 from tests import traces
 from tests.helpers import make_model_dir, random_tokens
-from tests.test_replay_gpu import compare, round64, run_trace
+from tests.test_replay_gpu import compare, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -48,10 +48,23 @@ def folders(tmp_path_factory):
 @pytest.mark.parametrize("size", sorted(SIZES))
 def test_gpt2_sizes_in_all_four_cuttings(folders, size, dtype):
     folder_124m = folders(size)
-    requests = {f"r{i}": random_tokens(500 + i, n, GPT2_124M["vocab_size"]) for i, n in enumerate((130, 40, 9, 200))}
-    cuttings = {"whole": (traces.whole(requests), 1), "decode32": (traces.prefill_then_decode(requests, 32), 1),
-                "portions": (traces.portions(requests), 1), "mixed": (traces.mixed(requests, max_live=4), 4)}
-    for mode, (tb, live) in cuttings.items():
-        biggest = sorted((round64(len(v)) for v in requests.values()), reverse=True)[:live]
-        outputs = run_trace(folder_124m, tb, dtype, sum(biggest), 16)
+    requests = {f"r{i}": random_tokens(500 + i, n, GPT2_124M["vocab_size"]) for i, n in enumerate((130, 40, 9, 200, 70, 25))}
+    cuttings = {"whole": traces.whole(requests), "decode32": traces.prefill_then_decode(requests, 32),
+                "portions": traces.portions(requests), "mixed": traces.mixed(requests, max_live=3)}
+    for mode, tb in cuttings.items():
+        outputs = run_trace(folder_124m, tb, dtype, 16, expect_reuse=mode == "mixed")
         compare(folder_124m, requests, tb, outputs, dtype, f"{size}/{dtype}/{mode}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gpt2_124m_through_cuda_graphs(folders, dtype):
+    """The benchmark's own size with every step run as the CUDA graph of its shape bucket (what
+    bench.py and every bfloat16 user run): portions and mixed batches in recycled pages, the last
+    token of every entry against the plain implementation."""
+    folder = folders("124M")
+    requests = {f"r{i}": random_tokens(500 + i, n, GPT2_124M["vocab_size"]) for i, n in enumerate((130, 40, 9, 200, 70, 25))}
+    for mode, tb in (("portions", traces.portions(requests)), ("mixed", traces.mixed(requests, max_live=3)),
+                     ("decode32", traces.prefill_then_decode(requests, 32))):
+        tb = traces.with_last_only(tb)
+        outputs = run_trace(folder, tb, dtype, 16, capture=True, expect_reuse=mode == "mixed")
+        compare(folder, requests, tb, outputs, dtype, f"124M/{dtype}/{mode}/graphs", partial=True)

@@ -178,61 +178,6 @@ def test_linear_with_the_norm_inside(m, k, n, w_is_nk):
     assert o.device_errors() == 0
 
 
-@pytest.mark.parametrize("m,k,hidden,n_out,act", [(8, 768, 3072, 768, "gelu_new"), (1, 768, 3072, 768, "gelu"),
-                                                  (16, 768, 3072, 768, "gelu_new"), (5, 512, 1024, 512, "gelu_new"),
-                                                  (13, 1024, 512, 256, "gelu"), (3, 640, 1536, 384, "gelu_new")])
-def test_feed_forward_in_one_kernel(m, k, hidden, n_out, act):
-    """LayerNorm, both products of the feed-forward and the sum over the hidden features in one
-    kernel (a few bfloat16 rows): the same as the two products apart, and as a plain float32
-    statement; the same bits at every launch; rows picked by an index list."""
-    o = ops()
-    torch.manual_seed(m + k + hidden)
-    x = (torch.randn(m + 3, k) * 2 + 0.5).to(DEV)
-    g, b = (1 + 0.1 * torch.randn(k)).to(DEV), (0.1 * torch.randn(k)).to(DEV)
-    w1 = (torch.randn(k, hidden) * k**-0.5).bfloat16().to(DEV)
-    w2 = (torch.randn(hidden, n_out) * hidden**-0.5).bfloat16().to(DEV)
-    b1, b2 = torch.randn(hidden).to(DEV), torch.randn(n_out).to(DEV)
-    res = torch.randn(m, n_out).to(DEV)
-    rows = torch.randperm(m + 3)[:m].to(torch.int32).to(DEV)
-    for pick in (None, rows):
-        lazy = o.NormedRows(x if pick is not None else x[:m], g, b, 1e-5, torch.bfloat16, rows=pick)
-        before, uses = o.use_fused_mlp(True), o.kernel_uses().get("mlp_fused", 0)
-        try:
-            fused = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
-            again = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
-            assert o.kernel_uses().get("mlp_fused", 0) == uses + 2, "the one-kernel form did not take the shape"
-            o.use_fused_mlp(False)
-            apart = o.mlp(lazy, w1, b1, act, w2, b2, residual=res)
-        finally:
-            o.use_fused_mlp(before)
-        assert o.device_errors() == 0
-        assert torch.equal(fused, again)
-        src = x[:m] if pick is None else x[pick.long()]
-        h = F.layer_norm(src, (k,), g, b, 1e-5).bfloat16().float()
-        inner = F.gelu(h @ w1.float() + b1, approximate="tanh" if act == "gelu_new" else "none").bfloat16().float()
-        want = inner @ w2.float() + b2 + res
-        torch.testing.assert_close(fused, want, atol=2e-2, rtol=2e-2)
-        torch.testing.assert_close(fused, apart, atol=2e-2, rtol=2e-2)
-
-
-def test_feed_forward_shapes_that_the_one_kernel_form_does_not_take():
-    """A hidden width that is no multiple of 512, or more than 16 rows: two products as before."""
-    o = ops()
-    torch.manual_seed(3)
-    for m, k, hidden, n_out in ((4, 96, 320, 96), (40, 768, 3072, 768)):
-        x = torch.randn(m, k).to(DEV)
-        g, b = torch.ones(k).to(DEV), torch.zeros(k).to(DEV)
-        w1 = (torch.randn(k, hidden) * k**-0.5).bfloat16().to(DEV)
-        w2 = (torch.randn(hidden, n_out) * hidden**-0.5).bfloat16().to(DEV)
-        b1, b2, res = torch.randn(hidden).to(DEV), torch.randn(n_out).to(DEV), torch.randn(m, n_out).to(DEV)
-        uses = o.kernel_uses().get("mlp_fused", 0)
-        got = o.mlp(o.NormedRows(x, g, b, 1e-5, torch.bfloat16), w1, b1, "gelu_new", w2, b2, residual=res)
-        assert o.kernel_uses().get("mlp_fused", 0) == uses
-        h = F.layer_norm(x, (k,), g, b, 1e-5).bfloat16().float()
-        want = F.gelu(h @ w1.float() + b1, approximate="tanh").bfloat16().float() @ w2.float() + b2 + res
-        torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
-
-
 def test_linear_rows_do_not_depend_on_the_batch():
     """In float32 a row's result is the same bits alone and among other rows."""
     torch.manual_seed(0)
@@ -313,6 +258,15 @@ class PagedCase:
         return o.paged_attention(self.q_rows, self.k_cache, self.v_cache, self.page_stride, self.page, self.n_pages,
                                  self.tables, self.row_entry, self.positions, self.seq_lens, self.n_heads, self.n_kv,
                                  self.hd, scale, window, **kernel_choice)
+
+    def run_fused(self, scale, window=0, max_context=4096):
+        """The one-launch decode attention (every entry one row): cache write and slice merge inside."""
+        o = ops()
+        out = o.decode_attention_fused(self.q_rows, self.k_new, self.v_new, self.slots, self.k_cache, self.v_cache, self.page_stride,
+                                       self.page, self.n_pages, self.tables, self.row_entry, self.positions, self.seq_lens,
+                                       self.n_heads, self.n_kv, self.hd, scale, window, max_context)
+        assert out is not None, "the fused decode attention did not take the case"
+        return out
 
     def plain(self, scale, window=0):
         outs = []
@@ -577,6 +531,78 @@ def test_window_edge():
             got = case.run(1.0, window).cpu().view(16)
             hit = torch.allclose(got, case.v_dense[0][far, 0], atol=1e-3)
             assert hit == visible, f"window {window}, query {pos}, key {far}: visible={visible}, hit={hit}"
+
+
+def _planted(entries, row, far, hd, page, seed):
+    """A case whose query row `row` (of entry 0) and key `far` point the same way, thirty long."""
+    direction = torch.randn(hd, generator=torch.Generator().manual_seed(seed))
+    direction /= direction.norm()
+
+    def mutate(case):
+        case.q[0][row, :] = (direction * 30).to(torch.bfloat16)
+        case.k_dense[0][far, :] = (direction * 30).to(torch.bfloat16)
+
+    return PagedCase(entries, 1, 1, hd, page, torch.bfloat16, seed=seed, garbage=float("inf"), mutate=mutate)
+
+
+@pytest.mark.parametrize("hd,page", [(64, 16), (32, 8), (128, 32)])
+def test_window_edge_in_the_bfloat16_decode_kernels(hd, page):
+    """The key just inside the window counts and the one just outside does not, in every form of
+    the bfloat16 decode attention: one slice and several, tensor-core and scalar tiles, with the
+    cache write and merge inside the kernel and without. Windows that end on a page's edge, a
+    32-key tile's edge and in between; unwritten slots hold inf."""
+    o = ops()
+    for window, pos in ((8, 40), (16, 16), (17, 33), (33, 300), (64, 511), (129, 400)):
+        for far, visible in ((pos - window + 1, True), (pos - window, False)):
+            if far < 0:
+                continue
+            for mma in (True, False):
+                before = o.use_decode_mma(mma, hd)
+                try:
+                    runs = {}
+                    for name, max_context in (("one slice", 64), ("slices", 4096)):
+                        case = _planted([(pos, 1)], 0, far, hd, page, seed=window + pos)
+                        runs[name] = case.run(1.0, window, decode_only=True, max_context=max_context)
+                        case = _planted([(pos, 1)], 0, far, hd, page, seed=window + pos)
+                        runs[name + ", fused"] = case.run_fused(1.0, window, max_context=max_context)
+                finally:
+                    o.use_decode_mma(before, hd)
+                want = case.v_dense[0][far, 0].float()
+                for name, got in runs.items():
+                    got = got.float().cpu().view(hd)
+                    assert torch.isfinite(got).all(), f"{name}: an unwritten slot leaked in"
+                    hit = torch.allclose(got, want, atol=5e-2)
+                    assert hit == visible, f"{name} (mma={mma}): window {window}, query {pos}, key {far}: visible={visible}, hit={hit}"
+
+
+@pytest.mark.parametrize("tc", [False, "always"])
+def test_window_edge_in_the_bfloat16_prefill_kernels(tc):
+    """The same for prompt portions in both prefill kernels (mma.sync with 64-row tiles, tcgen05 with
+    128-row tiles): the query row is the portion's first row, the first row of a later tile, the last
+    row of a tile and the portion's last row; windows that end on a page's edge and a key tile's."""
+    o = ops()
+    start, rows, hd, page = 40, 200, 64, 16
+    before = o.use_prefill_tc(tc)
+    uses = o.kernel_uses()
+    try:
+        for window in (24, 41, 64, 65, 130):
+            for row in (0, 63, 64, 127, 128, 199):
+                pos = start + row
+                for far, visible in ((pos - window + 1, True), (pos - window, False)):
+                    if far < 0:
+                        continue
+                    case = _planted([(start, rows)], row, far, hd, page, seed=window + row)
+                    got = case.run(1.0, window, q_start=case.q_start, n_tiles=case.n_tiles).float().cpu()
+                    assert torch.isfinite(got).all(), "an unwritten slot leaked in"
+                    hit = torch.allclose(got[row], case.v_dense[0][far, 0].float(), atol=5e-2)
+                    assert hit == visible, f"tc={tc}: window {window}, row {row} at {pos}, key {far}: visible={visible}, hit={hit}"
+                    # the rows around it see what the plain statement says they see
+                    torch.testing.assert_close(got, case.plain(1.0, window), atol=6e-2, rtol=6e-2)
+    finally:
+        o.use_prefill_tc(before)
+    name = "attention_prefill_tc" if tc else "attention_prefill"
+    assert o.kernel_uses().get(name, 0) > uses.get(name, 0), f"{name} never ran"
+    assert o.device_errors() == 0
 
 
 def test_pad_rows_are_zero():

@@ -241,3 +241,104 @@ def test_layers_that_differ_a_layer_twice_and_a_shared_cache():
     window_group = [g for g, spec in enumerate(step_fn.groups) if spec.window][0]
     assert cache.pages_held(0, window_group) <= 4, "the window group kept pages that the window has passed"
     assert np.abs(got - want).max() < 2e-4 * max(1.0, np.abs(want).max()), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_window_group_beside_a_full_one_in_portions_and_long_decoding(dtype):
+    """A model with a windowed layer and full layers has two cache groups, each with block tables,
+    slots and a pool of its own. Two requests are stepped together, in portions and then token by
+    token to the model's limit, in pools so small that the window group must give pages back as the
+    window passes them (block-table entries behind the window read as the null page) and that the
+    second request runs in pages the first has left. Unwritten slots hold inf. Every position's
+    logits against one dense pass of the plain implementation's functions."""
+    from research_2_b200.cache.manager import CacheManager
+    from research_2_b200.engine.step import StepFunction
+    from research_2_b200.models.decoder import DecoderModel
+
+    d, v = 64, 203
+    tensors = {k: t.to(dtype).float() for k, t in mixed_layers_tensors(d, v).items()}
+    model = DecoderModel(mixed_layers_spec({"d": d, "v": v}), tensors, rt(dtype))
+    step_fn = StepFunction(model, 8, 14, 2)   # 14 pages a group: one request of 96 tokens (12 pages) and a bit
+    cache = CacheManager(step_fn.cache_groups(), 2, 96)
+    window_group = [g for g, spec in enumerate(step_fn.groups) if spec.window][0]
+    step_fn.arena.fill_(float("inf"))
+    gen = torch.Generator().manual_seed(8)
+    ids = {r: torch.randint(0, v, (n,), generator=gen).tolist() for r, n in ((0, 96), (1, 41))}
+    want = {r: mixed_layers_plain(tensors, seq, d).numpy() for r, seq in ids.items()}
+    # request 0 in portions and then one by one; request 1 joins after request 0 has slid its window
+    plan = [[(0, 20)], [(0, 3)], [(0, 29)], [(0, 1)], [(0, 1)], [(0, 2)]] + [[(0, 1)]] * 16
+    plan += [[(0, 1), (1, 17)], [(0, 1), (1, 2)], [(0, 1), (1, 16)]] + [[(0, 1), (1, 1)]] * 6
+    plan += [[(0, 1)]] * 14
+    at = {0: 0, 1: 0}
+    got = {0: [], 1: []}
+    most_window_pages = 0
+    for entries in plan:
+        reqs, starts, toks = [], [], []
+        for r, rows in entries:
+            rows = min(rows, len(ids[r]) - at[r])
+            if rows <= 0:
+                continue
+            if not cache.is_open(r):
+                cache.open(r)
+            cache.slide(r, at[r])
+            cache.reserve(r, at[r], at[r] + rows)
+            reqs.append(r), starts.append(at[r]), toks.append(ids[r][at[r]: at[r] + rows])
+        if not reqs:
+            continue
+        n = sum(len(t) for t in toks)
+        batch = step_fn.new_batch(n, len(reqs), n, decode_only=all(len(t) == 1 for t in toks))
+        batch.set_entries(reqs, starts, toks)
+        cache.fill(batch)
+        batch.set_logit_rows(list(range(n)))
+        logits = step_fn(batch).float().cpu().numpy()
+        row = 0
+        for r, t in zip(reqs, toks):
+            got[r].append(logits[row: row + len(t)])
+            row += len(t)
+            at[r] += len(t)
+            most_window_pages = max(most_window_pages, cache.pages_held(r, window_group))
+            if at[r] == len(ids[r]):
+                cache.close(r)
+    assert most_window_pages <= 3, "the window group kept pages that the window (12 keys, pages of 8) has passed"
+    assert cache.check() == "" and all(cache.n_free(g) == 14 for g in range(2))
+    for r in ids:
+        out = np.concatenate(got[r])
+        assert out.shape == want[r].shape and np.isfinite(out).all(), "an unwritten or returned slot leaked in"
+        limit = (2e-4 if dtype == torch.float32 else 4e-2) * max(1.0, np.abs(want[r]).max())
+        err = np.abs(out - want[r]).max(axis=1)
+        assert err.max() < limit, f"request {r}: first position over the limit is {int(np.argmax(err >= limit))} ({err.max():.3g} >= {limit:.3g})"
+
+
+def test_a_two_group_model_through_the_engine():
+    """The same model through the scheduler and the engine (native batches with two groups' block tables
+    and slots, admission by the worst case of each group, pages given back as the window slides):
+    greedy tokens of three requests in a small pool equal the plain implementation's."""
+    from research_2_b200.config.engine_options import EngineOptions
+    from research_2_b200.engine.api import generate_with
+    from research_2_b200.engine.engine import Engine
+    from research_2_b200.models.decoder import DecoderModel
+
+    d, v = 64, 203
+    tensors = {k: t * (4.0 if k in ("emb",) else 1.0) for k, t in mixed_layers_tensors(d, v).items()}  # clear argmax gaps
+    model = DecoderModel(mixed_layers_spec({"d": d, "v": v}), tensors, rt(torch.float32))
+    gen = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, v, (n,), generator=gen).tolist() for n in (30, 9, 50)]
+    n_new = 24
+
+    def plain_generate(prompt):
+        seq = list(prompt)
+        for _ in range(n_new):
+            seq.append(int(mixed_layers_plain(tensors, seq, d)[-1].argmax()))
+        return seq[len(prompt):]
+
+    want = [plain_generate(p) for p in prompts]
+    opts = EngineOptions(dtype="float32", max_requests=3, block_size=8, num_slabs=18, max_batch_tokens=32, chunk_size=16)
+    with Engine.for_model(model, opts) as engine:
+        assert len(engine.scheduler.groups) == 2
+        engine.keep_events = True
+        got = generate_with(engine, prompts, n_new)
+        assert engine.scheduler.cache.check() == ""
+        assert all(engine.scheduler.cache.n_free(g) == 18 for g in range(2))
+        events = engine.request_events()
+        assert len(events) == 3 and all(e.n_generated == n_new and e.time_to_first_token_ms > 0 for e in events)
+    assert got == want

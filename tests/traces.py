@@ -100,3 +100,64 @@ def mixed(requests: dict[str, list[int]], max_live: int = 4, chunk_sizes=(24, 5,
         for rid in ended:
             del live[rid]
     return tb
+
+
+def with_last_only(tb: TraceBuilder) -> TraceBuilder:
+    """The same steps with only each entry's last token wanted: the one logit row per entry that
+    generation computes, and so what a step that runs as a CUDA graph can return."""
+    out = TraceBuilder()
+    for record in tb.steps:
+        out.step([(e["id"], e["tokens"], [len(e["tokens"]) - 1]) for e in record["entries"]], end=record["end"])
+    return out
+
+
+def peak_pages(tb: TraceBuilder, page_size: int) -> int:
+    """The most pages that the live requests hold at the same time: a request holds
+    ceil(tokens fed so far / page_size) pages from its first step to the step that ends it."""
+    fed: dict[str, int] = {}
+    peak = 0
+    for record in tb.steps:
+        for entry in record["entries"]:
+            fed[entry["id"]] = fed.get(entry["id"], 0) + len(entry["tokens"])
+        peak = max(peak, sum(-(-n // page_size) for n in fed.values()))
+        for rid in record["end"]:
+            fed.pop(rid, None)
+    return peak
+
+
+def max_live(tb: TraceBuilder) -> int:
+    live: set[str] = set()
+    most = 0
+    for record in tb.steps:
+        live |= {e["id"] for e in record["entries"]}
+        most = max(most, len(live))
+        live -= set(record["end"])
+    return most
+
+
+def page_traffic(tb: TraceBuilder, page_size: int, num_pages: int) -> dict[int, list[str]]:
+    """Which requests hold each page, in order, when the trace runs over the cache manager with a
+    pool of `num_pages` pages (no GPU): page -> its owners one after the other."""
+    from research_2_b200.cache import CacheManager, GroupSpec
+
+    cache = CacheManager([GroupSpec(page_size, 0, num_pages)], max(1, max_live(tb)), 1 << 20)
+    slots: dict[str, int] = {}
+    fed: dict[str, int] = {}
+    owners: dict[int, list[str]] = {}
+    for record in tb.steps:
+        for entry in record["entries"]:
+            rid = entry["id"]
+            if rid not in slots:
+                slots[rid] = min(set(range(cache.max_requests)) - set(slots.values()))
+                cache.open(slots[rid])
+                fed[rid] = 0
+            cache.reserve(slots[rid], fed[rid], fed[rid] + len(entry["tokens"]))
+            fed[rid] += len(entry["tokens"])
+            for page in cache.table(slots[rid]):
+                if page and (page not in owners or owners[int(page)][-1] != rid):
+                    owners.setdefault(int(page), []).append(rid)
+        for rid in record["end"]:
+            if rid in slots:
+                cache.close(slots.pop(rid))
+                del fed[rid]
+    return owners
