@@ -258,9 +258,10 @@ def test_logits_of_steps_that_run_as_graphs_through_the_engine(tiny_c_dir):
                     p = engine.poll(rid)
                     done[of[rid]] += p.new_tokens
                     if p.finished:
-                        i = of.pop(rid)
+                        of.pop(rid)
                         if waiting:
-                            of[engine.submit(waiting.pop(0), 24)] = len(prompts) - len(waiting) - 1
+                            nxt = len(prompts) - len(waiting)
+                            of[engine.submit(waiting.pop(0), 24)] = nxt
             assert n_graph_steps > 30 and any(t > r for t, r in engine.step_fn._graphs), "no graph with prompt portions ran"
             assert engine.scheduler.cache.check() == ""
         for i, prompt in enumerate(prompts):
