@@ -668,6 +668,84 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     return out
 
 
+_resident_decode = os.environ.get("R2_RESIDENT_DECODE", "1") != "0"
+
+
+def use_resident_decode(on: bool) -> bool:
+    """Switch the one-kernel form of a decode step's layers (csrc/kernels/decode_resident.cu) on or
+    off; off, every part of a layer launches its own kernels. Returns the previous setting."""
+    global _resident_decode
+    before, _resident_decode = _resident_decode, bool(on)
+    return before
+
+
+def resident_decode_enabled() -> bool:
+    return _resident_decode and _tensor_core_gemm and _fast_attention
+
+
+RESIDENT_MAX_GROUPS = 4
+
+
+class ResidentLayerC(C.Structure):
+    """One layer of the resident decode kernel (R2ResidentLayer in csrc/kernels/decode_resident.cu)."""
+
+    _fields_ = [("w_qkv", C.c_void_p), ("w_out", C.c_void_p), ("w_fc", C.c_void_p), ("w_pr", C.c_void_p),
+                ("b_qkv", C.c_void_p), ("b_out", C.c_void_p), ("b_fc", C.c_void_p), ("b_pr", C.c_void_p),
+                ("ln1_g", C.c_void_p), ("ln1_b", C.c_void_p), ("ln2_g", C.c_void_p), ("ln2_b", C.c_void_p),
+                ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("page_stride", C.c_longlong),
+                ("group", C.c_int), ("page_size", C.c_int), ("n_pages", C.c_int), ("window", C.c_int),
+                ("scale", C.c_float), ("eps1", C.c_float), ("eps2", C.c_float), ("act", C.c_int)]
+
+
+class ResidentShapeC(C.Structure):
+    _fields_ = [("n_layers", C.c_int), ("width", C.c_int), ("inner", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int),
+                ("n_rows", C.c_int), ("attn_slices", C.c_int)]
+
+
+class ResidentBuffersC(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("qkv", C.c_void_p), ("mixed", C.c_void_p), ("hidden", C.c_void_p), ("partial", C.c_void_p),
+                ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("tile_counters", C.c_void_p), ("attn_counters", C.c_void_p),
+                ("barrier", C.c_void_p), ("error_flag", C.c_void_p), ("positions", C.c_void_p), ("seq_lens", C.c_void_p),
+                ("block_tables", C.c_void_p * RESIDENT_MAX_GROUPS), ("slot_mapping", C.c_void_p * RESIDENT_MAX_GROUPS),
+                ("table_width", C.c_int * RESIDENT_MAX_GROUPS), ("stamps", C.c_void_p)]
+
+
+def pack_weight_tiles(w: torch.Tensor) -> torch.Tensor:
+    """A [K, N] matrix (stored [in, out]) in the order in which the resident decode kernel's warps hold
+    it: [N / 16 feature tiles][K / 16 k tiles][32 lanes][8 values], a lane's eight values being its
+    registers of the 16 x 16 operand tile of mma.sync m16n8k16 (rows = features, columns = k)."""
+    k, n = w.shape
+    if k % 16 or n % 16:
+        raise KernelError(f"pack_weight_tiles: both sizes must be multiples of 16, got {tuple(w.shape)}")
+    lane = torch.arange(32, device=w.device)
+    g, t = lane >> 2, lane & 3
+    r, e = torch.arange(4, device=w.device), torch.arange(2, device=w.device)
+    m_idx = (g[:, None, None] + 8 * (r[None, :, None] & 1) + 0 * e[None, None, :])      # feature within the tile
+    k_idx = (2 * t[:, None, None] + e[None, None, :] + 8 * (r[None, :, None] >> 1))      # k within the tile
+    tiles = w.reshape(k // 16, 16, n // 16, 16).permute(2, 0, 3, 1)                      # [feature tile, k tile, feature, k]
+    return tiles[:, :, m_idx, k_idx].contiguous().view(-1)
+
+
+def decode_resident_library(head_dim: int) -> C.CDLL:
+    return _lib_for_head_dim("decode_resident", head_dim)
+
+
+def decode_resident_slices(head_dim: int, n_rows: int, n_kv_heads: int, max_context: int, device) -> int:
+    return int(decode_resident_library(head_dim).r2_decode_resident_slices(n_rows, n_kv_heads, max(max_context, 1), 8 * sm_count(device)))
+
+
+def decode_resident(head_dim: int, layers: torch.Tensor, shape: ResidentShapeC, buffers: ResidentBuffersC, page_shift: int,
+                    device) -> bool:
+    """All layers of a decode-only step in one launch; False where the kernel does not take the case."""
+    status = decode_resident_library(head_dim).r2_decode_resident(
+        _p(layers), C.byref(shape), C.byref(buffers), page_shift, sm_count(device), _stream())
+    if status == -4:
+        return False
+    _check(status, "decode step (resident kernel)")
+    _used("decode_resident")
+    return True
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, key0: torch.Tensor,
            key1: torch.Tensor, sample_pos: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """One token per row of float32 logits [R, V] -> int32 [R]."""

@@ -18,6 +18,7 @@ import torch
 from ..cache.arena import MemberSpec
 from ..parts import LayerSpec, PartSpec, Runtime, build_part, registry
 from ..parts.embedding import Head, TokenEmbedding
+from ..parts.resident import ResidentLayers
 
 
 @dataclass(frozen=True)
@@ -77,6 +78,8 @@ class DecoderModel:
         head_table = self.embedding.table if spec.head == spec.embedding else tensors[spec.head].to(rt.device, rt.dtype)
         self.head = Head(build_part("norm", spec.final_norm, tensors, rt), head_table, rt.dtype)
         self.cache_members, self.state_members = self._members(mixers)
+        self._resident = None   # the one-kernel form of a decode step's layers, built at its first use
+        self._resident_tried = False
 
     def _members(self, mixers) -> tuple[list[MemberSpec], list]:
         cache: dict[int, MemberSpec] = {}
@@ -112,6 +115,12 @@ class DecoderModel:
         """The residual stream through the schedule, then logits at ctx.logit_rows: [W, V] float32."""
         table = self.positions.additive_table() if self.positions is not None else None
         x = self.embedding.forward(ctx, table)
+        if ctx.decode_only and ctx.n_tokens <= ResidentLayers.MAX_ROWS:
+            if not self._resident_tried:
+                self._resident_tried = True
+                self._resident = ResidentLayers.build(self.blocks, self.schedule, self.rt)
+            if self._resident is not None and self._resident.forward(x, ctx, cache_members) is not None:
+                return self.head.forward(x, ctx.logit_rows)
         for entry in self.schedule:
             cache = cache_members[entry.cache] if entry.cache is not None else None
             state = state_tensors[entry.state] if entry.state is not None else None

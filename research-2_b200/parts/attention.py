@@ -55,6 +55,14 @@ class PagedAttention:
     capturable = True  # nothing here depends on the batch's contents, only on its shape
     takes_lazy_norm = True  # the input goes straight into ops.linear
 
+    def resident_attention(self) -> dict | None:
+        """For the one-kernel form of a decode step; None while a positions part rotates q and k."""
+        if self.rotary is not None or self.w_out.shape[1] != self.w_qkv.shape[0]:
+            return None
+        return {"w_qkv": self.w_qkv, "b_qkv": self.b_qkv, "w_out": self.w_out, "b_out": self.b_out, "n_heads": self.n_heads,
+                "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window,
+                "width": self.w_qkv.shape[0]}
+
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
         in_cache = False
         if writes_cache and not ctx.decode_only and self.rotary is None:

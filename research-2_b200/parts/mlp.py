@@ -30,5 +30,9 @@ class DenseMLP:
         """The weight matrices in the order in which forward() uses them."""
         return [self.w_in, self.w_out]
 
+    def resident_mlp(self) -> dict:
+        return {"w_fc": self.w_in, "b_fc": self.b_in, "w_pr": self.w_out, "b_pr": self.b_out, "act": self.activation,
+                "width": self.w_in.shape[0], "inner": self.w_in.shape[1]}
+
     def forward(self, h, residual, ctx):
         return ops.mlp(h, self.w_in, self.b_in, self.activation, self.w_out, self.b_out, residual=residual)

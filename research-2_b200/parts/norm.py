@@ -19,6 +19,10 @@ class LayerNorm:
         self.gamma = vector(weights["gamma"], rt)
         self.beta = vector(weights["beta"], rt)
 
+    def layer_norm_params(self):
+        """(gain, shift, eps): for a kernel that normalises rows itself."""
+        return self.gamma, self.beta, self.eps
+
     def forward(self, x, out_dtype, rows=None, lazy: bool = False):
         """Normalised rows in out_dtype. With `lazy` the result is an `ops.NormedRows` that a
         following `ops.linear` may compute inside its own kernel."""

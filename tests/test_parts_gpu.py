@@ -342,3 +342,125 @@ def test_a_two_group_model_through_the_engine():
         events = engine.request_events()
         assert len(events) == 3 and all(e.n_generated == n_new and e.time_to_first_token_ms > 0 for e in events)
     assert got == want
+
+
+def resident_spec(d, v, n_layers, heads, kv, hd, f, windows, n_positions=160):
+    from research_2_b200.models.decoder import ModelSpec
+    from research_2_b200.parts import LayerSpec, PartSpec
+
+    def layer(i):
+        return LayerSpec(
+            block="pre_norm",
+            norm_1=PartSpec("layer_norm", {"eps": 1e-5}, {"gamma": f"l{i}.n1.g", "beta": f"l{i}.n1.b"}),
+            mixer=PartSpec("attention", {"n_heads": heads, "n_kv_heads": kv, "head_dim": hd, "scale": hd**-0.5 / (i + 1), "window": windows[i]},
+                           {"w_qkv": f"l{i}.qkv.w", "b_qkv": f"l{i}.qkv.b", "w_out": f"l{i}.o.w", "b_out": f"l{i}.o.b"}),
+            norm_2=PartSpec("layer_norm", {"eps": 3e-6}, {"gamma": f"l{i}.n2.g", "beta": f"l{i}.n2.b"}),
+            feed_forward=PartSpec("mlp", {"activation": "gelu" if i % 2 else "gelu_new"},
+                                  {"w_in": f"l{i}.fc.w", "b_in": f"l{i}.fc.b", "w_out": f"l{i}.pr.w", "b_out": f"l{i}.pr.b"}))
+
+    return ModelSpec(vocab_size=v, hidden=d, max_seq_len=n_positions, eos_token=None, embedding="emb", head="emb",
+                     positions=PartSpec("learned", {"n_positions": n_positions}, {"table": "pos"}),
+                     layers=tuple(layer(i) for i in range(n_layers)),
+                     final_norm=PartSpec("layer_norm", {"eps": 1e-5}, {"gamma": "nf.g", "beta": "nf.b"}))
+
+
+def resident_tensors(d, v, n_layers, heads, kv, hd, f, n_positions=160):
+    g = torch.Generator().manual_seed(21)
+
+    def rnd(*shape, s=0.1):
+        return (torch.randn(*shape, generator=g) * s).bfloat16().float()
+
+    t = {"emb": rnd(v, d, s=0.5), "pos": rnd(n_positions, d, s=0.5), "nf.g": 1 + rnd(d), "nf.b": rnd(d)}
+    for i in range(n_layers):
+        t.update({f"l{i}.n1.g": 1 + rnd(d), f"l{i}.n1.b": rnd(d), f"l{i}.n2.g": 1 + rnd(d), f"l{i}.n2.b": rnd(d),
+                  f"l{i}.qkv.w": rnd(d, (heads + 2 * kv) * hd, s=0.1), f"l{i}.qkv.b": rnd((heads + 2 * kv) * hd),
+                  f"l{i}.o.w": rnd(heads * hd, d, s=0.1), f"l{i}.o.b": rnd(d),
+                  f"l{i}.fc.w": rnd(d, f, s=0.1), f"l{i}.fc.b": rnd(f), f"l{i}.pr.w": rnd(f, d, s=0.1), f"l{i}.pr.b": rnd(d)})
+    return t
+
+
+def resident_plain(t, ids, n_layers, heads, kv, hd, windows):
+    n = len(ids)
+    x = plain.learned_positions(plain.embed_tokens(torch.tensor(ids), t["emb"]), torch.arange(n), t["pos"])
+    for i in range(n_layers):
+        h = plain.layer_norm(x, t[f"l{i}.n1.g"], t[f"l{i}.n1.b"], 1e-5)
+        qkv = plain.linear(h, t[f"l{i}.qkv.w"], t[f"l{i}.qkv.b"])
+        q = qkv[:, : heads * hd].reshape(n, heads, hd)
+        k = qkv[:, heads * hd: (heads + kv) * hd].reshape(n, kv, hd)
+        v = qkv[:, (heads + kv) * hd:].reshape(n, kv, hd)
+        x = x + plain.linear(plain.causal_attention(q, k, v, hd**-0.5 / (i + 1), windows[i]), t[f"l{i}.o.w"], t[f"l{i}.o.b"])
+        h = plain.layer_norm(x, t[f"l{i}.n2.g"], t[f"l{i}.n2.b"], 3e-6)
+        act = plain.ACTIVATIONS["gelu" if i % 2 else "gelu_new"]
+        x = x + plain.linear(act(plain.linear(h, t[f"l{i}.fc.w"], t[f"l{i}.fc.b"])), t[f"l{i}.pr.w"], t[f"l{i}.pr.b"])
+    return plain.tied_head(plain.layer_norm(x, t["nf.g"], t["nf.b"], 1e-5), t["emb"])
+
+
+@pytest.mark.parametrize("n_requests", [1, 5, 13, 30, 64])
+@pytest.mark.parametrize("shape", [(64, 4, 2, 32, 80, (0, 12, 0), 8), (192, 3, 3, 64, 448, (0, 0), 16), (128, 8, 1, 16, 256, (7, 0), 4)],
+                         ids=["grouped_heads_of_32_with_a_window", "heads_of_64", "eight_query_heads_to_a_kv_head"])
+def test_a_decode_steps_layers_as_one_resident_kernel(shape, n_requests):
+    """Batches of one new token per row run all layers as ONE kernel whose CTAs stay resident, with
+    grid barriers between a layer's phases. Requests of different lengths are prefilled (part by part)
+    and then decoded for many steps, once through the resident kernel and once with every part
+    launching its own kernels; both against a dense pass of the plain implementation. Grouped heads,
+    a windowed layer beside full ones (two cache groups), 1 to 64 rows (one to eight token tiles), pages
+    that are used again after a request has ended, unwritten slots holding inf."""
+    from research_2_b200.cache.manager import CacheManager
+    from research_2_b200.engine.step import StepFunction
+    from research_2_b200.kernels import ops
+    from research_2_b200.models.decoder import DecoderModel
+
+    d, heads, kv, hd, f, windows, page = shape
+    v, n_layers, n_decode = 211, len(windows), 24
+    tensors = resident_tensors(d, v, n_layers, heads, kv, hd, f)
+    model = DecoderModel(resident_spec(d, v, n_layers, heads, kv, hd, f, windows), tensors, rt(torch.bfloat16))
+    gen = torch.Generator().manual_seed(n_requests)
+    lengths = [int(torch.randint(1, 100, (1,), generator=gen)) + n_decode for _ in range(n_requests)]
+    ids = [torch.randint(0, v, (n,), generator=gen).tolist() for n in lengths]
+    want = [resident_plain(tensors, seq, n_layers, heads, kv, hd, windows).numpy() for seq in ids]
+    results = {}
+    for resident in (True, False):
+        before, uses = ops.use_resident_decode(resident), ops.kernel_uses().get("decode_resident", 0)
+        try:
+            pages = sum(-(-n // page) for n in lengths) + 2
+            step_fn = StepFunction(model, page, pages, n_requests)
+            cache = CacheManager(step_fn.cache_groups(), n_requests, 160)
+            step_fn.arena.fill_(float("inf"))
+            out = [[] for _ in ids]
+            for r, seq in enumerate(ids):   # prompts, one request a step
+                cache.open(r)
+                n = len(seq) - n_decode
+                cache.reserve(r, 0, n)
+                batch = step_fn.new_batch(n, 1, n)
+                batch.set_entries([r], [0], [seq[:n]])
+                cache.fill(batch)
+                batch.set_logit_rows(list(range(n)))
+                out[r].append(step_fn(batch).float().cpu().numpy())
+            for i in range(n_decode):        # then all requests together, one token each
+                reqs = list(range(n_requests))
+                for r in reqs:
+                    at = len(ids[r]) - n_decode + i
+                    cache.slide(r, at)
+                    cache.reserve(r, at, at + 1)
+                batch = step_fn.new_batch(n_requests, n_requests, n_requests, decode_only=True)
+                batch.set_entries(reqs, [len(ids[r]) - n_decode + i for r in reqs], [[ids[r][len(ids[r]) - n_decode + i]] for r in reqs])
+                cache.fill(batch)
+                batch.set_logit_rows(list(range(n_requests)))
+                logits = step_fn(batch).float().cpu().numpy()
+                for r in reqs:
+                    out[r].append(logits[r: r + 1])
+            assert ops.device_errors() == 0
+            used = ops.kernel_uses().get("decode_resident", 0) - uses
+            assert used == (n_decode if resident else 0), f"the resident kernel ran {used} times"
+            results[resident] = [np.concatenate(o) for o in out]
+        finally:
+            ops.use_resident_decode(before)
+    for r in range(n_requests):
+        limit = 4e-2 * max(1.0, np.abs(want[r]).max())
+        for resident in (True, False):
+            got = results[resident][r]
+            assert np.isfinite(got).all(), f"resident={resident}: an unwritten slot leaked into request {r}"
+            err = np.abs(got - want[r]).max(axis=1)
+            other = np.abs(results[not resident][r] - want[r]).max(axis=1)
+            assert err.max() < limit, (f"resident={resident} request {r} of {lengths[r]} tokens: position {int(np.argmax(err >= limit))} is off by "
+                                       f"{err.max():.3g} (limit {limit:.3g}); the other path is off by {other[int(np.argmax(err >= limit))]:.3g} there")
