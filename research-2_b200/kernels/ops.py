@@ -679,8 +679,21 @@ def use_resident_decode(on: bool) -> bool:
     return before
 
 
-def resident_decode_enabled() -> bool:
-    return _resident_decode and _tensor_core_gemm and _fast_attention
+_resident_rows = int(os.environ.get("R2_RESIDENT_ROWS", "8"))
+
+
+def set_resident_decode_rows(n: int) -> int:
+    """The most rows of a decode-only batch that run as the resident kernel (it takes up to 64). The
+    default is 8: up to there it measured faster than the chain of kernels (0.43 against 0.46 ms a step of
+    8 rows at GPT-2 124M sizes, 0.39 against 0.41 for one row), beyond it slower (0.59 ms for 16 rows,
+    1.07 against 0.89 for 64: every CTA reads all rows of a product's input). Returns the previous value."""
+    global _resident_rows
+    before, _resident_rows = _resident_rows, int(n)
+    return before
+
+
+def resident_decode_rows() -> int:
+    return _resident_rows if (_resident_decode and _tensor_core_gemm and _fast_attention) else 0
 
 
 RESIDENT_MAX_GROUPS = 4
@@ -699,12 +712,11 @@ class ResidentLayerC(C.Structure):
 
 class ResidentShapeC(C.Structure):
     _fields_ = [("n_layers", C.c_int), ("width", C.c_int), ("inner", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int),
-                ("n_rows", C.c_int), ("attn_slices", C.c_int)]
+                ("n_rows", C.c_int)]
 
 
 class ResidentBuffersC(C.Structure):
-    _fields_ = [("x", C.c_void_p), ("qkv", C.c_void_p), ("mixed", C.c_void_p), ("hidden", C.c_void_p), ("partial", C.c_void_p),
-                ("attn_o", C.c_void_p), ("attn_ml", C.c_void_p), ("tile_counters", C.c_void_p), ("attn_counters", C.c_void_p),
+    _fields_ = [("x", C.c_void_p), ("qkv", C.c_void_p), ("mixed", C.c_void_p), ("hidden", C.c_void_p),
                 ("barrier", C.c_void_p), ("error_flag", C.c_void_p), ("positions", C.c_void_p), ("seq_lens", C.c_void_p),
                 ("block_tables", C.c_void_p * RESIDENT_MAX_GROUPS), ("slot_mapping", C.c_void_p * RESIDENT_MAX_GROUPS),
                 ("table_width", C.c_int * RESIDENT_MAX_GROUPS), ("stamps", C.c_void_p)]
@@ -728,10 +740,6 @@ def pack_weight_tiles(w: torch.Tensor) -> torch.Tensor:
 
 def decode_resident_library(head_dim: int) -> C.CDLL:
     return _lib_for_head_dim("decode_resident", head_dim)
-
-
-def decode_resident_slices(head_dim: int, n_rows: int, n_kv_heads: int, max_context: int, device) -> int:
-    return int(decode_resident_library(head_dim).r2_decode_resident_slices(n_rows, n_kv_heads, max(max_context, 1), 8 * sm_count(device)))
 
 
 def decode_resident(head_dim: int, layers: torch.Tensor, shape: ResidentShapeC, buffers: ResidentBuffersC, page_shift: int,

@@ -18,6 +18,7 @@ import torch
 from ..cache.arena import MemberSpec
 from ..parts import LayerSpec, PartSpec, Runtime, build_part, registry
 from ..parts.embedding import Head, TokenEmbedding
+from ..kernels.ops import resident_decode_rows as ops_resident_rows
 from ..parts.resident import ResidentLayers
 
 
@@ -115,7 +116,7 @@ class DecoderModel:
         """The residual stream through the schedule, then logits at ctx.logit_rows: [W, V] float32."""
         table = self.positions.additive_table() if self.positions is not None else None
         x = self.embedding.forward(ctx, table)
-        if ctx.decode_only and ctx.n_tokens <= ResidentLayers.MAX_ROWS:
+        if ctx.decode_only and ctx.n_tokens <= ops_resident_rows():
             if not self._resident_tried:
                 self._resident_tried = True
                 self._resident = ResidentLayers.build(self.blocks, self.schedule, self.rt)

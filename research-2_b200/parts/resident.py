@@ -34,7 +34,6 @@ class ResidentLayers:
         self.layers = layers
         lib = ops.decode_resident_library(self.head_dim)
         self.max_rows = min(self.MAX_ROWS, int(lib.r2_decode_resident_max_rows()))
-        max_splits = int(lib.r2_decode_resident_max_splits())
         self.packed = {}
         for i, layer in enumerate(layers):
             if any(e.layer == i for e in schedule):
@@ -44,10 +43,7 @@ class ResidentLayers:
         self.qkv = torch.zeros(rows, qkv_width, **bf16)
         self.mixed = torch.zeros(rows, self.n_heads * self.head_dim, **bf16)
         self.hidden = torch.zeros(rows, self.inner, **bf16)
-        self.partial = torch.zeros(max_splits * rows * self.width, dtype=torch.float32, device=device)
-        self.attn_o = torch.zeros(rows * self.n_heads * 16 * self.head_dim, dtype=torch.float32, device=device)
-        self.attn_ml = torch.zeros(rows * self.n_heads * 16 * 2, dtype=torch.float32, device=device)
-        self.counters = torch.zeros(self.width // 16 + rows * self.n_kv_heads + 2, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)   # the grid barrier's, zero between launches
         self._tables: dict[int, torch.Tensor] = {}   # layer tables by the cache they point into
         self.stamps = None   # profiling: an int64 tensor of 1 + 10 * layers values that CTA 0 fills with the nanosecond clock
 
@@ -97,7 +93,7 @@ class ResidentLayers:
         """x [T, D] float32 through every layer, in place; None where the kernel does not take the
         batch (the caller then walks the parts)."""
         n = x.shape[0]
-        if not (ops.resident_decode_enabled() and ctx.decode_only and 0 < n <= self.max_rows and x.is_contiguous()):
+        if not (ctx.decode_only and 0 < n <= min(self.max_rows, ops.resident_decode_rows()) and x.is_contiguous()):
             return None
         if len(ctx.block_tables) > ops.RESIDENT_MAX_GROUPS:
             return None
@@ -109,15 +105,10 @@ class ResidentLayers:
         shift = size.bit_length() - 1 if len(sizes) == 1 and size & (size - 1) == 0 else -1
         if len(sizes) > 1 and any(s & (s - 1) for s in sizes):
             return None  # the kernel takes one way of splitting a position into page and offset
-        shape = ops.ResidentShapeC(len(self.schedule), self.width, self.inner, self.n_heads, self.n_kv_heads, n,
-                                   ops.decode_resident_slices(self.head_dim, n, self.n_kv_heads, ctx.max_context, self.device))
+        shape = ops.ResidentShapeC(len(self.schedule), self.width, self.inner, self.n_heads, self.n_kv_heads, n)
         b = ops.ResidentBuffersC()
         b.x, b.qkv, b.mixed, b.hidden = x.data_ptr(), self.qkv.data_ptr(), self.mixed.data_ptr(), self.hidden.data_ptr()
-        b.partial, b.attn_o, b.attn_ml = self.partial.data_ptr(), self.attn_o.data_ptr(), self.attn_ml.data_ptr()
-        tiles = self.width // 16
-        b.tile_counters = self.counters.data_ptr()
-        b.attn_counters = self.counters[tiles:].data_ptr()
-        b.barrier = self.counters[tiles + self.max_rows * self.n_kv_heads:].data_ptr()
+        b.barrier = self.counters.data_ptr()
         b.error_flag = ops.error_word(self.device).data_ptr()
         b.positions, b.seq_lens = ctx.positions.data_ptr(), ctx.seq_lens.data_ptr()
         for g, (tables, slots) in enumerate(zip(ctx.block_tables, ctx.slot_mapping)):
