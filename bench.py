@@ -13,7 +13,14 @@ A "step" is one decode step. The default run decodes a batch of 8 requests whose
   prefill    one step of 2,048 prompt tokens (2 x 1,024); frac = flops / time / bf16 peak
   roofline   bytes a decode step must read (every weight once + the live requests' cache)
              / its time, against the measured copy bandwidth
-  points     decode at batch 1 and 64
+  points     decode at batch 1 and 64, and at the headline's batch through the true 32-bit path
+  mixed      64 requests with prompts of 16 to 768 tokens, 256 new tokens each, portions of 512 tokens a
+             step beside the others' decoded tokens, through the Python entry point; with the median
+             and 90th-percentile time to a request's first token
+  kernels    the step's dominant kernels one by one: microseconds and fraction of the measured peak
+
+`--model gpt2-355M` and `--model gpt2-1.5B` run the same at those sizes (the 1.5B decode workload has
+1,000-token prompts and 24 new tokens, which bounds its steps).
 
 Between timed steps nothing is flushed: each step reads weights and cache larger than L2.
 """
@@ -46,6 +53,9 @@ SIZES = {
     "gpt2-1.5B": dict(GPT2_124M, n_layer=48, n_embd=1600, n_head=25, n_inner=6400),
 }
 SEED, PAGE, PROMPT_LEN, CONTEXT = 5, 16, 512, 1024
+# The prompts of each size's decode workload (the 1.5B workload fills the context with 1,000-token prompts
+# and 24 new tokens); `main` sets PROMPT_LEN from it.
+PROMPT_LENS = {"gpt2-124M": 512, "gpt2-355M": 512, "gpt2-1.5B": 1000}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -271,7 +281,9 @@ def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
     engine = Engine.for_model(model, opts)
     gen = torch.Generator().manual_seed(SEED + 200)
     prompts = torch.randint(0, model.vocab_size, (batch, PROMPT_LEN), generator=gen).tolist()
-    rids = [engine.submit(p, max_new_tokens=steps + warmup + 8) for p in prompts]
+    room = CONTEXT - PROMPT_LEN   # tokens a request can still generate
+    steps = max(1, min(steps, room - warmup - 6))   # (requests must stay alive through the timed steps)
+    rids = [engine.submit(p, max_new_tokens=min(steps + warmup + 8, room)) for p in prompts]
     while True:  # prefill until every request decodes
         engine.step()
         if all(engine.scheduler.request_info(r)["n_tokens"] > PROMPT_LEN for r in rids):
@@ -311,12 +323,14 @@ def mixed_point(model, n_requests: int = 64, new_tokens: int = 256) -> dict:
     from research_2_b200.engine.api import generate_with
     from research_2_b200.engine.engine import Engine
 
-    opts = EngineOptions(dtype="bfloat16", max_requests=n_requests, block_size=PAGE, max_batch_tokens=512 + n_requests, capture=True)
+    opts = EngineOptions(dtype="bfloat16", max_requests=n_requests, block_size=PAGE, max_batch_tokens=512 + n_requests, chunk_size=512,
+                         capture=True)
     engine = Engine.for_model(model, opts)
     rng = random.Random(SEED + 300)
     gen = torch.Generator().manual_seed(SEED + 300)
     prompts = [torch.randint(0, model.vocab_size, (rng.randint(16, 768),), generator=gen).tolist() for _ in range(n_requests)]
     generate_with(engine, prompts, new_tokens, wait=False)
+    engine.request_events()  # (the first pass's records)
     engine.keep_events = True
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -324,10 +338,39 @@ def mixed_point(model, n_requests: int = 64, new_tokens: int = 256) -> dict:
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     steps = len(engine.events)
+    records = engine.request_events()
+    preempted = sum(e.n_preempted for e in engine.events)
     engine.close()
     n_out, n_in = sum(len(o) for o in out), sum(len(p) for p in prompts)
+    ttft = sorted(r.time_to_first_token_ms for r in records if r.time_to_first_token_ms is not None)
     return {"generated_per_s": n_out / dt, "tokens_per_s": (n_in + n_out) / dt, "requests": n_requests,
-            "prompt_tokens": n_in, "generated_tokens": n_out, "steps": steps, "ms": dt * 1e3}
+            "prompt_tokens": n_in, "generated_tokens": n_out, "steps": steps, "ms": dt * 1e3, "preemptions": preempted,
+            "ttft_ms_median": statistics.median(ttft) if ttft else None, "ttft_ms_p90": ttft[int(0.9 * (len(ttft) - 1))] if ttft else None}
+
+
+def kernel_points(cfg, batch: int, pk: dict) -> dict:
+    """The step's dominant kernels one by one at this configuration's sizes, each timed in a CUDA graph of
+    20 launches: microseconds, and the fraction of the measured peak that its bytes (decode: the weights or
+    the cache it must read) or its flops (prefill at 2,048 tokens) make of that time."""
+    import torch
+    from research_2_b200.profiling import kernel_cases
+
+    kernel_cases.configure(cfg.n_embd, cfg.n_inner, cfg.n_head, cfg.head_dim, cfg.vocab_size, PAGE)
+    out = {}
+    for name, fn, n_bytes, flops in kernel_cases.cases(batch):
+        wanted = (name.startswith("decode: ") and "sampling at" not in name and f"{batch} rows x {cfg.n_head} heads" in name or
+                  name.startswith("decode: ") and " x " in name and "rows" not in name or
+                  name.startswith(f"logits, {batch} rows") or name.startswith("decode: greedy") or
+                  name.startswith("prefill") and "2,048" in name or "2 x 1,024" in name and "tcgen05" in name)
+        if not wanted:
+            continue
+        us = kernel_cases.time_in_graph(fn)
+        if n_bytes:
+            out[name] = {"us": round(us, 2), "GB/s": round(n_bytes / us / 1e3, 1), "frac": round(n_bytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        else:
+            out[name] = {"us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+    torch.cuda.empty_cache()
+    return out
 
 
 def main() -> int:
@@ -348,13 +391,15 @@ def main() -> int:
         args.warmup = 3
     if args.layers is None:
         args.layers = SIZES[args.model]["n_layer"]
+    global PROMPT_LEN
+    PROMPT_LEN = PROMPT_LENS[args.model]
     steps = min(args.steps, CONTEXT - PROMPT_LEN - args.warmup)
     if args.impl == "reference":
         from baseline import reference_arm
 
         cfg_data = SIZES[args.model]
         skeleton = {
-            "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, 512-token prompts)", "value": None, "unit": "tokens/s",
+            "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, {PROMPT_LEN}-token prompts)", "value": None, "unit": "tokens/s",
             "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random weights (seed 5)", "impl": "reference",
             "config": {"model": args.model, "n_layer": cfg_data["n_layer"], "n_layer_model": cfg_data["n_layer"], "n_embd": cfg_data["n_embd"],
@@ -383,7 +428,7 @@ def main() -> int:
     torch.cuda.empty_cache()
 
     line = {
-        "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, 512-token prompts)", "value": value, "unit": "tokens/s",
+        "metric": f"decode tokens/s (GPT-2 {args.model[5:]}, batch {args.batch}, {PROMPT_LEN}-token prompts)", "value": value, "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random weights (seed 5)",
         "impl": "ours",
@@ -410,6 +455,15 @@ def main() -> int:
             torch.cuda.empty_cache()
         line["points"] = points
         line["mixed"] = mixed_point(model)
+        torch.cuda.empty_cache()
+        line["kernels"] = kernel_points(cfg, args.batch, pk)
+        # the true 32-bit path of the same model (CUDA-core products and attention, no tensor cores)
+        del model
+        torch.cuda.empty_cache()
+        model32, _ = build_model(args.layers, dtype="float32", size=args.model)
+        v32, ms32, lp, _ = decode_point(model32, args.batch, min(steps, 24), args.warmup)
+        points[f"decode_b{args.batch}_float32"] = v32
+        del lp
     print(json.dumps(line))
     return 0
 

@@ -1,18 +1,23 @@
-"""Runs each hot kernel twice at benchmark shapes (GPT-2 124M), for ncu to capture:
+"""Runs the hot kernels of a decoder of given layer sizes, each case twice, for ncu to capture one
+kernel at a time (a few launches, one kernel name: a capture that ends by itself):
 
-    ncu --set full --clock-control none -k regex:'gemm_tc|mlp_fused|decode_kernel|prefill' -c 40 \
-        -o kernels python -m research_2_b200.profiling.kernel_cases
+    python -m research_2_b200.profiling.kernel_cases --width 768 --inner 3072 --heads 12 --head-dim 64 \
+        --vocab 50257 --case "qkv product, 2,048" &&
+    ncu --set full --clock-control none -k regex:gemm_tc -c 2 -o qkv \
+        python -m research_2_b200.profiling.kernel_cases --width 768 --inner 3072 --heads 12 --head-dim 64 \
+        --vocab 50257 --case "qkv product, 2,048"
 
-With `--time` it instead times each case inside a CUDA graph of 20 launches (CUDA events around
-two replays; the same buffers every launch, so whatever fits the L2 stays there) and prints
-microseconds per launch.
+The sizes are arguments: nothing about a model lives here (bench.py passes its configuration's).
+`--case TEXT` keeps the cases whose name contains TEXT; `--list` prints the names. With `--time`
+each case is timed inside a CUDA graph of 20 launches (CUDA events around two replays; the same
+buffers every launch, so whatever fits the L2 stays there) and microseconds per launch are printed.
 
-Shapes: prefill products at 2,048 tokens (QKV and the MLP's first product with gelu) and at 8,192
-tokens (the same two: persistent CTA pairs), the tied logits product for 8 and 64 rows (77 MB of
-weights), a decode step's kernels at 8 rows, decode attention for 64 rows at context 640 (126 MB of cache), prefill attention for
-2 x 1,024 and 8 x 1,024 tokens (the tcgen05 kernel `prefill_tc_kernel`, then the mma.sync kernel
-`prefill_kernel`).
+Cases: prefill products at 2,048 and 8,192 tokens (q/k/v; the feed-forward's first product with its
+activation), the logits product for 8 and 64 rows, a decode step's kernels at 8 rows (products with the
+LayerNorm inside, attention with cache write, sampling), decode attention for 64 rows at context 640,
+prefill attention for 2 x 1,024 and 8 x 1,024 tokens (the tcgen05 kernel, then the mma.sync kernel).
 """
+import argparse
 import sys
 
 import torch
@@ -20,7 +25,8 @@ import torch
 from ..kernels import ops
 
 dev = "cuda:0"
-D, F, H, HD, V, PS = 768, 3072, 12, 64, 50257, 16
+D = F = H = HD = V = 0   # set from the arguments
+PS = 16
 
 
 def paged(batch):
@@ -32,77 +38,73 @@ def paged(batch):
     return flat, flat[H * PS * HD:], tables, page_stride, n_pages
 
 
-def cases():
-    """(name, function) pairs; every function launches the kernels of one case once."""
+def cases(rows: int = 8):
+    """(name, function, bytes that the case must read, flops) tuples; every function launches the
+    kernels of one case once. `rows` is the batch of the decode cases."""
     torch.manual_seed(0)
+    Q = H * HD
     x = torch.randn(2048, D, device=dev).bfloat16()
-    wqkv = (torch.randn(D, 3 * D, device=dev) * 0.02).bfloat16()
+    wqkv = (torch.randn(D, 3 * Q, device=dev) * 0.02).bfloat16()
     wfc = (torch.randn(D, F, device=dev) * 0.02).bfloat16()
-    wte = (torch.randn(V, D, device=dev) * 0.02).bfloat16()
-    bias = torch.zeros(F, device=dev)
-    bqkv = bias[: 3 * D].contiguous()
-    x8k = torch.randn(8192, D, device=dev).bfloat16()
-    x8, x64 = x[:8].contiguous(), x[:64].contiguous()
-    out = [
-        ("qkv product, 2,048 x 768 x 2,304", lambda: ops.linear(x, wqkv, bqkv)),
-        ("fc product with gelu, 2,048 x 768 x 3,072", lambda: ops.linear(x, wfc, bias, act="gelu_new")),
-        ("qkv product, 8,192 x 768 x 2,304", lambda: ops.linear(x8k, wqkv, bqkv)),
-        ("fc product with gelu, 8,192 x 768 x 3,072", lambda: ops.linear(x8k, wfc, bias, act="gelu_new")),
-        ("logits, 8 rows x 768 x 50,257", lambda: ops.linear(x8, wte, None, w_is_nk=True, out_dtype=torch.float32)),
-        ("logits, 64 rows x 768 x 50,257", lambda: ops.linear(x64, wte, None, w_is_nk=True, out_dtype=torch.float32)),
-    ]
-    # a decode step's kernels at 8 rows (the products of one layer, the fused attention, sampling)
-    h8 = torch.randn(8, D, device=dev)  # the residual stream is float32
-    gamma, beta = torch.ones(D, device=dev), torch.zeros(D, device=dev)
-    wproj = (torch.randn(D, D, device=dev) * 0.02).bfloat16()
+    wproj = (torch.randn(Q, D, device=dev) * 0.02).bfloat16()
     wproj2 = (torch.randn(F, D, device=dev) * 0.02).bfloat16()
-    a8 = torch.randn(8, D, device=dev).bfloat16()
-    f8 = torch.randn(8, F, device=dev).bfloat16()
-    bd = bias[:D].contiguous()
-    normed = lambda: ops.NormedRows(h8, gamma, beta, 1e-5, torch.bfloat16)
+    wte = (torch.randn(V, D, device=dev) * 0.02).bfloat16()
+    bf, bqkv, bd = torch.zeros(F, device=dev), torch.zeros(3 * Q, device=dev), torch.zeros(D, device=dev)
+    x8k = torch.randn(8192, D, device=dev).bfloat16()
+    h2k = torch.randn(2048, F, device=dev).bfloat16()
+    r2k = torch.randn(2048, D, device=dev)
+    out = []
+    for t, xt in ((2048, x), (8192, x8k)):
+        out += [
+            (f"prefill: qkv product, {t:,} x {D:,} x {3 * Q:,}", lambda xt=xt: ops.linear(xt, wqkv, bqkv), 0, 2 * t * D * 3 * Q),
+            (f"prefill: fc product with gelu, {t:,} x {D:,} x {F:,}", lambda xt=xt: ops.linear(xt, wfc, bf, act="gelu_new"), 0, 2 * t * D * F),
+        ]
     out += [
-        ("decode: LayerNorm + qkv product, 8 x 768 x 2,304", lambda: ops.linear(normed(), wqkv, bqkv)),
-        ("decode: attention output product + residual, 8 x 768 x 768", lambda: ops.linear(a8, wproj, bd, residual=h8)),
-        ("decode: LayerNorm + fc product with gelu, 8 x 768 x 3,072", lambda: ops.linear(normed(), wfc, bias, act="gelu_new")),
-        ("decode: mlp output product + residual, 8 x 3,072 x 768", lambda: ops.linear(f8, wproj2, bd, residual=h8)),
+        (f"prefill: attention output product + residual, 2,048 x {Q:,} x {D:,}", lambda: ops.linear(x[:, :Q].contiguous() if Q != D else x, wproj, bd, residual=r2k), 0, 2 * 2048 * Q * D),
+        (f"prefill: mlp output product + residual, 2,048 x {F:,} x {D:,}", lambda: ops.linear(h2k, wproj2, bd, residual=r2k), 0, 2 * 2048 * F * D),
     ]
-    out.append(("decode: feed-forward in one kernel (off by default), 8 x 768 x 3,072 x 768",
-                lambda: (ops.use_fused_mlp(True), ops.mlp(normed(), wfc, bias, "gelu_new", wproj2, bd, residual=h8), ops.use_fused_mlp(False))))
-    logits8 = torch.randn(8, V, device=dev)
-    zeros_i = torch.zeros(8, dtype=torch.int32, device=dev)
-    ones_i, temp = torch.ones(8, dtype=torch.int32, device=dev), torch.full((8,), 0.8, device=dev)
-    k40 = torch.full((8,), 40, dtype=torch.int32, device=dev)
+    for r in sorted({8, 64, rows}):
+        xr = x[:r].contiguous()
+        out.append((f"logits, {r} rows x {D:,} x {V:,}", lambda xr=xr: ops.linear(xr, wte, None, w_is_nk=True, out_dtype=torch.float32),
+                    wte.numel() * 2, 2 * r * D * V))
+    # a decode step's kernels (the products of one layer with the LayerNorm inside, attention with cache write, sampling)
+    hr = torch.randn(rows, D, device=dev)  # the residual stream is float32
+    gamma, beta = torch.ones(D, device=dev), torch.zeros(D, device=dev)
+    ar = torch.randn(rows, Q, device=dev).bfloat16()
+    fr = torch.randn(rows, F, device=dev).bfloat16()
+    normed = lambda: ops.NormedRows(hr, gamma, beta, 1e-5, torch.bfloat16)
     out += [
-        ("decode: greedy sampling, 8 rows x 50,257", lambda: ops.sample(logits8, temp, ones_i, zeros_i, zeros_i, zeros_i)),
-        ("decode: sampling at temperature 0.8, 8 rows x 50,257", lambda: ops.sample(logits8, temp, zeros_i, zeros_i, zeros_i, zeros_i)),
-        ("decode: sampling at temperature 0.8 with top-k 40, 8 rows x 50,257", lambda: ops.sample(logits8, temp, k40, zeros_i, zeros_i, zeros_i)),
+        (f"decode: LayerNorm + qkv product, {rows} x {D:,} x {3 * Q:,}", lambda: ops.linear(normed(), wqkv, bqkv), wqkv.numel() * 2, 2 * rows * D * 3 * Q),
+        (f"decode: attention output product + residual, {rows} x {Q:,} x {D:,}", lambda: ops.linear(ar, wproj, bd, residual=hr), wproj.numel() * 2, 2 * rows * Q * D),
+        (f"decode: LayerNorm + fc product with gelu, {rows} x {D:,} x {F:,}", lambda: ops.linear(normed(), wfc, bf, act="gelu_new"), wfc.numel() * 2, 2 * rows * D * F),
+        (f"decode: mlp output product + residual, {rows} x {F:,} x {D:,}", lambda: ops.linear(fr, wproj2, bd, residual=hr), wproj2.numel() * 2, 2 * rows * F * D),
     ]
-    batch, ctx_len = 8, 768
-    kc8, vc8, tables8, page_stride8, n_pages8 = paged(batch)
-    qkv8 = torch.randn(batch, 3 * D, device=dev).bfloat16()
-    rows8 = torch.arange(batch, dtype=torch.int32, device=dev)
-    pos8 = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=dev)
-    lens8 = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
-    slots8 = (tables8[:, (ctx_len - 1) // PS] * PS + (ctx_len - 1) % PS).to(torch.int32)
-    out.append(("decode: attention with cache write, 8 rows x 12 heads, context 768",
-                lambda: ops.decode_attention_fused(qkv8[:, :D], qkv8[:, D: 2 * D], qkv8[:, 2 * D:], slots8, kc8, vc8, page_stride8, PS,
-                                                   n_pages8, tables8, rows8, pos8, lens8, H, H, HD, 0.125, 0, 1024)))
-    # decode attention, 64 rows at context 640
-    batch, ctx_len = 64, 640
-    kc, vc, tables, page_stride, n_pages = paged(batch)
-    qkv = torch.randn(batch, 3 * D, device=dev).bfloat16()
-    rows = torch.arange(batch, dtype=torch.int32, device=dev)
-    pos = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=dev)
-    lens = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
-    slots = (tables[:, (ctx_len - 1) // PS] * PS + (ctx_len - 1) % PS).to(torch.int32)
-    out.append(("decode attention, 64 rows x 12 heads, context 640",
-                lambda: ops.decode_attention_fused(qkv[:, :D], qkv[:, D: 2 * D], qkv[:, 2 * D:], slots, kc, vc, page_stride, PS,
-                                                   n_pages, tables, rows, pos, lens, H, H, HD, 0.125, 0, 1024)))
+    logits = torch.randn(rows, V, device=dev)
+    zeros_i = torch.zeros(rows, dtype=torch.int32, device=dev)
+    ones_i, temp = torch.ones(rows, dtype=torch.int32, device=dev), torch.full((rows,), 0.8, device=dev)
+    k40 = torch.full((rows,), 40, dtype=torch.int32, device=dev)
+    out += [
+        (f"decode: greedy sampling, {rows} rows x {V:,}", lambda: ops.sample(logits, temp, ones_i, zeros_i, zeros_i, zeros_i), rows * V * 4, 0),
+        (f"decode: sampling at temperature 0.8, {rows} rows x {V:,}", lambda: ops.sample(logits, temp, zeros_i, zeros_i, zeros_i, zeros_i), rows * V * 4, 0),
+        (f"decode: sampling at temperature 0.8 with top-k 40, {rows} rows x {V:,}", lambda: ops.sample(logits, temp, k40, zeros_i, zeros_i, zeros_i), rows * V * 4, 0),
+    ]
+    for batch, ctx_len in sorted({(rows, 768), (64, 640)}):
+        kc, vc, tables, page_stride, n_pages = paged(batch)
+        qkv = torch.randn(batch, 3 * Q, device=dev).bfloat16()
+        row_ids = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=dev)
+        lens = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
+        slots = (tables[:, (ctx_len - 1) // PS] * PS + (ctx_len - 1) % PS).to(torch.int32)
+        out.append((f"decode: attention with cache write, {batch} rows x {H} heads, context {ctx_len}",
+                    lambda qkv=qkv, slots=slots, kc=kc, vc=vc, page_stride=page_stride, n_pages=n_pages, tables=tables, row_ids=row_ids,
+                    pos=pos, lens=lens: ops.decode_attention_fused(qkv[:, :Q], qkv[:, Q: 2 * Q], qkv[:, 2 * Q:], slots, kc, vc, page_stride,
+                                                                   PS, n_pages, tables, row_ids, pos, lens, H, H, HD, HD**-0.5, 0, 1024),
+                    batch * ctx_len * 2 * Q * 2, 4 * batch * ctx_len * Q))
     # prefill attention, 2 and 8 prompts of 1,024 tokens: the tcgen05 kernel, then the mma.sync one
     for batch in (2, 8):
         n = 1024
         kc, vc, tables, page_stride, n_pages = paged(batch)
-        q = torch.randn(batch * n, D, device=dev).bfloat16()
+        q = torch.randn(batch * n, Q, device=dev).bfloat16()
         row_entry = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(n)
         positions = torch.arange(n, dtype=torch.int32, device=dev).repeat(batch)
         lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
@@ -111,12 +113,13 @@ def cases():
         def attention(tc, q=q, kc=kc, vc=vc, page_stride=page_stride, n_pages=n_pages, tables=tables, row_entry=row_entry,
                       positions=positions, lens=lens, q_start=q_start, batch=batch, n=n):
             before = ops.use_prefill_tc(tc)
-            ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, 0.125, 0,
+            ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, HD**-0.5, 0,
                                 q_start=q_start, n_tiles=batch * n // 64)
             ops.use_prefill_tc(before)
 
-        out.append((f"prefill attention on tcgen05, {batch} x 1,024 tokens x 12 heads", lambda f=attention: f(True)))
-        out.append((f"prefill attention on mma.sync, {batch} x 1,024 tokens x 12 heads", lambda f=attention: f(False)))
+        flops = batch * 4 * Q * n * (n + 1) // 2
+        out.append((f"prefill attention on tcgen05, {batch} x 1,024 tokens x {H} heads", lambda f=attention: f(True), 0, flops))
+        out.append((f"prefill attention on mma.sync, {batch} x 1,024 tokens x {H} heads", lambda f=attention: f(False), 0, flops))
     return out
 
 
@@ -139,11 +142,37 @@ def time_in_graph(fn, launches=20) -> float:
     return start.elapsed_time(end) / (2 * launches) * 1e3
 
 
+def configure(width: int, inner: int, heads: int, head_dim: int, vocab: int, page_size: int = 16) -> None:
+    """The layer sizes that `cases` builds its tensors for."""
+    global D, F, H, HD, V, PS
+    if width < 1 or heads * head_dim < 1:
+        raise ValueError("sizes must be positive")
+    D, F, H, HD, V, PS = width, inner, heads, head_dim, vocab, page_size
+
+
 def main(argv):
-    timed = "--time" in argv
-    for name, fn in cases():
-        if timed:
-            print(f"{time_in_graph(fn):8.1f} us  {name}")
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--width", type=int, required=True)
+    ap.add_argument("--inner", type=int, required=True)
+    ap.add_argument("--heads", type=int, required=True)
+    ap.add_argument("--head-dim", type=int, required=True)
+    ap.add_argument("--vocab", type=int, required=True)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--rows", type=int, default=8, help="the batch of the decode cases")
+    ap.add_argument("--case", default="", help="keep the cases whose name contains this text")
+    ap.add_argument("--list", action="store_true")
+    ap.add_argument("--time", action="store_true")
+    args = ap.parse_args(argv)
+    configure(args.width, args.inner, args.heads, args.head_dim, args.vocab, args.page_size)
+    for name, fn, n_bytes, flops in cases(args.rows):
+        if args.case not in name:
+            continue
+        if args.list:
+            print(name)
+        elif args.time:
+            us = time_in_graph(fn)
+            rate = f"{n_bytes / us / 1e3:7.0f} GB/s" if n_bytes else f"{flops / us / 1e6:7.0f} TFLOP/s"
+            print(f"{us:8.1f} us  {rate}  {name}")
         else:
             fn()
             fn()

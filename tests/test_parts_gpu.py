@@ -397,8 +397,10 @@ def resident_plain(t, ids, n_layers, heads, kv, hd, windows):
 
 
 @pytest.mark.parametrize("n_requests", [1, 5, 13, 30, 64])
-@pytest.mark.parametrize("shape", [(64, 4, 2, 32, 80, (0, 12, 0), 8), (192, 3, 3, 64, 448, (0, 0), 16), (128, 8, 1, 16, 256, (7, 0), 4)],
-                         ids=["grouped_heads_of_32_with_a_window", "heads_of_64", "eight_query_heads_to_a_kv_head"])
+@pytest.mark.parametrize("shape", [(64, 4, 2, 32, 80, (0, 12, 0), 8), (192, 3, 3, 64, 448, (0, 0), 16), (128, 8, 1, 16, 256, (7, 0), 4),
+                                   (64, 4, 4, 16, 6416, (0,), 12)],
+                         ids=["grouped_heads_of_32_with_a_window", "heads_of_64", "eight_query_heads_to_a_kv_head",
+                              "an_inner_width_beyond_what_shared_memory_holds_of_the_rows_and_pages_of_12"])
 def test_a_decode_steps_layers_as_one_resident_kernel(shape, n_requests):
     """Batches of one new token per row run all layers as ONE kernel whose CTAs stay resident, with
     grid barriers between a layer's phases. Requests of different lengths are prefilled (part by part)
