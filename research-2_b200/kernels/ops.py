@@ -149,6 +149,7 @@ def build_all(head_dims=()) -> None:
         _lib_for_head_dim("attention_decode", head_dim)
         if head_dim <= 128:
             _lib_for_head_dim("attention_prefill", head_dim)
+            _lib_for_head_dim("decode_resident", head_dim)
 
 
 _tensor_core_gemm = os.environ.get("R2_GEMM", "tc") != "simt"

@@ -51,6 +51,18 @@ def test_greedy_tiny_a_workload(wide_a):
     assert solo == want, "a request's tokens depend on who it was batched with"
 
 
+def test_pages_of_twelve_tokens_through_the_engine(wide_a):
+    """A page size that is no power of two (positions are split into page and offset by division) through
+    the scheduler, the native batch fill and every kernel, in both precisions' paths, with few pages."""
+    import research_2_b200 as r2
+
+    prompts = [random_tokens(90 + i, n, 512) for i, n in enumerate((1, 13, 40, 25))]
+    want = plain_generate(wide_a, prompts, 20)
+    got = r2.generate(wide_a, prompts, 20, dtype="float32", block_size=12, num_slabs=14, max_requests=3, max_batch_tokens=36)
+    assert got == want
+    assert r2.generate(wide_a, prompts, 20, dtype="float32", block_size=24, max_requests=4, capture=True) == want
+
+
 def test_sampled_tiny_b_workload(wide_b):
     """Six requests, prompts of 3 to 130 tokens, 24 tokens at temperature 0.8 with seed 4, the
     largest prompt prefilled in portions of 48, pages of 8."""
