@@ -901,6 +901,9 @@ __global__ void __launch_bounds__(THREADS, 1) resident_kernel(const Params p) {
       prologue<NT>(p, g, pro, bars, smem);
       ok = barrier_wait(p, target += gridDim.x, &ok_s);
       stamp(p, n_stamps);
+      // The last phase of the last layer occupies a third of the CTAs: the others leave now, and the kernel
+      // behind this one may start on their SMs (it fetches its weights before it waits for this kernel's end).
+      if (which == 3 && l + 1 == p.s.n_layers) pdl_launch_dependents();
       if (ok) ok = gemm_phase<NT>(p, g, pro, bars, smem);
       stamp(p, n_stamps);
     }
