@@ -268,7 +268,8 @@ def test_a_window_group_beside_a_full_one_in_portions_and_long_decoding(dtype):
     # request 0 in portions and then one by one; request 1 joins after request 0 has slid its window
     plan = [[(0, 20)], [(0, 3)], [(0, 29)], [(0, 1)], [(0, 1)], [(0, 2)]] + [[(0, 1)]] * 16
     plan += [[(0, 1), (1, 17)], [(0, 1), (1, 2)], [(0, 1), (1, 16)]] + [[(0, 1), (1, 1)]] * 6
-    plan += [[(0, 1)]] * 14
+    plan += [[(0, 1)]] * 15
+    assert all(sum(n for q, n in sum(plan, []) if q == r) == len(seq) for r, seq in ids.items())
     at = {0: 0, 1: 0}
     got = {0: [], 1: []}
     most_window_pages = 0
