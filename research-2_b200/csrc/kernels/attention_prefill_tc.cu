@@ -85,13 +85,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __shared__ int tile_info[5];  // entry, first row of the tile within it, the entry's first row in the batch, its rows, its length
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;   // heads vary fastest: CTAs start in the order of their tiles, the longest of an entry first
   const int kvh = h / (p.n_heads / p.n_kv_heads);
 
   const uint32_t q_full_a = smem_u32(q_full), kv_full_a = smem_u32(kv_full), kv_empty_a = smem_u32(kv_empty);
   const uint32_t s_ready_a = smem_u32(s_ready), p_ready_a = smem_u32(p_ready), pv_done_a = smem_u32(pv_done), o_done_a = smem_u32(o_done);
   // Which entry and which 128 rows of it this CTA has: tiles are handed out from the end of the
-  // batch. Warp 0 looks through the entries 32 at a time (these read the batch, which no kernel
+  // batch (blockIdx.y counts them). Warp 0 looks through the entries 32 at a time (these read the batch, which no kernel
   // writes), while warp 1 sets up the barriers and the tensor memory.
   if (warp == 1) {
     if (lane == 0) {
@@ -117,7 +117,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (warp == 0) {
-    const int left = int(gridDim.x) - 1 - int(blockIdx.x);
+    const int left = int(gridDim.y) - 1 - int(blockIdx.y);
     int found = -1, row0 = 0, first = 0, rows_of = 0, len_of = 0, before = 0;
     for (int e0 = 0; e0 < p.n_entries && found < 0; e0 += 32) {
       const int e = e0 + lane;
@@ -282,8 +282,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // ---- softmax and output: one thread per row ------------------------------------------------
     const int q = warp & 3;                       // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
     const int row = q * 32 + lane;
-    const bool row_live = row < rows_here;
-    const int pos = pmin + row;
+    // (a row past the entry's last, whose queries are zeros, takes the last row's mask: its result is
+    // finite and never stored, and its thread goes the way of the warp's other threads)
+    const int pos = min(pmin + row, pmax);
     const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
     const float scale2 = p.scale * 1.4426950408889634f;  // scores in units of log2(e): one exp2 per element
     float m_run = -INFINITY, l_run = 0.f;         // the maximum in use and the sum against it
@@ -300,14 +301,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tmem_load32(s_at, s0);
       tmem_load32(s_at + 32u, s1);
       tmem_load_wait();
-      // mask in float: causal, window, and rows past the entry's own
-      const bool all_seen = row_live && j0 + BN - 1 <= pos && (p.window == 0 || j0 > pos - p.window);
-      if (!all_seen) {
+      // mask in float: causal and window. Key c of the tile is seen if lo_c <= c <= hi (plain predicate
+      // logic on two registers: written with && and || over the position this loop took 1,300 cycles a tile).
+      const int hi = pos - j0;
+      const int lo_c = p.window > 0 ? pos - p.window + 1 - j0 : 0;
+      if (hi < BN - 1 || lo_c > 0) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const int ja = j0 + c, jb = j0 + 32 + c;
-          const bool seen_a = row_live && ja <= pos && (p.window == 0 || ja > pos - p.window);
-          const bool seen_b = row_live && jb <= pos && (p.window == 0 || jb > pos - p.window);
+          const bool seen_a = (c <= hi) & (c >= lo_c);
+          const bool seen_b = (c + 32 <= hi) & (c + 32 >= lo_c);
           s0[c] = seen_a ? s0[c] : __float_as_uint(-INFINITY);
           s1[c] = seen_b ? s1[c] : __float_as_uint(-INFINITY);
         }
@@ -465,15 +467,24 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
       !r2::page_map(&mv, v_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD)) {
     return R2_UNSUPPORTED;
   }
-  const size_t smem = 1024 + Q_BYTES + 2 * STAGES * size_t(KV_BYTES) + 16 * 8 + 16;
+  if (n_tiles > 65535) return R2_UNSUPPORTED;
+  size_t smem = 1024 + Q_BYTES + 2 * STAGES * size_t(KV_BYTES) + 16 * 8 + 16;
   static bool configured = false;
+  static int n_sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return R2_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
     if (e != cudaSuccess) return int(e);
     e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  r2_launch(prefill_tc_kernel, dim3(dim3(n_tiles, n_heads)), dim3(THREADS), size_t(smem), stream, mq, mk, mv, p);
+  // Two CTAs share an SM's special-function units and each runs slower for it. With many tiles that is
+  // the better trade (one CTA's softmax under the other's products); with fewer than two per SM the step
+  // waits for the CTA with the most keys, which then should have an SM to itself: the CTA asks for more
+  // than half an SM's shared memory, and the ones that do not fit at first start as the short ones end.
+  if (long(n_tiles) * n_heads <= 2L * n_sms) smem = 120 * 1024;
+  r2_launch(prefill_tc_kernel, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
   return launch_status();
 }
