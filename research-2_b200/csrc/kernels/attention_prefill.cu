@@ -347,13 +347,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           }
         }
       } else {
+        // key k of the tile is seen by a row if lo <= k <= hi (two compares against registers: the same test
+        // written with && and || over the position compiles to a chain of branches per element)
+        const int hi_a = row_a < rows_here ? pos_a - j0 : -1, hi_b = row_b < rows_here ? pos_b - j0 : -1;
+        const int lo_a = p.window > 0 ? pos_a - p.window + 1 - j0 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 - j0 : 0;
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            int j = j0 + nt * 8 + 2 * tq + c;
-            bool va = j <= pos_a && (p.window == 0 || j > pos_a - p.window) && row_a < rows_here;
-            bool vb = j <= pos_b && (p.window == 0 || j > pos_b - p.window) && row_b < rows_here;
+            const int k = nt * 8 + 2 * tq + c;
+            const bool va = (k <= hi_a) & (k >= lo_a);
+            const bool vb = (k <= hi_b) & (k >= lo_b);
             s[nt][c] = va ? s[nt][c] : -INFINITY;
             s[nt][2 + c] = vb ? s[nt][2 + c] : -INFINITY;
             mx_a = fmaxf(mx_a, s[nt][c]);
