@@ -189,8 +189,8 @@ _prefill_tc = {"0": False, "always": "always"}.get(os.environ.get("R2_PREFILL_TC
 
 def use_prefill_tc(on):
     """The tcgen05 prefill attention kernel (head size 64): False, the mma.sync kernel takes
-    every shape; True, the tcgen05 kernel takes batches whose 128-row tiles are at least half
-    full; "always", every batch that it can take (tests). Returns the previous setting."""
+    every shape; True (or "always", which older callers pass), the tcgen05 kernel takes every
+    batch that it can take. Returns the previous setting."""
     global _prefill_tc
     before, _prefill_tc = _prefill_tc, ("always" if on == "always" else bool(on))
     return before
@@ -594,11 +594,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
-    if (q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64
-            and (_prefill_tc == "always" or 2 * n >= 64 * n_tiles)):
+    if q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64:
         # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles, one entry to a
-        # tile. Where most tiles would be mostly empty (single decoded tokens beside a portion: 64 such rows
-        # and 448 of a prompt took 77 us against 39), the mma.sync kernel with its 64-row tiles goes on.
+        # tile. Also where most tiles are mostly empty (single decoded tokens beside a portion: 64 such rows
+        # and 448 of a prompt take 40 us against the mma.sync kernel's 49).
         _need(q_start, "q_start", torch.int32, 1)
         n_entries = q_start.shape[0] - 1
         status = _lib("attention_prefill_tc").r2_attention_prefill_tc(
