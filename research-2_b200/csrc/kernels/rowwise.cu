@@ -122,10 +122,14 @@ layer_norm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ 
     if (k < width) {
       float4 g = *reinterpret_cast<const float4*>(gamma + k);
       float4 b = *reinterpret_cast<const float4*>(beta + k);
-      o[k] = from_float<O>((v[i].x - mean) * inv * g.x + b.x);
-      o[k + 1] = from_float<O>((v[i].y - mean) * inv * g.y + b.y);
-      o[k + 2] = from_float<O>((v[i].z - mean) * inv * g.z + b.z);
-      o[k + 3] = from_float<O>((v[i].w - mean) * inv * g.w + b.w);
+      const float y0 = (v[i].x - mean) * inv * g.x + b.x, y1 = (v[i].y - mean) * inv * g.y + b.y;
+      const float y2 = (v[i].z - mean) * inv * g.z + b.z, y3 = (v[i].w - mean) * inv * g.w + b.w;
+      if constexpr (sizeof(O) == 2) {  // four values, one 8-byte store (rows are multiples of 4 wide and the output 8-byte aligned)
+        __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+        *reinterpret_cast<uint2*>(o + k) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        *reinterpret_cast<float4*>(o + k) = make_float4(y0, y1, y2, y3);
+      }
     }
   }
 }
@@ -135,7 +139,7 @@ extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* g
   if (n_rows <= 0) return R2_OK;
   if (width < 1 || size_t(width) * 4 > 200 * 1024) return R2_BAD_SHAPE;
   const bool aligned = width % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && !(reinterpret_cast<uintptr_t>(gamma) & 15) &&
-                       !(reinterpret_cast<uintptr_t>(beta) & 15);
+                       !(reinterpret_cast<uintptr_t>(beta) & 15) && !(reinterpret_cast<uintptr_t>(out) & 15);
   if (width <= 2048 && aligned && (odtype == R2_F32 || odtype == R2_BF16)) {
     dim3 grid((n_rows + 3) / 4);
     if (odtype == R2_F32) {
