@@ -118,12 +118,17 @@ class StepGraph:
         torch.cuda.synchronize(step_fn.device)
         try:
             self._capture(step_fn)
-        except RuntimeError:
+        except RuntimeError as first:
             # a driver that cannot record programmatic launch edges in a graph: plain edges then
             if not ops.use_programmatic_dependent_launch(False):
                 raise
             torch.cuda.synchronize(step_fn.device)
-            self._capture(step_fn)
+            try:
+                self._capture(step_fn)
+            except RuntimeError as second:
+                # not the launch edges: a part that says `capturable` did what a capture forbids (a copy from
+                # pageable host memory, a synchronisation, an allocation outside the graph's pool)
+                raise RuntimeError(f"the step could not be captured in a CUDA graph: {first}") from second
 
     def _capture(self, step_fn: "StepFunction") -> None:
         self.graph = torch.cuda.CUDAGraph()
