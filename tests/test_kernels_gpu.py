@@ -684,6 +684,39 @@ def test_sampling_rows_split_over_several_ctas(vocab):
         assert got == want
 
 
+def test_top_k_where_the_k_th_value_is_hard_to_find():
+    """Rows made so that the k-th largest value is tied, lies among thousands of equal values (more than
+    the kernel lists in shared memory: it falls back to its selection over the row), sits beside a
+    neighbour one float away, is a zero of either sign, or is -inf; 64 rows of GPT-2's vocabulary so that
+    rows are cut into slices and more CTAs than SMs run. Draws equal the plain sampler's, twice (the
+    counters and bins are left clean)."""
+    vocab, n = 50257, 64
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(n, vocab, generator=g) * 2
+    top_ks = torch.tensor([40, 5, 2, 300] * (n // 4), dtype=torch.int32)
+    logits[1, [7, 30000, 50256, 123, 45000, 9]] = 9.5                      # six tied at the top, k = 5: all six are kept
+    logits[2] = 1.25                                                      # every value equal, k = 2
+    logits[3, :6000] = 3.0                                                # the k-th lies among 6,000 equal values
+    logits[4, 100] = 8.0
+    logits[4, 200:240] = torch.nextafter(torch.tensor(8.0), torch.tensor(0.0))   # one float below
+    logits[5] = -torch.rand(vocab, generator=g) - 1.0                     # k = 5 among negatives, with zeros of both signs on top
+    logits[5, [3, 4]] = 0.0
+    logits[5, [10, 11, 12]] = -0.0
+    logits[6, 50:] = float("-inf")                                        # fewer finite values than k = 2 ... no: 50 finite, k = 2
+    logits[7, 300:] = float("-inf")                                       # exactly k = 300 finite values
+    logits[11, 200:] = float("-inf")                                      # fewer finite values (200) than k = 300
+    temps = torch.tensor([0.8, 1.0, 1.7, 0.3] * (n // 4))
+    key0 = torch.arange(n, dtype=torch.int64) * 104729 % (2**31)
+    key1 = torch.arange(n, dtype=torch.int64) + 5
+    pos = torch.arange(n, dtype=torch.int32) * 7 + 3
+    want = [plain.sample_token(logits[i], float(temps[i]), int(top_ks[i]), (int(key0[i]), int(key1[i])), int(pos[i]))
+            for i in range(n)]
+    for _ in range(2):
+        got = ops().sample(logits.to(DEV), temps.to(DEV), top_ks.to(DEV), key0.to(torch.int32).to(DEV),
+                           key1.to(torch.int32).to(DEV), pos.to(DEV)).tolist()
+        assert got == want, [i for i in range(n) if got[i] != want[i]]
+
+
 def test_top_k_frequencies():
     """Draws with top_k = 3 land on the three largest logits with softmax(top3 / T) frequencies
     (the reference's sampler check: kelpie/scripts/check_build_step.py:101-140)."""
