@@ -289,18 +289,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const float scale2 = p.scale * 1.4426950408889634f;  // scores in units of log2(e): one exp2 per element
     float m_run = -INFINITY, l_run = 0.f;         // the maximum in use and the sum against it
     bool ok = true;
-    for (int it = 0; it < n_tiles; ++it) {
-      const int j0 = j_first + it * BN;
-      const uint32_t s_at = lane_base + uint32_t(it & 1) * 64u;
-      if (ok && !mbar_wait(s_ready_a + uint32_t(it & 1) * 8u, uint32_t(it >> 1) & 1u)) {
+    // A tile's scores are asked for while the tile before it is still being handed over (its P on the way
+    // into tensor memory, the arrival at the barrier): the wait for the scores, their way into the registers
+    // and the store's completion pass under one another instead of one after the other. `fetch` always
+    // issues its loads (past the last tile: of a buffer that exists), so that the registers are defined on
+    // one path only and nothing the compiler adds reads them before the wait at the end of the loop's body.
+    uint32_t s0[32], s1[32];
+    auto fetch = [&](int it) {
+      if (it < n_tiles && ok && !mbar_wait(s_ready_a + uint32_t(it & 1) * 8u, uint32_t(it >> 1) & 1u)) {
         if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
         ok = false;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t s0[32], s1[32];
-      tmem_load32(s_at, s0);
-      tmem_load32(s_at + 32u, s1);
-      tmem_load_wait();
+      const uint32_t at = lane_base + uint32_t(it & 1) * 64u;
+      tmem_load32(at, s0);
+      tmem_load32(at + 32u, s1);
+    };
+    fetch(0);
+    tmem_load_wait();
+    for (int it = 0; it < n_tiles; ++it) {
+      const int j0 = j_first + it * BN;
+      const uint32_t s_at = lane_base + uint32_t(it & 1) * 64u;
       // mask in float: causal and window. Key c of the tile is seen if lo_c <= c <= hi (plain predicate
       // logic on two registers: written with && and || over the position this loop took 1,300 cycles a tile).
       const int hi = pos - j0;
@@ -339,7 +348,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       l_run = l_run * corr + (sum_a + sum_b);
       m_run = m_new;
-      tmem_store32(s_at, pk);  // over the scores this thread has read
       if (it > 0 && __any_sync(0xffffffffu, grow)) {
         // O times the correction, once the product of the previous tile has completed (the warp
         // decides together: every lane's tensor-memory access is one instruction)
@@ -358,6 +366,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tmem_store32(lane_base + 128u + uint32_t(part * 32), o);
         }
       }
+      tmem_store32(s_at, pk);  // over the scores this thread has read
+      fetch(it + 1);           // (the registers of the scores are free)
       if (j0 < lo || j0 + BN - 1 > pmax) {
         // Keys of this tile outside those that any row may see were not copied, or hold whatever
         // their slots held: their p is 0, but the product multiplies, so their value rows must
@@ -374,6 +384,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready_a + uint32_t(it & 1) * 8u);
+      tmem_load_wait();  // the next tile's scores
     }
     // the last product has completed: O / l is the output row
     if (ok && n_tiles > 0 && !mbar_wait(o_done_a, 0)) {
