@@ -86,7 +86,7 @@ class Engine:
     def plan(self) -> Plan | None:
         """The next step's entries, or None when there is nothing to run (the by-hand rung:
         kelpie_engine/sdk/engine.py:585-601). Follow with `commit`."""
-        self.finish()
+        self.finish(want_event=self.keep_events)   # (the record is only built where someone will read it)
         plan = self.scheduler.plan()
         if plan.n_entries == 0:
             self.scheduler.commit([])
@@ -129,13 +129,16 @@ class Engine:
             self.events.append(event)
         return event
 
-    def finish(self) -> StepEvent | None:
-        """Completes a step that `step(wait=False)` launched: waits for its tokens, commits them."""
+    def finish(self, want_event: bool = True) -> StepEvent | None:
+        """Completes a step that `step(wait=False)` launched: waits for its tokens, commits them. Returns the
+        step's record (None if nothing was launched, or with `want_event=False`)."""
         if self._launched is None:
             return None
         graph, n = self._launched
         self._launched = None
         self.commit(graph.tokens_on_host(n))
+        if not want_event:
+            return None
         event = self.scheduler.event()
         if self.keep_events:
             self.events.append(event)

@@ -321,7 +321,8 @@ class Scheduler:
         batch.trusted = True
 
     def commit(self, tokens) -> None:
-        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        if not (isinstance(tokens, np.ndarray) and tokens.dtype == np.int32 and tokens.ndim == 1 and tokens.flags.c_contiguous):
+            tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
         status = self._lib.r2_sched_commit(self._h, tokens.ctypes.data_as(_host.I32P), len(tokens))
         if status == -9:
             raise CommitError("commit without a plan")
