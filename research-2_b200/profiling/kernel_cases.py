@@ -15,7 +15,8 @@ buffers every launch, so whatever fits the L2 stays there) and microseconds per 
 Cases: prefill products at 2,048 and 8,192 tokens (q/k/v; the feed-forward's first product with its
 activation), the logits product for 8 and 64 rows, a decode step's kernels at 8 rows (products with the
 LayerNorm inside, attention with cache write, sampling), decode attention for 64 rows at context 640,
-prefill attention for 2 x 1,024 and 8 x 1,024 tokens (the tcgen05 kernel, then the mma.sync kernel).
+prefill attention (the tcgen05 kernel, then the mma.sync kernel) for 2 x and 8 x 1,024 tokens, one prompt of
+128 to 1,024 tokens, a ragged length, and single decoded tokens beside a portion of a prompt.
 """
 import argparse
 import sys
@@ -63,6 +64,11 @@ def cases(rows: int = 8):
         (f"prefill: attention output product + residual, 2,048 x {Q:,} x {D:,}", lambda: ops.linear(x[:, :Q].contiguous() if Q != D else x, wproj, bd, residual=r2k), 0, 2 * 2048 * Q * D),
         (f"prefill: mlp output product + residual, 2,048 x {F:,} x {D:,}", lambda: ops.linear(h2k, wproj2, bd, residual=r2k), 0, 2 * 2048 * F * D),
     ]
+    h128, r128 = h2k[:128].contiguous(), r2k[:128].contiguous()
+    out.append((f"prefill: mlp output product + residual, 128 x {F:,} x {D:,} (6 tiles: what one SM takes in)",
+                lambda: ops.linear(h128, wproj2, bd, residual=r128), 0, 2 * 128 * F * D))
+    ln_out, ln_g, ln_b = torch.empty(2048, D, device=dev, dtype=torch.bfloat16), torch.ones(D, device=dev), torch.zeros(D, device=dev)
+    out.append((f"prefill: LayerNorm, 2,048 x {D:,}", lambda: ops.layer_norm(r2k, ln_g, ln_b, 1e-5, torch.bfloat16, out=ln_out), 2048 * D * 6, 0))
     for r in sorted({8, 64, rows}):
         xr = x[:r].contiguous()
         out.append((f"logits, {r} rows x {D:,} x {V:,}", lambda xr=xr: ops.linear(xr, wte, None, w_is_nk=True, out_dtype=torch.float32),
@@ -100,26 +106,37 @@ def cases(rows: int = 8):
                     pos=pos, lens=lens: ops.decode_attention_fused(qkv[:, :Q], qkv[:, Q: 2 * Q], qkv[:, 2 * Q:], slots, kc, vc, page_stride,
                                                                    PS, n_pages, tables, row_ids, pos, lens, H, H, HD, HD**-0.5, 0, 1024),
                     batch * ctx_len * 2 * Q * 2, 4 * batch * ctx_len * Q))
-    # prefill attention, 2 and 8 prompts of 1,024 tokens: the tcgen05 kernel, then the mma.sync one
-    for batch in (2, 8):
-        n = 1024
+    # prefill attention: the tcgen05 kernel, then the mma.sync one. 2 and 8 prompts of 1,024 tokens; one prompt of 128 to
+    # 1,024 tokens (every CTA alone on an SM: the time of a key tile and what a CTA costs besides); a length that is no
+    # multiple of 128; single decoded tokens (context 600 and up) beside a portion of a prompt
+    def attention_case(name, entries):   # entries: (rows, context length after them)
+        batch = len(entries)
+        rows = [r for r, _ in entries]
         kc, vc, tables, page_stride, n_pages = paged(batch)
-        q = torch.randn(batch * n, Q, device=dev).bfloat16()
-        row_entry = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(n)
-        positions = torch.arange(n, dtype=torch.int32, device=dev).repeat(batch)
-        lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
-        q_start = torch.arange(batch + 1, dtype=torch.int32, device=dev) * n
+        n = sum(rows)
+        q = torch.randn(n, Q, device=dev).bfloat16()
+        row_entry = torch.cat([torch.full((r,), e, dtype=torch.int32) for e, r in enumerate(rows)]).to(dev)
+        positions = torch.cat([torch.arange(length - r, length, dtype=torch.int32) for r, length in entries]).to(dev)
+        lens = torch.tensor([length for _, length in entries], dtype=torch.int32, device=dev)
+        q_start = torch.tensor([sum(rows[:i]) for i in range(batch + 1)], dtype=torch.int32, device=dev)
+        n_tiles = sum((r + 63) // 64 for r in rows)
 
-        def attention(tc, q=q, kc=kc, vc=vc, page_stride=page_stride, n_pages=n_pages, tables=tables, row_entry=row_entry,
-                      positions=positions, lens=lens, q_start=q_start, batch=batch, n=n):
+        def attention(tc):
             before = ops.use_prefill_tc(tc)
             ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, H, HD, HD**-0.5, 0,
-                                q_start=q_start, n_tiles=batch * n // 64)
+                                q_start=q_start, n_tiles=n_tiles)
             ops.use_prefill_tc(before)
 
-        flops = batch * 4 * Q * n * (n + 1) // 2
-        out.append((f"prefill attention on tcgen05, {batch} x 1,024 tokens x {H} heads", lambda f=attention: f(True), 0, flops))
-        out.append((f"prefill attention on mma.sync, {batch} x 1,024 tokens x {H} heads", lambda f=attention: f(False), 0, flops))
+        flops = sum(4 * Q * (r * (length - r) + r * (r + 1) // 2) for r, length in entries)
+        out.append((f"prefill attention on tcgen05, {name} x {H} heads", lambda: attention(True), 0, flops))
+        out.append((f"prefill attention on mma.sync, {name} x {H} heads", lambda: attention(False), 0, flops))
+
+    attention_case("2 x 1,024 tokens", [(1024, 1024)] * 2)
+    attention_case("8 x 1,024 tokens", [(1024, 1024)] * 8)
+    for n in (128, 512, 1024):
+        attention_case(f"1 x {n:,} tokens", [(n, n)])
+    attention_case("2 x 1,000 tokens", [(1000, 1000)] * 2)
+    attention_case("64 decoded tokens beside a portion of 448", [(1, 600 + i) for i in range(64)] + [(448, 704)])
     return out
 
 
