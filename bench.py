@@ -373,6 +373,44 @@ def kernel_points(cfg, batch: int, pk: dict) -> dict:
     return out
 
 
+def resident_phases(model, batch: int) -> dict:
+    """Where a layer's time goes inside the resident decode kernel (up to 64 rows): the kernel's own clock at
+    the end of every phase and at the exit of every grid barrier (`ResidentLayers.stamps`), taken as the latest
+    CTA's time minus the latest CTA's at the point before, mean over the middle layers, in microseconds."""
+    import torch
+    from research_2_b200.engine.step import StepContext
+    from research_2_b200.kernels import ops
+
+    before = ops.set_resident_decode_rows(64)
+    try:
+        loop = DecodeLoop(model, batch, 40)
+        resident = getattr(model, "_resident", None)
+        if resident is None:
+            return {"unavailable": "the model's layers are not of the kind that the resident kernel runs"}
+        n_layers = len(resident.schedule)
+        n = 1 + 10 * n_layers
+        ctx = StepContext(loop.graph.host, loop.graph.dev, counts=(batch, batch, batch))
+        loop.run(3)
+        for _ in range(3):
+            stamps = torch.zeros(3 * n, dtype=torch.int64, device="cuda:0")
+            stamps[n: 2 * n] = 1 << 62
+            resident.stamps = stamps
+            loop.step_fn.sample(loop.step_fn.forward(ctx), ctx)
+            torch.cuda.synchronize()
+        resident.stamps = None
+        early, late = stamps[n: 2 * n].cpu().tolist(), stamps[2 * n:].cpu().tolist()
+        names = ["A norm + q/k/v", "barrier", "B attention", "barrier", "C output + residual", "barrier", "D norm + feed-forward in", "barrier",
+                 "E feed-forward out + residual", "barrier"]
+        layers = range(min(3, n_layers - 1), max(min(3, n_layers - 1) + 1, n_layers - 1))
+        out = {"rows": batch, "kernel_us": (late[-1] - early[0]) / 1e3, "phases_us": []}
+        for i, name in enumerate(names):
+            spans = [(late[1 + 10 * layer + i] - late[10 * layer + i]) / 1e3 for layer in layers]
+            out["phases_us"].append([name, round(sum(spans) / len(spans), 2)])
+        return out
+    finally:
+        ops.set_resident_decode_rows(before)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -383,6 +421,7 @@ def main() -> int:
     ap.add_argument("--model", default="gpt2-124M", choices=sorted(SIZES), help="layer sizes (the default is the baseline's benchmark configuration)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip prefill, e2e and the batch 1 / 64 points")
+    ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -415,6 +454,9 @@ def main() -> int:
 
     pk, pk_source = peaks()
     model, cfg = build_model(args.layers, size=args.model)
+    if args.phases:
+        print(json.dumps(resident_phases(model, args.batch)))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     before = ops.launch_count()
