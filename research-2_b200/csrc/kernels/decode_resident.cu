@@ -30,11 +30,11 @@
 // the LayerNorm's gain and shift and the bfloat16 input rows come the same way.
 //
 // Attention: a CTA takes a (row, kv head) pair at a time and its eight warps an eighth of the
-// pair's keys each: 32-key tiles through shared memory by 16-byte asynchronous copies (two tiles
-// in flight per warp for head sizes up to 64), scores and outputs by mma.sync with the group's
-// query heads as rows, online softmax in float, the warps' results merged in warp order in
-// shared memory. A tile's rows come by one bulk copy per run of keys that lie in one page and are
-// then spread to padded rows for ldmatrix.
+// pair's keys each: 32-key tiles by 16-byte asynchronous copies straight into padded rows of
+// shared memory (two tiles in flight per warp for head sizes up to 64), scores and outputs by
+// mma.sync with the group's query heads as rows, online softmax in float, the warps' results
+// merged in warp order in shared memory. The newest key's rows and cache slot are fetched at the
+// phase's start by the warp whose keys end with them.
 //
 // Everything that one CTA writes and another reads inside the kernel (x, qkv, mixed, hidden,
 // partial sums) is read with loads that bypass the L1.
@@ -123,13 +123,16 @@ __host__ __device__ constexpr int stage_bytes(int nt) { return nt * 8 * (chunk_k
 __host__ __device__ constexpr int red_bytes(int nt) { return WARPS * nt * 32 * 16; }
 __host__ __device__ constexpr int merge_bytes() { return WARPS * 8 * (HD + 2) * 4; }  // the warps' attention results
 // Shared memory of the product phases: [weight slot 0][input rows][warps' sums][gain, shift][weight
-// slots 1 ...]. Attention's key/value tiles lie over it from 0, the warps' attention results behind them.
+// slots 1 ...]. Attention's key/value tiles lie over it from 0, the warps' attention results and the newest
+// key's and value's rows behind them.
 __host__ __device__ constexpr int hs_off(int) { return WITEM; }
 __host__ __device__ constexpr int red_off(int nt) { return hs_off(nt) + stage_bytes(nt); }
 __host__ __device__ constexpr int lnp_off(int nt) { return red_off(nt) + red_bytes(nt); }
 __host__ __device__ constexpr int slot_off(int nt, int s) { return s == 0 ? 0 : lnp_off(nt) + LNP_BYTES + (s - 1) * WITEM; }
 __host__ __device__ constexpr int merge_off(int) { return ATTN_SMEM; }
-__host__ __device__ constexpr int total_smem(int nt) { return max2(slot_off(nt, w_slots(nt)), ATTN_SMEM + merge_bytes()); }
+__host__ __device__ constexpr int fresh_off(int) { return ATTN_SMEM + merge_bytes(); }   // per warp: the newest key's and value's rows
+__host__ __device__ constexpr int fresh_bytes() { return WARPS * 2 * HD * 2; }
+__host__ __device__ constexpr int total_smem(int nt) { return max2(slot_off(nt, w_slots(nt)), fresh_off(nt) + fresh_bytes()); }
 static_assert(total_smem(1) <= SMEM_LIMIT && total_smem(2) <= SMEM_LIMIT && total_smem(4) <= SMEM_LIMIT && total_smem(8) <= SMEM_LIMIT,
               "the kernel's shared memory must fit an SM's");
 
@@ -258,27 +261,8 @@ __device__ __forceinline__ long long key_row(const Params& p, const R2ResidentLa
 // piece c of row `row` of a tile in shared memory
 __device__ __forceinline__ uint32_t piece(int row, int c) { return uint32_t(row * ROW_BYTES + (c << 4)); }
 
-// The warps' key/value tile buffers arrive by bulk copies, one per run of keys that lie in one page
-// (a page holds a kv head's rows back to back): a lane whose key starts a run issues the run's two copies
-// (keys, values), so a tile of 32 keys in pages of 16 is four copy instructions. The rows land densely at
-// the front of the buffer; `settle_tile` then spreads them to the padded rows that ldmatrix reads without
-// bank conflicts. Their bytes are counted on the mbarrier of (warp, buffer); `phases` holds, per buffer, the
-// parity of the next wait.
-struct KvBars {
-  uint64_t* bar;      // [WARPS][NBUF] mbarriers in shared memory
-  uint32_t phases;    // this warp's
-  int* error_flag;
-  __device__ __forceinline__ uint32_t at(int buf) const { return r2ptx::smem_u32(bar + (threadIdx.x >> 5) * NBUF + buf); }
-  __device__ __forceinline__ bool wait(int buf) {
-    const bool ok = r2ptx::mbar_wait(at(buf), (phases >> buf) & 1u);
-    phases ^= 1u << buf;
-    if (!ok && (threadIdx.x & 31) == 0) atomicMax(error_flag, R2_ERR_TIMEOUT_GRID);
-    return ok;
-  }
-};
-
 // rows of the tile that come from the cache: the keys up to the last one, the newest key apart (its row
-// comes from this step's q/k/v product: `settle_tile` puts it in place)
+// comes from this step's q/k/v product and is put in place once the tile has landed)
 __device__ __forceinline__ int cache_rows(const Unit& un, int tile) {
   const int j0 = un.first + tile * 32;
   const int upto = tile == un.tile_of_new ? un.pos - 1 : un.last;
@@ -286,55 +270,42 @@ __device__ __forceinline__ int cache_rows(const Unit& un, int tile) {
   return n < 0 ? 0 : (n > 32 ? 32 : n);
 }
 
-// Requests a tile's key and value rows from the cache into the warp's buffer `buf`: lane r has found row
-// r's place in the cache (`at`).
-__device__ __forceinline__ void copy_tile(const R2ResidentLayer& L, const Unit& un, uint8_t* my_smem, KvBars& bars, int tile, int buf,
-                                          long long at, int page_shift) {
-  const int lane = threadIdx.x & 31;
-  const bf16* k_cache = reinterpret_cast<const bf16*>(L.k_cache);
-  const bf16* v_cache = reinterpret_cast<const bf16*>(L.v_cache);
-  uint8_t* kd = my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES;
-  uint8_t* vd = my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES;
-  const int n = cache_rows(un, tile);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // what the warp wrote into the buffer before
-  if (lane == 0) r2ptx::mbar_expect_tx(bars.at(buf), uint32_t(n) * uint32_t(2 * HD * 2));
-  __syncwarp();
-  if (lane < n) {
-    const int j = un.first + tile * 32 + lane;
-    const int in_page = page_offset(j, L.page_size, page_shift);
-    if (lane == 0 || in_page == 0) {  // this key starts a run: the rest of its page, or of the tile
-      const int run = min(L.page_size - in_page, n - lane);
-      bulk_copy(r2ptx::smem_u32(kd + lane * (HD * 2)), k_cache + at, uint32_t(run) * (HD * 2), bars.at(buf));
-      bulk_copy(r2ptx::smem_u32(vd + lane * (HD * 2)), v_cache + at, uint32_t(run) * (HD * 2), bars.at(buf));
-    }
-  }
-}
-// After the tile's copies have landed: its rows from dense to padded (all rows are read before any is
-// written), zeros for the rows past the last key, the newest key's row from this step's product.
-__device__ __forceinline__ void settle_tile(const Unit& un, uint8_t* my_smem, int tile, int buf, const bf16* k_new, const bf16* v_new) {
+// Requests a tile's key and value rows from the cache into the warp's buffer `buf`, straight into the padded
+// rows that ldmatrix reads without bank conflicts: 16-byte asynchronous copies, a row's pieces by neighbouring
+// lanes (every instruction of the warp fetches whole 128-byte lines), zeros for the rows past the last key and
+// for the newest key's. Lane r has found row r's place in the cache (`at`); one commit group per tile.
+// (One bulk copy per run of keys in a page, landing densely and spread to the padded rows afterwards, cost the
+// warp 1,000 cycles to issue per tile and another 1,000 to spread.)
+__device__ __forceinline__ void copy_tile(const R2ResidentLayer& L, const Unit& un, uint8_t* my_smem, int tile, int buf, long long at) {
   const int lane = threadIdx.x & 31;
   constexpr int RPI = 32 / VECS;    // rows that one warp-wide 16-byte access covers
   constexpr int TURNS = 32 / RPI;
+  const bf16* k_cache = reinterpret_cast<const bf16*>(L.k_cache);
+  const bf16* v_cache = reinterpret_cast<const bf16*>(L.v_cache);
+  const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
+  const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES);
   const int n = cache_rows(un, tile);
-  const int new_row = tile == un.tile_of_new ? un.pos - (un.first + tile * 32) : -1;
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
+  for (int i = 0; i < TURNS; ++i) {
+    const int row = i * RPI + lane / VECS, c = lane % VECS;
+    const long long from = __shfl_sync(0xffffffffu, at, row);
+    const bool there = row < n && from >= 0;
+    const int bytes = there ? 16 : 0;  // 0 source bytes: zeros
+    const bf16* ks = there ? k_cache + from + c * 8 : k_cache;
+    const bf16* vs = there ? v_cache + from + c * 8 : v_cache;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd + piece(row, c)), "l"(ks), "r"(bytes) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd + piece(row, c)), "l"(vs), "r"(bytes) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// After the tile has landed: the newest key's and value's rows, which this step's q/k/v product made and the
+// warp holds in shared memory (`fresh`: key row, then value row), go into their place.
+__device__ __forceinline__ void place_newest(const Unit& un, uint8_t* my_smem, int tile, int buf, const bf16* fresh) {
+  const int lane = threadIdx.x & 31;
+  if (tile == un.tile_of_new && lane < 2 * VECS) {
+    const int row = un.pos - (un.first + tile * 32), which = lane / VECS, c = lane % VECS;
     uint8_t* base = my_smem + (size_t(buf) * 2 + which) * 32 * ROW_BYTES;
-    const bf16* fresh = which == 0 ? k_new : v_new;
-    uint4 v[TURNS];
-#pragma unroll
-    for (int i = 0; i < TURNS; ++i) {
-      const int row = i * RPI + lane / VECS, c = lane % VECS;
-      if (row < n) v[i] = *reinterpret_cast<const uint4*>(base + row * (HD * 2) + c * 16);
-      else if (row == new_row) v[i] = __ldcg(reinterpret_cast<const uint4*>(fresh) + c);
-      else v[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < TURNS; ++i) {
-      const int row = i * RPI + lane / VECS, c = lane % VECS;
-      *reinterpret_cast<uint4*>(base + row * ROW_BYTES + c * 16) = v[i];
-    }
+    *reinterpret_cast<uint4*>(base + piece(row, c)) = reinterpret_cast<const uint4*>(fresh + which * HD)[c];
   }
   __syncwarp();
 }
@@ -629,7 +600,7 @@ __device__ bool gemm_phase(const Params& p, const Gemm& g, Prologue& pro, Bars& 
 
 // Attention of the layer: a CTA takes (row, kv head) pairs in turn, its warps the pair's keys in eight
 // slices; the slices' results are merged in warp order in shared memory.
-__device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const AttnAhead& ahead, KvBars& bars, uint8_t* smem, float* merge) {
+__device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const AttnAhead& ahead, uint8_t* smem, float* merge, bf16* fresh_rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.s.n_heads / p.s.n_kv_heads;
   const int q_width = p.s.n_heads * HD, kv_width = p.s.n_kv_heads * HD, qkv_stride = q_width + 2 * kv_width;
@@ -651,15 +622,28 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
     const size_t head_off = size_t(kvh) * page_size * HD;
     const bf16* k_new = qkv + size_t(t) * qkv_stride + q_width + size_t(kvh) * HD;
     const bf16* v_new = k_new + kv_width;
+    bf16* fresh = fresh_rows + size_t(warp) * 2 * HD;   // this warp's copy of the newest key's and value's rows
+    const bool has_new = tile_of_new >= tile_begin && tile_of_new < tile_end;
 
     auto issue = [&](int tile, int buf) {
       const int i = tile - tile_begin;
       long long at;
       if (mine && i < AHEAD_TILES) at = i == 0 ? ahead.at[0] : i == 1 ? ahead.at[1] : i == 2 ? ahead.at[2] : ahead.at[3];
       else at = key_row(p, L, un, tile);
-      copy_tile(L, un, my_smem, bars, tile, buf, at, shift);
+      copy_tile(L, un, my_smem, tile, buf, at);
     };
     if (tile_begin < tile_end) issue(tile_begin, 0);
+    // The warp whose keys end with the newest one fetches its rows and its cache slot now: both are needed
+    // again at the end, where a round trip for each would be nobody's but the whole phase's time.
+    int new_slot = -1;
+    if (has_new) {
+      new_slot = p.b.slot_mapping[L.group][t];
+      if (lane < 2 * VECS) {
+        const bf16* from = lane < VECS ? k_new : v_new;
+        reinterpret_cast<uint4*>(fresh)[lane] = __ldcg(reinterpret_cast<const uint4*>(from) + lane % VECS);
+      }
+      __syncwarp();
+    }
 
     uint32_t qf[KS][4];
     {
@@ -682,8 +666,10 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
       const int j0 = first + tile * 32;
       const int buf = NBUF == 2 ? (it & 1) : 0;
       if (NBUF == 2 && tile + 1 < tile_end) issue(tile + 1, buf ^ 1);
-      ok = bars.wait(buf) && ok;  // this tile's rows have landed
-      settle_tile(un, my_smem, tile, buf, k_new, v_new);
+      if (NBUF == 2 && tile + 1 < tile_end) asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's rows have landed
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
+      place_newest(un, my_smem, tile, buf, fresh);
       const uint32_t kt = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
       const uint32_t vt = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES);
       float sc[4][4];  // [8-key tile][row gq: 2 keys, row gq + 8: 2 keys]
@@ -798,19 +784,13 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
       *reinterpret_cast<uint32_t*>(out + size_t(t) * q_width + size_t(h0 + g) * HD + d) = pack_bf16(oa * inv, ob * inv);
     }
     // the newest key and value go into the cache (off the path to the output): the warp whose slice holds them
-    if (tile_of_new >= tile_begin && tile_of_new < tile_end) {
-      const int slot = p.b.slot_mapping[L.group][t];
+    if (has_new) {
+      const int slot = new_slot;
       const int page = slot < 0 ? -1 : page_index(slot, page_size, shift);
-      if (page >= 0 && page < L.n_pages) {
+      if (page >= 0 && page < L.n_pages && lane < 2 * VECS) {
         const size_t dst = size_t(page) * L.page_stride + head_off + size_t(page_offset(slot, page_size, shift)) * HD;
-        const uint32_t* ks = reinterpret_cast<const uint32_t*>(k_new);
-        const uint32_t* vs = reinterpret_cast<const uint32_t*>(v_new);
-        uint32_t* kd = reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(L.k_cache) + dst);
-        uint32_t* vd = reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(L.v_cache) + dst);
-        for (int i = lane; i < HD / 2; i += 32) {
-          kd[i] = __ldcg(ks + i);
-          vd[i] = __ldcg(vs + i);
-        }
+        bf16* to = reinterpret_cast<bf16*>(lane < VECS ? L.k_cache : L.v_cache) + dst;
+        reinterpret_cast<uint4*>(to)[lane % VECS] = reinterpret_cast<const uint4*>(fresh)[lane];
       }
     }
     __syncthreads();  // the warps' results have been read
@@ -860,18 +840,12 @@ __global__ void __launch_bounds__(THREADS, 1) resident_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int ok_s;
   __shared__ __align__(8) uint64_t bar_s[N_BARS];
-  __shared__ __align__(8) uint64_t kv_bar_s[WARPS * NBUF];
-  KvBars kv_bars;
-  kv_bars.bar = kv_bar_s;
-  kv_bars.phases = 0u;
-  kv_bars.error_flag = p.b.error_flag;
   Bars bars;
   bars.bar = bar_s;
   bars.phases = 0u;
   bars.error_flag = p.b.error_flag;
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) r2ptx::mbar_init(r2ptx::smem_u32(bar_s + i), 1);
-    for (int i = 0; i < WARPS * NBUF; ++i) r2ptx::mbar_init(r2ptx::smem_u32(kv_bar_s + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -893,7 +867,7 @@ __global__ void __launch_bounds__(THREADS, 1) resident_kernel(const Params p) {
     ok = barrier_wait(p, target += gridDim.x, &ok_s) && ok;
     stamp(p, n_stamps);
     if (!ok) break;
-    ok = attention_phase(p, L, ahead, kv_bars, smem, reinterpret_cast<float*>(smem + merge_off(NT)));
+    ok = attention_phase(p, L, ahead, smem, reinterpret_cast<float*>(smem + merge_off(NT)), reinterpret_cast<bf16*>(smem + fresh_off(NT)));
     stamp(p, n_stamps);
     for (int which = 1; which < 4 && ok; ++which) {
       barrier_arrive(p);
