@@ -33,7 +33,7 @@
 // pair's keys each: 32-key tiles by 16-byte asynchronous copies straight into padded rows of
 // shared memory (two tiles in flight per warp for head sizes up to 64), scores and outputs by
 // mma.sync with the group's query heads as rows, online softmax in float, the warps' results
-// merged in warp order in shared memory. The newest key's rows and cache slot are fetched at the
+// merged in warp order in shared memory. The newest key's rows and cache slot are asked for at the
 // phase's start by the warp whose keys end with them.
 //
 // Everything that one CTA writes and another reads inside the kernel (x, qkv, mixed, hidden,
@@ -123,16 +123,13 @@ __host__ __device__ constexpr int stage_bytes(int nt) { return nt * 8 * (chunk_k
 __host__ __device__ constexpr int red_bytes(int nt) { return WARPS * nt * 32 * 16; }
 __host__ __device__ constexpr int merge_bytes() { return WARPS * 8 * (HD + 2) * 4; }  // the warps' attention results
 // Shared memory of the product phases: [weight slot 0][input rows][warps' sums][gain, shift][weight
-// slots 1 ...]. Attention's key/value tiles lie over it from 0, the warps' attention results and the newest
-// key's and value's rows behind them.
+// slots 1 ...]. Attention's key/value tiles lie over it from 0, the warps' attention results behind them.
 __host__ __device__ constexpr int hs_off(int) { return WITEM; }
 __host__ __device__ constexpr int red_off(int nt) { return hs_off(nt) + stage_bytes(nt); }
 __host__ __device__ constexpr int lnp_off(int nt) { return red_off(nt) + red_bytes(nt); }
 __host__ __device__ constexpr int slot_off(int nt, int s) { return s == 0 ? 0 : lnp_off(nt) + LNP_BYTES + (s - 1) * WITEM; }
 __host__ __device__ constexpr int merge_off(int) { return ATTN_SMEM; }
-__host__ __device__ constexpr int fresh_off(int) { return ATTN_SMEM + merge_bytes(); }   // per warp: the newest key's and value's rows
-__host__ __device__ constexpr int fresh_bytes() { return WARPS * 2 * HD * 2; }
-__host__ __device__ constexpr int total_smem(int nt) { return max2(slot_off(nt, w_slots(nt)), fresh_off(nt) + fresh_bytes()); }
+__host__ __device__ constexpr int total_smem(int nt) { return max2(slot_off(nt, w_slots(nt)), ATTN_SMEM + merge_bytes()); }
 static_assert(total_smem(1) <= SMEM_LIMIT && total_smem(2) <= SMEM_LIMIT && total_smem(4) <= SMEM_LIMIT && total_smem(8) <= SMEM_LIMIT,
               "the kernel's shared memory must fit an SM's");
 
@@ -298,14 +295,15 @@ __device__ __forceinline__ void copy_tile(const R2ResidentLayer& L, const Unit& 
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
-// After the tile has landed: the newest key's and value's rows, which this step's q/k/v product made and the
-// warp holds in shared memory (`fresh`: key row, then value row), go into their place.
-__device__ __forceinline__ void place_newest(const Unit& un, uint8_t* my_smem, int tile, int buf, const bf16* fresh) {
+// After the tile has landed: the newest key's and value's rows, which this step's q/k/v product made and
+// the warp's first lanes hold a 16-byte piece each of (`fresh`: the key's pieces, then the value's), go into
+// their place.
+__device__ __forceinline__ void place_newest(const Unit& un, uint8_t* my_smem, int tile, int buf, const uint4& fresh) {
   const int lane = threadIdx.x & 31;
   if (tile == un.tile_of_new && lane < 2 * VECS) {
     const int row = un.pos - (un.first + tile * 32), which = lane / VECS, c = lane % VECS;
     uint8_t* base = my_smem + (size_t(buf) * 2 + which) * 32 * ROW_BYTES;
-    *reinterpret_cast<uint4*>(base + piece(row, c)) = reinterpret_cast<const uint4*>(fresh + which * HD)[c];
+    *reinterpret_cast<uint4*>(base + piece(row, c)) = fresh;
   }
   __syncwarp();
 }
@@ -600,7 +598,7 @@ __device__ bool gemm_phase(const Params& p, const Gemm& g, Prologue& pro, Bars& 
 
 // Attention of the layer: a CTA takes (row, kv head) pairs in turn, its warps the pair's keys in eight
 // slices; the slices' results are merged in warp order in shared memory.
-__device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const AttnAhead& ahead, uint8_t* smem, float* merge, bf16* fresh_rows) {
+__device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const AttnAhead& ahead, uint8_t* smem, float* merge) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.s.n_heads / p.s.n_kv_heads;
   const int q_width = p.s.n_heads * HD, kv_width = p.s.n_kv_heads * HD, qkv_stride = q_width + 2 * kv_width;
@@ -622,7 +620,6 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
     const size_t head_off = size_t(kvh) * page_size * HD;
     const bf16* k_new = qkv + size_t(t) * qkv_stride + q_width + size_t(kvh) * HD;
     const bf16* v_new = k_new + kv_width;
-    bf16* fresh = fresh_rows + size_t(warp) * 2 * HD;   // this warp's copy of the newest key's and value's rows
     const bool has_new = tile_of_new >= tile_begin && tile_of_new < tile_end;
 
     auto issue = [&](int tile, int buf) {
@@ -633,16 +630,14 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
       copy_tile(L, un, my_smem, tile, buf, at);
     };
     if (tile_begin < tile_end) issue(tile_begin, 0);
-    // The warp whose keys end with the newest one fetches its rows and its cache slot now: both are needed
-    // again at the end, where a round trip for each would be nobody's but the whole phase's time.
+    // The warp whose keys end with the newest one asks for its rows (a 16-byte piece a lane) and its cache
+    // slot now: both are needed again at the end, where a round trip for each would be nobody's but the whole
+    // phase's time. (They are first used when the tile that holds them has landed.)
     int new_slot = -1;
+    uint4 fresh = make_uint4(0u, 0u, 0u, 0u);
     if (has_new) {
       new_slot = p.b.slot_mapping[L.group][t];
-      if (lane < 2 * VECS) {
-        const bf16* from = lane < VECS ? k_new : v_new;
-        reinterpret_cast<uint4*>(fresh)[lane] = __ldcg(reinterpret_cast<const uint4*>(from) + lane % VECS);
-      }
-      __syncwarp();
+      if (lane < 2 * VECS) fresh = __ldcg(reinterpret_cast<const uint4*>(lane < VECS ? k_new : v_new) + lane % VECS);
     }
 
     uint32_t qf[KS][4];
@@ -790,7 +785,7 @@ __device__ bool attention_phase(const Params& p, const R2ResidentLayer& L, const
       if (page >= 0 && page < L.n_pages && lane < 2 * VECS) {
         const size_t dst = size_t(page) * L.page_stride + head_off + size_t(page_offset(slot, page_size, shift)) * HD;
         bf16* to = reinterpret_cast<bf16*>(lane < VECS ? L.k_cache : L.v_cache) + dst;
-        reinterpret_cast<uint4*>(to)[lane % VECS] = reinterpret_cast<const uint4*>(fresh)[lane];
+        reinterpret_cast<uint4*>(to)[lane % VECS] = fresh;
       }
     }
     __syncthreads();  // the warps' results have been read
@@ -867,7 +862,7 @@ __global__ void __launch_bounds__(THREADS, 1) resident_kernel(const Params p) {
     ok = barrier_wait(p, target += gridDim.x, &ok_s) && ok;
     stamp(p, n_stamps);
     if (!ok) break;
-    ok = attention_phase(p, L, ahead, smem, reinterpret_cast<float*>(smem + merge_off(NT)), reinterpret_cast<bf16*>(smem + fresh_off(NT)));
+    ok = attention_phase(p, L, ahead, smem, reinterpret_cast<float*>(smem + merge_off(NT)));
     stamp(p, n_stamps);
     for (int which = 1; which < 4 && ok; ++which) {
       barrier_arrive(p);
