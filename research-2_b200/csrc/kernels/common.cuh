@@ -64,6 +64,16 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.f + tanhf(inner));
 }
 
+// gelu_new with the hardware's tanh (relative error about 2^-11, below bfloat16's rounding).
+__device__ __forceinline__ float gelu_tanh_hw(float x) {
+  const float x2 = x * x;
+  const float u = x * fmaf(x2, 0.7978845608028654f * 0.044715f, 0.7978845608028654f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
 }

@@ -569,17 +569,31 @@ __device__ bool gemm_phase(const Params& p, const Gemm& g, Prologue& pro, Bars& 
           const float4 part = red[(w * NT + nt) * 32 + lane];
           v[0] += part.x; v[1] += part.y; v[2] += part.z; v[3] += part.w;
         }
+        // What the sums are added to: the first two units' bias and residual values came before the barrier.
+        // (A third unit fetches them here, in a branch of its own: as the last arm of a selection the compiler
+        // makes the loads unconditional, and every unit paid a round trip for values it already had.)
+        float add[4];
+        if (unit < 2) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            add[i] = unit == 0 ? pro.bias[0][i >> 1] : pro.bias[1][i >> 1];
+            if (g.residual) add[i] += unit == 0 ? pro.res[0][i] : pro.res[1][i];
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int n = it.tile * 16 + gq + 8 * (i >> 1), tok = nt * 8 + 2 * tq + (i & 1);
+            add[i] = __ldg(g.bias + n);
+            if (g.residual && tok < p.s.n_rows) add[i] += __ldcg(p.b.x + size_t(tok) * g.N + n);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int n = it.tile * 16 + gq + 8 * (i >> 1), tok = nt * 8 + 2 * tq + (i & 1);
           if (tok < p.s.n_rows) {
-            const float y = v[i] + (unit == 0 ? pro.bias[0][i >> 1] : unit == 1 ? pro.bias[1][i >> 1] : __ldg(g.bias + n));
-            if (g.residual) {
-              float* xp = p.b.x + size_t(tok) * g.N + n;
-              *xp = (unit == 0 ? pro.res[0][i] : unit == 1 ? pro.res[1][i] : __ldcg(xp)) + y;
-            } else {
-              g.out[size_t(tok) * g.out_stride + n] = __float2bfloat16_rn(activate(y, g.act));
-            }
+            const float y = v[i] + add[i];
+            if (g.residual) p.b.x[size_t(tok) * g.N + n] = y;
+            else g.out[size_t(tok) * g.out_stride + n] = __float2bfloat16_rn(g.act == R2_ACT_GELU_TANH ? gelu_tanh_hw(y) : activate(y, g.act));  // (bfloat16 output: the hardware's tanh, as the tcgen05 product's epilogue)
           }
         }
       }

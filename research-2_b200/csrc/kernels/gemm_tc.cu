@@ -329,16 +329,6 @@ __device__ __forceinline__ uint4 ld_shared16(uint32_t addr) {
   return v;
 }
 
-// gelu_new with the hardware's tanh (relative error about 2^-11, below bfloat16's rounding).
-__device__ __forceinline__ float gelu_tanh_hw(float x) {
-  const float x2 = x * x;
-  const float u = x * fmaf(x2, 0.7978845608028654f * 0.044715f, 0.7978845608028654f);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-  const float hx = 0.5f * x;
-  return fmaf(hx, t, hx);
-}
-
 // The same load without its wait: several may be in flight before one tmem_wait().
 __device__ __forceinline__ void tmem_load32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
