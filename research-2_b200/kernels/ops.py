@@ -679,14 +679,15 @@ def use_resident_decode(on: bool) -> bool:
     return before
 
 
-_resident_rows = int(os.environ.get("R2_RESIDENT_ROWS", "8"))
+_resident_rows = int(os.environ.get("R2_RESIDENT_ROWS", "16"))
 
 
 def set_resident_decode_rows(n: int) -> int:
     """The most rows of a decode-only batch that run as the resident kernel (it takes up to 64). The
-    default is 8: up to there it measured faster than the chain of kernels (0.43 against 0.46 ms a step of
-    8 rows at GPT-2 124M sizes, 0.39 against 0.41 for one row), beyond it slower (0.59 ms for 16 rows,
-    1.07 against 0.89 for 64: every CTA reads all rows of a product's input). Returns the previous value."""
+    default is 16: up to there it measured faster than the chain of kernels at GPT-2 124M sizes (0.39 against
+    0.46 ms a step of 8 rows, 0.46 against 0.54 at 12, 0.53 against 0.57 at 16), at 24 rows the same (0.62) and
+    beyond it slower (0.73 against 0.69 at 32, 1.07 against 0.88 at 64: every CTA reads all rows of a
+    product's input). Returns the previous value."""
     global _resident_rows
     before, _resident_rows = _resident_rows, int(n)
     return before
