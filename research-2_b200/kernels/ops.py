@@ -310,7 +310,7 @@ def error_word(device) -> torch.Tensor:
 
 def raise_on_device_error(device="cuda:0", code: int | None = None) -> None:
     """Raises KernelTimeout if a kernel on `device` has recorded that a bounded wait ran out, and
-    clears the word so that later steps are judged on their own. `code` is the word's value when the
+    clears the word so that later steps are checked on their own. `code` is the word's value when the
     caller has read it already (a graph's pinned copy); else it is read here (synchronises)."""
     if code is None:
         code = device_errors(device)
