@@ -422,6 +422,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip prefill, e2e and the batch 1 / 64 points")
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
+    ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -456,6 +457,9 @@ def main() -> int:
     model, cfg = build_model(args.layers, size=args.model)
     if args.phases:
         print(json.dumps(resident_phases(model, args.batch)))
+        return 0
+    if args.prefill:
+        print(json.dumps(prefill_point(model, cfg, pk)))
         return 0
     sampler = ClockSampler()
     sampler.start()

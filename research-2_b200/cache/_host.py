@@ -6,7 +6,7 @@ import ctypes as C
 
 from ..csrc.build import host_library
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 I32P = C.POINTER(C.c_int32)
 
 
@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
         "r2_sched_cancel": (i32, [vp, i32]),
         "r2_sched_plan": (i32, [vp, C.POINTER(PlanC)]),
         "r2_sched_fill_step_batch": (i32, [vp, C.POINTER(StepBatchC)]),
+        "r2_step_batch_check": (i32, [C.POINTER(StepBatchC), i32, i32, i32, i32, C.POINTER(GroupSpecC), I32P, i32, I32P]),
         "r2_sched_commit": (i32, [vp, I32P, i32]),
         "r2_sched_poll": (i32, [vp, i32, I32P, i32, I32P, I32P]),
         "r2_sched_stall": (i32, [vp, C.POINTER(StallC)]),

@@ -174,6 +174,50 @@ int32_t r2_sched_plan(void* sched, R2Plan* out) {
 }
 
 int32_t r2_sched_fill_step_batch(void* sched, const R2StepBatch* out) { return SC(sched)->fill_step_batch(*out); }
+int32_t r2_step_batch_check(const R2StepBatch* b, int32_t t, int32_t r, int32_t vocab_size, int32_t max_seq_len,
+                            const R2GroupSpec* groups, const int32_t* table_widths, int32_t n_groups, int32_t* where) {
+  *where = -1;
+  if (t <= 0) return 0;
+  if (t > b->t_cap || r < 1 || r > b->r_cap) return 1;
+  for (int32_t i = 0; i < t; ++i) {
+    const int32_t e = b->row_entry[i];
+    if (e < 0 || e >= r) return 1;
+  }
+  // an entry's rows are its newest positions (the reference asserts this on the device:
+  // kelpie-models/kelpie_models/kernels/ops/paged_attention.py:143-157)
+  for (int32_t i = 0; i < t; ++i) {
+    const int32_t e = b->row_entry[i];
+    const int32_t first = b->q_start[e], end = b->q_start[e + 1];
+    if (i < first || i >= end || b->positions[i] != b->seq_lens[e] - (end - i)) {
+      *where = e;
+      return 2;
+    }
+  }
+  for (int32_t i = 0; i < t; ++i) {
+    if (b->input_ids[i] < 0 || b->input_ids[i] >= vocab_size) return 3;
+  }
+  const int32_t* tables = b->block_tables;
+  for (int32_t g = 0; g < n_groups; ++g) {
+    *where = g;
+    const int32_t page = groups[g].page_size;
+    const int64_t limit = (int64_t(groups[g].num_pages) + 1) * page;
+    const int32_t* slots = b->slot_mapping + size_t(g) * b->t_cap;
+    for (int32_t i = 0; i < t; ++i) {
+      if (slots[i] < page || slots[i] >= limit) return 4;
+    }
+    const int32_t width = table_widths[g];
+    for (int64_t i = 0; i < int64_t(r) * width; ++i) {
+      if (tables[i] < 0 || tables[i] > groups[g].num_pages) return 5;
+    }
+    tables += size_t(b->r_cap) * width;
+  }
+  *where = -1;
+  for (int32_t e = 0; e < r; ++e) {
+    if (b->seq_lens[e] > max_seq_len) return 6;
+  }
+  return 0;
+}
+
 int32_t r2_sched_commit(void* sched, const int32_t* tokens, int32_t n) { return SC(sched)->commit(tokens, n); }
 int32_t r2_sched_poll(void* sched, int32_t id, int32_t* out, int32_t cap, int32_t* finished, int32_t* state) {
   return SC(sched)->poll(id, out, cap, finished, state);

@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define R2_ABI_VERSION 3
+#define R2_ABI_VERSION 4
 
 typedef struct {
   int32_t page_size;
@@ -138,6 +138,13 @@ int32_t r2_sched_plan(void* sched, R2Plan* out);
    per entry (its last row) with its sampling parameters, and inert padding up to the capacities.
    Every index it writes lies inside the pool by construction. Negative on a plan that does not fit. */
 int32_t r2_sched_fill_step_batch(void* sched, const R2StepBatch* out);
+/* Bounds checks of a batch that the caller filled itself, in one pass over its rows: 0 if it is sound, else
+   1 a row names an entry outside the batch, 2 the rows of entry *where are not its newest positions, 3 a token
+   lies outside the vocabulary, 4 a slot of group *where lies outside the pool or in the null page, 5 a block
+   table of group *where names a page outside the pool, 6 an entry reaches beyond max_seq_len.
+   `table_widths` has the width of each group's block table. */
+int32_t r2_step_batch_check(const R2StepBatch* batch, int32_t n_tokens, int32_t n_entries, int32_t vocab_size, int32_t max_seq_len,
+                            const R2GroupSpec* groups, const int32_t* table_widths, int32_t n_groups, int32_t* where);
 int32_t r2_sched_commit(void* sched, const int32_t* tokens, int32_t n);
 int32_t r2_sched_poll(void* sched, int32_t id, int32_t* out, int32_t cap, int32_t* finished, int32_t* state);
 int32_t r2_sched_stall(const void* sched, R2Stall* out);

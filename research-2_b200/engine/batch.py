@@ -14,6 +14,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import ctypes as C
+
 import numpy as np
 
 _ALIGN = 4  # sections start on 16-byte boundaries
@@ -162,21 +164,41 @@ class StepBatch:
         for table in self.block_tables:
             table[r:] = 0
 
-    def check(self) -> None:
-        """Host-side statement of the invariant that the reference asserts on the device
-        (kernels/ops/paged_attention.py:143-157): an entry's rows are its newest positions."""
-        t, r = self.n_tokens, self.n_entries
-        if t == 0:
+    def check(self, limits: "BatchLimits") -> None:
+        """Host-side bounds checks of a batch that the caller filled (there is no device-side
+        sanitizer to lean on), in one native pass over the rows: every row belongs to an entry of
+        the batch and an entry's rows are its newest positions (the invariant that the reference
+        asserts on the device, kernels/ops/paged_attention.py:143-157); token ids lie in the
+        vocabulary; slots and block-table entries lie inside the pool; no entry reaches beyond
+        the longest sequence."""
+        from ..cache import _host
+
+        where = C.c_int32(-1)
+        code = _host.lib().r2_step_batch_check(C.byref(self.native()), self.n_tokens, self.n_entries, limits.vocab_size,
+                                               limits.max_seq_len, limits.groups, limits.table_widths, limits.n_groups, C.byref(where))
+        if code == 0:
             return
-        e = self.row_entry[:t]
-        if e.min() < 0 or e.max() >= r:
+        if code == 1:
             raise AssertionError("a row names an entry outside the batch")
-        rows = np.arange(t, dtype=np.int32)
-        want = self.seq_lens[e] - (self.q_start[1: r + 1][e] - rows)
-        inside = (rows >= self.q_start[:r][e]) & (rows < self.q_start[1: r + 1][e])
-        if not (np.array_equal(self.positions[:t], want) and inside.all()):
-            bad = int(e[np.argmax((self.positions[:t] != want) | ~inside)])
-            raise AssertionError(f"entry {bad}: rows are not its newest positions")
+        if code == 2:
+            raise AssertionError(f"entry {where.value}: rows are not its newest positions")
+        raise ValueError({
+            3: f"a token id lies outside the vocabulary [0, {limits.vocab_size})",
+            4: f"group {where.value}: a slot lies outside the pool or in the null page",
+            5: f"group {where.value}: a block table names a page outside the pool",
+            6: "an entry reaches beyond max_seq_len",
+        }[code])
+
+
+class BatchLimits:
+    """What a batch is checked against, in the native side's types (made once per step function)."""
+
+    def __init__(self, vocab_size: int, max_seq_len: int, groups, table_widths):
+        from ..cache import _host
+
+        self.vocab_size, self.max_seq_len, self.n_groups = int(vocab_size), int(max_seq_len), len(groups)
+        self.groups = (_host.GroupSpecC * len(groups))(*[_host.GroupSpecC(g.page_size, g.window, g.num_pages) for g in groups])
+        self.table_widths = (C.c_int32 * len(groups))(*[int(w) for w in table_widths])
 
 
 def batch_for(table_widths, n_tokens: int, n_entries: int, n_logit_rows: int, pinned: bool = False) -> StepBatch:

@@ -26,7 +26,7 @@ import torch
 from ..cache.arena import KVArena, derive_groups
 from ..cache.manager import GroupSpec
 from ..kernels import ops
-from .batch import BatchLayout, StepBatch
+from .batch import BatchLayout, BatchLimits, StepBatch
 
 
 class StepContext:
@@ -178,6 +178,7 @@ class StepFunction:
         ]
         self.max_requests = max_requests
         self.table_widths = tuple(-(-model.max_seq_len // g.page_size) for g in self.groups)
+        self._limits = BatchLimits(model.vocab_size, model.max_seq_len, self.groups, self.table_widths)
         # A mixer with state of its own folds an entry's rows on the host side of the launch, so
         # only models whose mixers all say `capturable` may run inside a CUDA graph.
         self.capture = capture and all(getattr(b.mixer, "capturable", False) for b in model.blocks)
@@ -248,23 +249,10 @@ class StepFunction:
         return StepContext(batch, dev)
 
     def validate(self, batch: StepBatch) -> None:
-        """Host-side bounds checks (there is no device-side sanitizer to lean on). A batch that the
-        scheduler filled natively is inside the pool by construction and is not checked again."""
-        if batch.trusted:
-            return
-        batch.check()
-        t = batch.n_tokens
-        if t and (batch.input_ids[:t].min() < 0 or batch.input_ids[:t].max() >= self.model.vocab_size):
-            raise ValueError(f"a token id lies outside the vocabulary [0, {self.model.vocab_size})")
-        for g, spec in enumerate(self.groups):
-            limit = (spec.num_pages + 1) * spec.page_size
-            if t and (batch.slot_mapping[g, :t].min() < spec.page_size or batch.slot_mapping[g, :t].max() >= limit):
-                raise ValueError(f"group {g}: a slot lies outside the pool or in the null page")
-            table = batch.block_tables[g][: batch.n_entries]
-            if table.size and (table.min() < 0 or table.max() > spec.num_pages):
-                raise ValueError(f"group {g}: a block table names a page outside the pool")
-        if t and batch.seq_lens[: batch.n_entries].max() > self.model.max_seq_len:
-            raise ValueError("an entry reaches beyond max_seq_len")
+        """Host-side bounds checks of a batch that the caller filled. A batch that the scheduler
+        filled natively is inside the pool by construction and is not checked again."""
+        if not batch.trusted:
+            batch.check(self._limits)
 
     # ---- running ---------------------------------------------------------------------------
     def forward(self, ctx: StepContext) -> torch.Tensor:

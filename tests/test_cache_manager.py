@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from research_2_b200.cache import CacheError, CacheManager, GroupSpec, OutOfPages
-from research_2_b200.engine.batch import batch_for
+from research_2_b200.engine.batch import BatchLimits, batch_for
 
 
 def test_pages_come_in_order_and_never_the_null_page():
@@ -105,11 +105,54 @@ def test_fill_batch_slots_tables_and_state():
     u2 = cm.table(2, 1)
     assert list(b.slot_mapping[1, :3]) == [u2[2] * 2, u2[2] * 2 + 1, u2[3] * 2]
     assert np.array_equal(b.block_tables[0][0], t2) and np.array_equal(b.block_tables[1][1], cm.table(0, 1))
-    b.check()
+    b.check(BatchLimits(100, 16, [GroupSpec(4, 0, 8), GroupSpec(2, 0, 16)], cm.table_widths))
     b2 = batch_for(cm.table_widths, 4, 1, 1)
     b2.set_entries([0], [3], [[1, 2, 3, 4]])  # positions 3..6 were never reserved
     with pytest.raises(OutOfPages):
         cm.fill(b2)
+
+
+def test_a_batch_that_the_caller_filled_is_checked_against_the_pool():
+    """Each refusal of the host-side check, on a batch that is sound but for one value; the second
+    group's arrays lie behind the first's in the buffer."""
+    groups = [GroupSpec(4, 0, 8), GroupSpec(2, 0, 16)]
+    cm = CacheManager(groups, 3, 16)
+    cm.open(2); cm.open(0)
+    cm.reserve(2, 0, 7)
+    cm.reserve(0, 0, 3)
+    b = batch_for(cm.table_widths, 8, 3, 3)  # capacities beyond the counts
+    b.set_entries([2, 0], [4, 0], [[9, 9, 9], [5, 6, 7]])
+    cm.fill(b)
+    b.pad()
+    limits = BatchLimits(10, 16, groups, cm.table_widths)
+    b.check(limits)
+
+    def refused(array, index, value, error, text):
+        before = array[index]
+        array[index] = value
+        with pytest.raises(error, match=text):
+            b.check(limits)
+        array[index] = before
+        b.check(limits)
+
+    refused(b.row_entry, 4, 2, AssertionError, "a row names an entry outside the batch")
+    refused(b.row_entry, 4, -1, AssertionError, "a row names an entry outside the batch")
+    refused(b.row_entry, 3, 0, AssertionError, "entry 0: rows are not its newest positions")
+    refused(b.positions, 5, 3, AssertionError, "entry 1: rows are not its newest positions")
+    refused(b.seq_lens, 0, 8, AssertionError, "entry 0: rows are not its newest positions")
+    refused(b.input_ids, 2, 10, ValueError, "outside the vocabulary")
+    refused(b.input_ids, 2, -1, ValueError, "outside the vocabulary")
+    refused(b.slot_mapping[0], 1, 3, ValueError, "group 0: a slot lies outside the pool or in the null page")
+    refused(b.slot_mapping[0], 1, 9 * 4, ValueError, "group 0: a slot lies outside the pool")
+    refused(b.slot_mapping[1], 5, 17 * 2, ValueError, "group 1: a slot lies outside the pool")
+    refused(b.block_tables[0], (1, 3), 9, ValueError, "group 0: a block table names a page outside the pool")
+    refused(b.block_tables[1], (0, 7), -1, ValueError, "group 1: a block table names a page outside the pool")
+    with pytest.raises(ValueError, match="beyond max_seq_len"):
+        b.check(BatchLimits(10, 6, groups, cm.table_widths))
+    # (what lies beyond the counts is padding and is not looked at)
+    b.block_tables[1][2, 0] = 99
+    b.slot_mapping[1, 7] = 999
+    b.check(limits)
 
 
 @pytest.mark.parametrize("seed", range(6))
