@@ -17,6 +17,10 @@
 //              The maximum that the exponents are taken against only moves when a tile's maximum
 //              exceeds it by more than 8 (in units of log2): P stays below 2^8, the row's sum
 //              and O keep their scale, and O (in tensor memory) is rescaled only then.
+// With few CTAs for the GPU (a prompt or two) the step waits for the CTA with the most keys, so the
+// kernel then runs as clusters of two: CTA c of a cluster takes the key tiles c, c + 2, c + 4, ... of
+// the same 128 rows on an SM of its own, the second writes its maximum, sum and unnormalised output
+// per row into the first one's shared memory, and after a cluster barrier the first joins the two.
 // A score buffer is overwritten by the scores two tiles on; warp 1 issues that product only when
 // the second product of this tile has completed (products into different accumulators are not
 // ordered by their issue).
@@ -59,6 +63,11 @@ struct Params {
 
 using namespace r2ptx;
 
+// The join buffer in the first CTA's shared memory: [HD outputs, maximum, sum][128 rows] floats, so that a warp's
+// accesses are consecutive.
+constexpr int JOIN_BYTES = (HD + 2) * BM * 4;
+
+template <int SPLIT>
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -67,7 +76,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint8_t* q_s = smem;                                  // [128 rows][64 dims], swizzled
   uint8_t* k_s = q_s + Q_BYTES;                         // STAGES x [64 keys][64 dims]
   uint8_t* v_s = k_s + STAGES * KV_BYTES;               // STAGES x [64 keys][64 dims]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + STAGES * KV_BYTES);
+  float* join_s = reinterpret_cast<float*>(v_s + STAGES * KV_BYTES);   // (SPLIT > 1 only)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + STAGES * KV_BYTES + (SPLIT > 1 ? JOIN_BYTES : 0));
   uint64_t* q_full = bars;                 // the query tile has landed
   uint64_t* kv_full = bars + 1;            // [STAGES] a stage's keys and values have landed
   uint64_t* kv_empty = kv_full + STAGES;   // [STAGES] the second product has read the stage
@@ -85,6 +95,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __shared__ int tile_info[5];  // entry, first row of the tile within it, the entry's first row in the batch, its rows, its length
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chain = SPLIT > 1 ? int(blockIdx.z) : 0;   // the CTA's rank in its cluster (the cluster lies along z)
   const int h = blockIdx.x;   // heads vary fastest: CTAs start in the order of their tiles, the longest of an entry first
   const int kvh = h / (p.n_heads / p.n_kv_heads);
 
@@ -174,6 +185,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
   const int j_first = lo / BN * BN;
   const int n_tiles = (pmax - j_first) / BN + 1;
+  // Rows with few keys stay with the first CTA of the two: the second would cost more than it saves.
+  const bool joined = SPLIT > 1 && n_tiles >= 4;
+  if (SPLIT > 1 && !joined && chain != 0) {
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    return;
+  }
+  // This CTA's tiles: number i of them is tile step * i + chain of the rows, keys from j_of(i) on.
+  const int step = joined ? SPLIT : 1;
+  const int n_mine = (n_tiles - chain + step - 1) / step;
+  auto j_of = [&](int i) { return j_first + (step * i + chain) * BN; };
+
+  // (a softmax thread's running maximum and sum, and whether its waits all came true: they outlive the role's block)
+  float m_run = -INFINITY, l_run = 0.f;
+  bool ok = true;
+  if (joined) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs": waited for before its shared memory is written
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------
@@ -187,24 +213,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (jb + p.box_rows - 1 >= lo && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
       }
     };
-    box_lookup(j_first);
+    if (n_mine > 0) box_lookup(j_of(0));
     pdl_wait();  // the previous kernels wrote the queries and the cache
-    if (lane == 0) {
+    if (lane == 0 && n_mine > 0) {  // (a CTA without tiles asks for nothing: no copy may land after it has gone)
       mbar_expect_tx(q_full_a, Q_BYTES);
       tma_load_2d(smem_u32(q_s), &map_q, h * HD, t0 + r0, q_full_a);
     }
     uint32_t round_parity = 0;
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = 0; it < n_mine; ++it) {
       const int stage = it % STAGES;
       if (it >= STAGES && !mbar_wait(kv_empty_a + stage * 8, round_parity ^ 1u)) {
         if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
         break;
       }
-      const int j0 = j_first + it * BN;
+      const int j0 = j_of(it);
       const bool mine = box_page != INT_MIN;
-      const uint32_t n_mine = __popc(__ballot_sync(0xffffffffu, mine));
+      const uint32_t n_boxes_here = __popc(__ballot_sync(0xffffffffu, mine));
       const uint32_t bar = kv_full_a + stage * 8;
-      if (lane == 0) mbar_expect_tx(bar, 2u * n_mine * box_bytes);  // with no box at all the phase completes at once
+      if (lane == 0) mbar_expect_tx(bar, 2u * n_boxes_here * box_bytes);  // with no box at all the phase completes at once
       __syncwarp();
       if (mine) {
         const int jb = j0 + lane * p.box_rows;
@@ -214,7 +240,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tma_load_4d(smem_u32(k_s) + dst, &map_k, 0, off, kvh, page, bar);
         tma_load_4d(smem_u32(v_s) + dst, &map_v, 0, off, kvh, page, bar);
       }
-      if (it + 1 < n_tiles) box_lookup(j0 + BN);
+      if (it + 1 < n_mine) box_lookup(j_of(it + 1));
       if (stage == STAGES - 1) round_parity ^= 1u;
     }
   } else if (warp == 1) {
@@ -226,7 +252,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t q_at = (smem_u32(q_s) >> 4) & 0x3FFFu;
     const uint32_t k_at = (smem_u32(k_s) >> 4) & 0x3FFFu, v_at = (smem_u32(v_s) >> 4) & 0x3FFFu;
     const uint64_t kmajor = smem_desc(0, 16, 1024), mnmajor = smem_desc(0, BN * 128, 1024);
-    bool ok = mbar_wait(q_full_a, 0);
+    ok = n_mine == 0 || mbar_wait(q_full_a, 0);
     if (!ok && lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
     auto scores = [&](int it) {  // S(it) = Q K(it)^T into score buffer it & 1
       const int stage = it % STAGES;
@@ -246,8 +272,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       __syncwarp();
     };
-    if (ok) scores(0);
-    for (int it = 0; it < n_tiles && ok; ++it) {
+    if (ok && n_mine > 0) scores(0);
+    for (int it = 0; it < n_mine && ok; ++it) {
       // The scores of tile it + 1 go where P of tile it - 1 lies: that second product must have
       // completed (products into different accumulators are not ordered among themselves). It also
       // keeps pv_done at most one phase behind any softmax warp that has these scores, which is
@@ -256,7 +282,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
         break;
       }
-      if (it + 1 < n_tiles) scores(it + 1);  // under the softmax of tile `it`
+      if (it + 1 < n_mine) scores(it + 1);  // under the softmax of tile `it`
       if (!ok) break;
       if (!mbar_wait(p_ready_a + uint32_t(it & 1) * 8u, uint32_t(it >> 1) & 1u)) {
         if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
@@ -274,7 +300,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         umma_commit(kv_empty_a + uint32_t(stage) * 8u);
         umma_commit(pv_done_a);
-        if (it == n_tiles - 1) umma_commit(o_done_a);
+        if (it == n_mine - 1) umma_commit(o_done_a);
       }
       __syncwarp();
     }
@@ -287,8 +313,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int pos = min(pmin + row, pmax);
     const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
     const float scale2 = p.scale * 1.4426950408889634f;  // scores in units of log2(e): one exp2 per element
-    float m_run = -INFINITY, l_run = 0.f;         // the maximum in use and the sum against it
-    bool ok = true;
+    // (m_run: the maximum in use; l_run: the sum against it)
     // A tile's scores are asked for while the tile before it is still being handed over (its P on the way
     // into tensor memory, the arrival at the barrier): the wait for the scores, their way into the registers
     // and the store's completion pass under one another instead of one after the other. `fetch` always
@@ -296,7 +321,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // one path only and nothing the compiler adds reads them before the wait at the end of the loop's body.
     uint32_t s0[32], s1[32];
     auto fetch = [&](int it) {
-      if (it < n_tiles && ok && !mbar_wait(s_ready_a + uint32_t(it & 1) * 8u, uint32_t(it >> 1) & 1u)) {
+      if (it < n_mine && ok && !mbar_wait(s_ready_a + uint32_t(it & 1) * 8u, uint32_t(it >> 1) & 1u)) {
         if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
         ok = false;
       }
@@ -306,9 +331,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       tmem_load32(at + 32u, s1);
     };
     fetch(0);
-    tmem_load_wait();
-    for (int it = 0; it < n_tiles; ++it) {
-      const int j0 = j_first + it * BN;
+    tmem_load_wait(s0);
+    tmem_tie(s1);
+    for (int it = 0; it < n_mine; ++it) {
+      const int j0 = j_of(it);
       const uint32_t s_at = lane_base + uint32_t(it & 1) * 64u;
       // mask in float: causal and window. Key c of the tile is seen if lo_c <= c <= hi (plain predicate
       // logic on two registers: written with && and || over the position this loop took 1,300 cycles a tile).
@@ -360,7 +386,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         for (int part = 0; part < 2; ++part) {
           uint32_t o[32];
           tmem_load32(lane_base + 128u + uint32_t(part * 32), o);
-          tmem_load_wait();
+          tmem_load_wait(o);
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
           tmem_store32(lane_base + 128u + uint32_t(part * 32), o);
@@ -384,29 +410,79 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready_a + uint32_t(it & 1) * 8u);
-      tmem_load_wait();  // the next tile's scores
+      tmem_load_wait(s0);  // the next tile's scores
+      tmem_tie(s1);
     }
-    // the last product has completed: O / l is the output row
-    if (ok && n_tiles > 0 && !mbar_wait(o_done_a, 0)) {
+    // this CTA's last product has completed
+    if (ok && n_mine > 0 && !mbar_wait(o_done_a, 0)) {
       if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ATTN);
       ok = false;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+
+  if (joined) {
+    __syncwarp();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // the other CTA runs
+    if (warp >= 2 && chain != 0) {
+      // the second CTA's row: 64 unnormalised outputs, maximum and sum into the first CTA's join buffer
+      const int q = warp & 3, row = q * 32 + lane;
+      const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(join_s)), "r"(0));
+      remote += uint32_t(row) * 4u;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        uint32_t o[32];
+        tmem_load32(lane_base + 128u + uint32_t(part * 32), o);
+        tmem_load_wait(o);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + uint32_t((part * 32 + c) * BM * 4)), "r"(o[c]) : "memory");
+      }
+      asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + uint32_t(HD * BM * 4)), "r"(__float_as_uint(m_run)) : "memory");
+      asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + uint32_t((HD + 1) * BM * 4)), "r"(__float_as_uint(l_run)) : "memory");
+    }
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+
+  if (warp >= 2 && chain == 0) {
+    // ---- the output rows: (O of this CTA and of the other one, each against its own maximum) / the joint sum ----
+    const int q = warp & 3, row = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+    float w_mine = 1.f, w_other = 0.f, l_all = l_run;
+    if (joined) {
+      const float m_other = join_s[HD * BM + row], l_other = join_s[(HD + 1) * BM + row];
+      const float m_all = fmaxf(m_run, m_other);
+      const float base = m_all == -INFINITY ? 0.f : m_all;
+      w_mine = fast_exp2(m_run - base);
+      w_other = fast_exp2(m_other - base);
+      l_all = l_run * w_mine + l_other * w_other;
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    w_mine *= inv;
+    w_other *= inv;
     // The row goes through the query tile's shared memory (every product that read it has
     // completed), so that the warp's stores to global memory are whole 128-byte rows.
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     const uint32_t o_row = smem_u32(q_s) + uint32_t(row * 128);
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
       uint32_t o[32];
       tmem_load32(lane_base + 128u + uint32_t(part * 32), o);
-      tmem_load_wait();
+      tmem_load_wait(o);
+      float r[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        r[c] = __uint_as_float(o[c]) * w_mine;
+        if (joined) r[c] = fmaf(join_s[(part * 32 + c) * BM + row], w_other, r[c]);
+      }
 #pragma unroll
       for (int c8 = 0; c8 < 4; ++c8) {
-        const uint32_t w0 = pack_bf16(__uint_as_float(o[c8 * 8]) * inv, __uint_as_float(o[c8 * 8 + 1]) * inv);
-        const uint32_t w1 = pack_bf16(__uint_as_float(o[c8 * 8 + 2]) * inv, __uint_as_float(o[c8 * 8 + 3]) * inv);
-        const uint32_t w2 = pack_bf16(__uint_as_float(o[c8 * 8 + 4]) * inv, __uint_as_float(o[c8 * 8 + 5]) * inv);
-        const uint32_t w3 = pack_bf16(__uint_as_float(o[c8 * 8 + 6]) * inv, __uint_as_float(o[c8 * 8 + 7]) * inv);
+        const uint32_t w0 = pack_bf16(r[c8 * 8], r[c8 * 8 + 1]);
+        const uint32_t w1 = pack_bf16(r[c8 * 8 + 2], r[c8 * 8 + 3]);
+        const uint32_t w2 = pack_bf16(r[c8 * 8 + 4], r[c8 * 8 + 5]);
+        const uint32_t w3 = pack_bf16(r[c8 * 8 + 6], r[c8 * 8 + 7]);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(o_row + uint32_t(((part * 4 + c8) ^ (row & 7)) << 4)), "r"(w0), "r"(w1),
                      "r"(w2), "r"(w3) : "memory");
       }
@@ -479,23 +555,47 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
     return R2_UNSUPPORTED;
   }
   if (n_tiles > 65535) return R2_UNSUPPORTED;
-  size_t smem = 1024 + Q_BYTES + 2 * STAGES * size_t(KV_BYTES) + 16 * 8 + 16;
   static bool configured = false;
   static int n_sms = 0;
+  const size_t smem_one = 1024 + Q_BYTES + 2 * STAGES * size_t(KV_BYTES) + 16 * 8 + 16, smem_two = smem_one + JOIN_BYTES;
   if (!configured) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return R2_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
-    if (e != cudaSuccess) return int(e);
-    e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_two));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  // Two CTAs share an SM's special-function units and each runs slower for it. With many tiles that is
-  // the better trade (one CTA's softmax under the other's products); with fewer than two per SM the step
-  // waits for the CTA with the most keys, which then should have an SM to itself: the CTA asks for more
-  // than half an SM's shared memory, and the ones that do not fit at first start as the short ones end.
-  if (long(n_tiles) * n_heads <= 2L * n_sms) smem = 120 * 1024;
-  r2_launch(prefill_tc_kernel, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
+  // How many CTAs have rows: about one per 128 rows, and at least one per entry (`n_tiles` is only an upper
+  // bound). With fewer than one per SM (a single prompt or a portion of one) the step waits for the CTA with
+  // the most keys while SMs stand idle: pairs of CTAs then share the keys of each 128 rows (1 x 1,024 tokens
+  // x 12 heads: 11.9 us against 14.4; at 2 x 1,024, with twice the CTAs, 16.6 against 14.9, so not there).
+  const long busy = long(n_rows / BM > n_entries ? n_rows / BM : n_entries) * n_heads;
+  if (busy <= n_sms) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(n_heads, n_tiles, 2);
+    config.blockDim = dim3(THREADS);
+    config.dynamicSmemBytes = smem_two;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 2;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = (g_r2_pdl && !t_r2_plain_order) ? 2 : 1;
+    cudaLaunchKernelEx(&config, prefill_tc_kernel<2>, mq, mk, mv, p);  // a failure shows in launch_status()
+  } else {
+    // Two CTAs share an SM's special-function units and each runs slower for it. With many CTAs that is the
+    // better trade (one CTA's softmax under the other's products); with fewer than two per SM the step waits
+    // for the CTA with the most keys, which then should have an SM to itself: the CTA asks for more than half
+    // an SM's shared memory, and the ones that do not fit at first start as the short ones end.
+    const size_t smem = busy <= 2L * n_sms ? size_t(120) * 1024 : smem_one;
+    r2_launch(prefill_tc_kernel<1>, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
+  }
   return launch_status();
 }

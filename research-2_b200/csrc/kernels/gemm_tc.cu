@@ -97,7 +97,7 @@ struct GemmParams {
   bf16* kv_k;
   bf16* kv_v;
   long long kv_page_stride;
-  int kv_page_size, kv_page_shift, kv_n_pages, kv_col, kv_width, kv_head_dim;
+  int kv_page_size, kv_page_shift, kv_n_pages, kv_col, kv_width, kv_head_dim, kv_head_shift;
 };
 
 
@@ -200,11 +200,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"   // one statement: no use of the registers can come between the load and its wait
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      : "r"(taddr)
+      : "memory");
 }
 
 // LayerNorm of the token rows, written as the K-major, 128-byte-swizzled bfloat16 tiles that the
@@ -314,10 +315,11 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
 
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"   // one statement: no use of the registers can come between the load and its wait
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      : "r"(taddr)
+      : "memory");
 }
 
 __device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -336,7 +338,14 @@ __device__ __forceinline__ void tmem_load32_issue(uint32_t taddr, uint32_t (&r)[
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The wait for them. The loaded registers are operands of the wait (`tmem_tie` for a second set): to the compiler
+// a load is complete when its statement is, and without this tie it may place a use of the registers before the wait.
+__device__ __forceinline__ void tmem_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) : : "memory");
+}
+__device__ __forceinline__ void tmem_tie(uint32_t (&r)[32]) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) : : "memory");
+}
 
 constexpr int STAGING_ROW = 36;                       // words per staged row: 32 and four of padding (rows stay 16-byte aligned)
 constexpr int STAGING_WORDS = 32 * STAGING_ROW;       // per epilogue warp
@@ -396,6 +405,17 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
   if (p.out_is_bf16 && p.residual == nullptr) {
     bf16* out = reinterpret_cast<bf16*>(p.out);
     const bool vec_ok = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (col0 & 7) == 0;
+    // Where in a cache tensor this lane's row (row0 + lane) lies: elements from the tensor's start to the row's
+    // slot in kv head 0, or -1 for a row that is not stored. Asked for and worked out once per slab, ahead of the
+    // first group's accumulators; step (2) gets the eight rows it stores from their lanes by shuffles, so that
+    // nothing more than this is held while the accumulators fill the registers.
+    const bool scatters = p.kv_slots != nullptr && col0 + c_end > p.kv_col;
+    long long my_at = -1;
+    if (scatters && lane < rows) {
+      const int slot = p.kv_slots[row0 + lane];
+      const int page = slot >= 0 ? page_index(slot, p.kv_page_size, p.kv_page_shift) : p.kv_n_pages;
+      if (page < p.kv_n_pages) my_at = (long long)page * p.kv_page_stride + (long long)page_offset(slot, p.kv_page_size, p.kv_page_shift) * p.kv_head_dim;
+    }
     for (int c0 = c_begin; c0 < c_end; c0 += 64) {
       if (col0 + c0 >= p.b_total) break;
       {
@@ -405,7 +425,8 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
         if (have_acc) {
           tmem_load32_issue(lane_addr + uint32_t(c0), r0);
           if (two) tmem_load32_issue(lane_addr + uint32_t(c0 + 32), r1);
-          tmem_wait();
+          tmem_wait(r0);
+          if (two) tmem_tie(r1);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
@@ -430,27 +451,25 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
       // Step (2). Each lane decides for its own eight columns; the warp stays together.
       const int col = col0 + c0 + 8 * piece;                                   // this lane's eight columns
       const int n_cols = min(8, min(c_end - (c0 + 8 * piece), p.b_total - col));
+      long long slot_at[8];
+      if (scatters) {  // (the whole warp)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) slot_at[i] = __shfl_sync(0xffffffffu, my_at, 4 * i + sub);
+      }
       if (n_cols <= 0) {
         // nothing of this lane's lies inside the output
-      } else if (p.kv_slots != nullptr && col >= p.kv_col) {
+      } else if (scatters && col >= p.kv_col) {
         // keys or values of one kv head: each row's piece goes to the row's slot in the cache
         // ([page][kv head][offset][dim]); nothing of it goes to `out`
-        const int which = (col - p.kv_col) / p.kv_width, within = (col - p.kv_col) % p.kv_width;
-        const int head = within / p.kv_head_dim, dim = within % p.kv_head_dim;
+        const int rel = col - p.kv_col;
+        const int which = rel >= p.kv_width ? 1 : 0, within = rel - which * p.kv_width;   // keys, then values
+        const int head = p.kv_head_shift >= 0 ? within >> p.kv_head_shift : within / p.kv_head_dim;
+        const int dim = within - head * p.kv_head_dim;
         bf16* base = (which == 0 ? p.kv_k : p.kv_v) + size_t(head) * p.kv_page_size * p.kv_head_dim + dim;
-        int slot[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) slot[i] = 4 * i + sub < rows ? p.kv_slots[row0 + 4 * i + sub] : -1;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const uint4 w = ld_shared16(slab + uint32_t((4 * i + sub) * STAGING_ROW + 4 * piece) * 4u);
-          if (slot[i] >= 0) {
-            const int page = page_index(slot[i], p.kv_page_size, p.kv_page_shift);
-            if (page < p.kv_n_pages) {
-              *reinterpret_cast<uint4*>(base + size_t(page) * p.kv_page_stride +
-                                        size_t(page_offset(slot[i], p.kv_page_size, p.kv_page_shift)) * p.kv_head_dim) = w;
-            }
-          }
+          if (slot_at[i] >= 0) *reinterpret_cast<uint4*>(base + slot_at[i]) = w;
         }
       } else if (inside && vec_ok && n_cols == 8) {
         // the common case, free of per-element conditions
@@ -1556,6 +1575,7 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
     p.kv_col = kv->col;
     p.kv_width = kv->width;
     p.kv_head_dim = kv->head_dim;
+    p.kv_head_shift = (kv->head_dim & (kv->head_dim - 1)) == 0 ? page_shift_of(kv->head_dim) : -1;
   }
   p.a_total = pl.a_total;
   p.b_total = pl.b_total;

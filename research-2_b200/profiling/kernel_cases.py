@@ -60,6 +60,12 @@ def cases(rows: int = 8):
             (f"prefill: qkv product, {t:,} x {D:,} x {3 * Q:,}", lambda xt=xt: ops.linear(xt, wqkv, bqkv), 0, 2 * t * D * 3 * Q),
             (f"prefill: fc product with gelu, {t:,} x {D:,} x {F:,}", lambda xt=xt: ops.linear(xt, wfc, bf, act="gelu_new"), 0, 2 * t * D * F),
         ]
+    # the same q/k/v product with the keys and values going straight into the rows' cache slots (2 x 1,024 tokens)
+    kc2, vc2, _, stride2, pages2 = paged(2)
+    slots2 = torch.arange(PS, PS + 2048, dtype=torch.int32, device=dev)
+    scatter = ops.kv_scatter(slots2, kc2, vc2, stride2, PS, pages2, Q, Q, HD)
+    q_out = torch.empty(2048, 3 * Q, device=dev, dtype=torch.bfloat16)
+    out.append((f"prefill: qkv product with cache write, 2,048 x {D:,} x {3 * Q:,}", lambda: ops.linear(x, wqkv, bqkv, out=q_out, kv=scatter), 0, 2 * 2048 * D * 3 * Q))
     out += [
         (f"prefill: attention output product + residual, 2,048 x {Q:,} x {D:,}", lambda: ops.linear(x[:, :Q].contiguous() if Q != D else x, wproj, bd, residual=r2k), 0, 2 * 2048 * Q * D),
         (f"prefill: mlp output product + residual, 2,048 x {F:,} x {D:,}", lambda: ops.linear(h2k, wproj2, bd, residual=r2k), 0, 2 * 2048 * F * D),
