@@ -790,9 +790,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ---- epilogue: warps 2..5, each on the 32 accumulator lanes it may read ------------------
   bool acc_ok = true;
-  float bias_ahead = 0.f, res_ahead[16];  // feature-major epilogue: the lane's bias, and its residual for the first 16 tokens
+  float bias_ahead = 0.f, res_ahead[32];  // feature-major epilogue: the lane's bias, and its residual for the first 32 tokens
 #pragma unroll
-  for (int j = 0; j < 16; ++j) res_ahead[j] = 0.f;
+  for (int j = 0; j < 32; ++j) res_ahead[j] = 0.f;
   if (threadIdx.x == 64 && p.prefetch != nullptr) {
     // weights never change: this CTA's slice of the next product's weight goes to L2 right away
     const long long n_ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
@@ -835,7 +835,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.bias != nullptr) bias_ahead = p.bias[a];
         if (p.residual != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) res_ahead[j] = b0 + j < p.b_total ? p.residual[size_t(b0 + j) * p.ldr + a] : 0.f;
+          for (int j = 0; j < 32; ++j) res_ahead[j] = (j < p.bn && b0 + j < p.b_total) ? p.residual[size_t(b0 + j) * p.ldr + a] : 0.f;
         }
       }
     }
@@ -941,9 +941,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
           }
           if (p.residual != nullptr) {
-            if (c0 == 0) {
+            if (c0 == 0) {  // (asked for before the products ran: a chunk's residual read here costs it a round trip to L2)
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] += res_ahead[j];
+            } else if (c0 == 16) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += res_ahead[16 + j];
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
