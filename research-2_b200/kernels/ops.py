@@ -145,6 +145,7 @@ def build_all(head_dims=()) -> None:
     for the given head sizes (a model compiles its own head size at first use otherwise)."""
     for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling", "wait_selftest"):
         _lib(source)
+    kernel_library("sfu_probe")  # (profiling/sfu_probe.py: a measurement, no part of a step)
     for head_dim in head_dims:
         _lib_for_head_dim("attention_decode", head_dim)
         if head_dim <= 128:
