@@ -513,6 +513,49 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
             assert torch.allclose(got, want, atol=5e-2), f"far key {far} {choice}: max diff {(got - want).abs().max():.3f}"
 
 
+@pytest.mark.parametrize("entries,window", [([(0, 1024)], 0), ([(300, 700)], 0), ([(0, 1024)], 200), ([(77, 500), (0, 130)], 0)])
+def test_prefill_attention_in_clusters_of_two_finds_every_row_its_key(entries, window):
+    """With fewer CTAs than SMs the tcgen05 prefill kernel runs as clusters of two CTAs that take every other
+    64-key tile of the same 128 rows and are joined at the end. Every query row is pointed at one key of its own
+    (anywhere it may see: first tile, last tile, tiles of the first CTA and of the second, the tile before the
+    window's edge), so that its output must be that key's value: a tile that is dropped, taken twice or joined
+    with the wrong weight shows in the rows whose key lies there. Unwritten slots hold inf."""
+    heads, hd, page = 2, 64, 16
+    targets = []
+
+    def mutate(case):
+        g = torch.Generator().manual_seed(len(entries) + window)
+        for e, (start, rows) in enumerate(entries):
+            ctx = start + rows
+            directions = torch.randn(ctx, hd, generator=g)
+            directions /= directions.norm(dim=1, keepdim=True)
+            case.k_dense[e][:, :, :] = (directions * 6).to(torch.bfloat16)[:, None, :]
+            tgt = torch.empty(rows, dtype=torch.long)
+            for r in range(rows):
+                pos = start + r
+                lo = max(0, pos - window + 1) if window else 0
+                choice = r % 5   # the newest key, the oldest it may see, and three random ones
+                tgt[r] = pos if choice == 0 else lo if choice == 1 else int(torch.randint(lo, pos + 1, (1,), generator=g))
+            case.q[e][:, :, :] = (directions[tgt] * 6).to(torch.bfloat16)[:, None, :]
+            targets.append(tgt)
+
+    case = PagedCase(entries, heads, heads, hd, page, torch.bfloat16, seed=window + 3, garbage=float("inf"), mutate=mutate)
+    o = ops()
+    before = dict(o.kernel_uses())
+    got = case.run(1.0, window, q_start=case.q_start, n_tiles=case.n_tiles).float().cpu()
+    used = {k: v - before.get(k, 0) for k, v in o.kernel_uses().items() if v != before.get(k, 0)}
+    assert any("prefill_tc" in k for k in used), f"the tcgen05 prefill kernel did not run: {used}"
+    at = 0
+    for e, (start, rows) in enumerate(entries):
+        want = case.v_dense[e][targets[e]].float().reshape(rows, -1)     # scores: 36 at the key, about 36 * N(0, 1/8) elsewhere
+        block = got[at: at + rows]
+        bad = ((block - want).abs() > 0.06).any(dim=1).nonzero().flatten().tolist()
+        assert not bad, f"entry {e}: rows {bad[:8]} (keys {targets[e][bad[:8]].tolist()}) did not get their key's value"
+        at += rows
+    torch.testing.assert_close(got, case.plain(1.0, window), atol=3e-2, rtol=3e-2)
+    assert o.device_errors() == 0
+
+
 def test_window_edge():
     """With a window the key just outside must not count and the one just inside must."""
     dtype = torch.float32
