@@ -603,7 +603,7 @@ __device__ __forceinline__ void finish_tile_rows(const GemmParams& p, uint32_t l
 // per k) instead of K-major (rows of 64 k-elements, one row per MN index).
 // TRANSPOSED: the a side is the features and the b side the tokens.
 template <bool A_MN, bool B_MN, bool TRANSPOSED, bool FUSED_LN = false>
-__global__ void __launch_bounds__(THREADS, TRANSPOSED ? 1 : 2)  // token-major tiles run two CTAs to an SM
+__global__ void __launch_bounds__(THREADS, (TRANSPOSED && !FUSED_LN) ? 1 : 2)  // token-major tiles run two CTAs to an SM, and so does the form with the norm inside (the logits' 393 CTAs)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
