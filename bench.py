@@ -411,6 +411,39 @@ def resident_phases(model, batch: int) -> dict:
         ops.set_resident_decode_rows(before)
 
 
+def logits_ctas(model, batch: int) -> dict:
+    """How the CTAs of a decode step's last product (the logits) share the GPU: every CTA's own times
+    (`ops.gemm_cta_stamps`), in microseconds from the first CTA's start."""
+    import numpy as np
+    import torch
+    from research_2_b200.kernels import ops
+
+    stamps = torch.zeros(2048, 6, dtype=torch.int64, device="cuda:0")
+    ops.gemm_cta_stamps(stamps)
+    try:
+        loop = DecodeLoop(model, batch, 40)   # (the graph is captured with the buffer in the kernels' arguments)
+        loop.run(6)
+        torch.cuda.synchronize()
+        n = min(ops.gemm_cta_stamps(None), stamps.shape[0])
+    finally:
+        ops.gemm_cta_stamps(None)
+    t = stamps[:n].cpu().numpy().astype(np.int64)
+    t = (t - t[:, 0].min()) / 1e3
+    names = ["start", "before the wait", "after the wait", "tokens normalised", "products complete", "end"]
+    starts = np.sort(t[:, 0])
+    waves, at = [], 0
+    while at < n:   # CTAs that start within 2 us of one another
+        upto = int(np.searchsorted(starts, starts[at] + 2.0, side="right"))
+        waves.append({"ctas": upto - at, "from_us": round(float(starts[at]), 2)})
+        at = upto
+    seg = np.diff(t, axis=1)
+    return {"rows": batch, "ctas": n, "waves": waves,
+            "median_us": {name: round(float(np.median(t[:, i])), 2) for i, name in enumerate(names)},
+            "segments_median_us": {name: round(float(v), 2) for name, v in zip(["set-up", "wait", "norm", "products", "epilogue"], np.median(seg, axis=0))},
+            "cta_life_median_us": round(float(np.median(t[:, 5] - t[:, 0])), 2),
+            "kernel_us": round(float(t[:, 5].max()), 2), "after_the_wait_us": round(float(t[:, 5].max() - np.median(t[:, 2])), 2)}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -422,6 +455,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has, if memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip prefill, e2e and the batch 1 / 64 points")
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
+    ap.add_argument("--logits-ctas", action="store_true", help="print when each CTA of a decode step's logits product starts and ends (its waves), and stop")
     ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -460,6 +494,9 @@ def main() -> int:
         return 0
     if args.prefill:
         print(json.dumps(prefill_point(model, cfg, pk)))
+        return 0
+    if args.logits_ctas:
+        print(json.dumps(logits_ctas(model, args.batch)))
         return 0
     sampler = ClockSampler()
     sampler.start()

@@ -98,7 +98,23 @@ struct GemmParams {
   bf16* kv_v;
   long long kv_page_stride;
   int kv_page_size, kv_page_shift, kv_n_pages, kv_col, kv_width, kv_head_dim, kv_head_shift;
+  // Profiling hook, normally null: six times of the nanosecond clock per CTA of the single-CTA forms (its start,
+  // before and after the wait on the kernel before, tokens ready (the form with the norm inside), products
+  // complete, end), [CTA][6], for the first `cta_stamps_cap` CTAs: shows how many CTAs an SM really holds.
+  long long* cta_stamps;
+  int cta_stamps_cap;
 };
+
+__device__ __forceinline__ void cta_stamp(const GemmParams& p, int which) {
+  if (p.cta_stamps != nullptr && threadIdx.x == 64) {
+    const int cta = int(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+    if (cta < p.cta_stamps_cap) {
+      long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      p.cta_stamps[cta * 6 + which] = now;
+    }
+  }
+}
 
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -625,6 +641,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   float* reduce = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  cta_stamp(p, 0);
   const int a0 = blockIdx.x * BM, b0 = blockIdx.y * p.bn;
   uint32_t rank = 0;  // this CTA's place in its cluster = its slice of K
   if (p.splits > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -815,12 +832,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (r < p.b_total) src_first[u] = p.ln_rows != nullptr ? p.ln_rows[r] : r;
       }
     }
+    cta_stamp(p, 1);
     pdl_wait();  // the epilogue reads the residual stream and writes the output
+    cta_stamp(p, 2);
     if constexpr (fused_ln) {
       build_normed_tokens(p, b_tiles, b_stride, kb_begin, n_kb, warp & 3, lane, gam, bet, src_first);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor core
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(tokens_ready)) : "memory");
+      cta_stamp(p, 3);
     }
     const int q = warp & 3;  // tensor-memory lanes [32q, 32q + 32) belong to warps with id % 4 == q
     if constexpr (!TRANSPOSED) {
@@ -840,6 +860,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
     bool ok = n_kb <= 0 || mbar_wait(acc_ready, 0);
+    cta_stamp(p, 4);
     if (!ok) atomicMax(p.error_flag, R2_ERR_TIMEOUT_ACC);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
@@ -972,6 +993,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
+  cta_stamp(p, 5);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   // A CTA whose tile is still being copied out of its shared memory must not leave: the leader
@@ -1502,9 +1524,20 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   return launch_status();
 }
 
+long long* g_cta_stamps = nullptr;  // (r2_gemm_tc_set_cta_stamps)
+int g_cta_stamps_cap = 0, g_last_grid = 0;
+
 int g_pair_form = 1;  // 0: never, 1: where it is the faster form, 2: wherever it can run (r2_gemm_tc_set_pair; tests compare the forms)
 
 }  // namespace
+
+// Profiling: launches from now on leave six times per CTA in `buffer` ([cap][6] int64 on the device; null: off).
+// Returns the number of CTAs of the last launch of a single-CTA form.
+extern "C" int r2_gemm_tc_set_cta_stamps(long long* buffer, int cap) {
+  g_cta_stamps = buffer;
+  g_cta_stamps_cap = buffer != nullptr ? cap : 0;
+  return g_last_grid;
+}
 
 extern "C" int r2_gemm_tc_set_pair(int mode) {
   int before = g_pair_form;
@@ -1580,6 +1613,8 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
     p.kv_head_dim = kv->head_dim;
     p.kv_head_shift = (kv->head_dim & (kv->head_dim - 1)) == 0 ? page_shift_of(kv->head_dim) : -1;
   }
+  p.cta_stamps = g_cta_stamps;
+  p.cta_stamps_cap = g_cta_stamps_cap;
   p.a_total = pl.a_total;
   p.b_total = pl.b_total;
   p.k_total = k;
@@ -1625,6 +1660,7 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
     }
   }
 
+  g_last_grid = int(grid.x * grid.y * grid.z);
   CUtensorMap ma, mb;
   bool ok;
   if (!pl.swapped) {

@@ -269,6 +269,19 @@ def use_pair_gemm(mode):
     return names[_lib("gemm_tc").r2_gemm_tc_set_pair(code)]
 
 
+def gemm_cta_stamps(buffer: torch.Tensor | None) -> int:
+    """Profiling: the tensor-core products launched (or captured into a graph) from now on leave six times of
+    the nanosecond clock per CTA in `buffer` (int64 [n, 6] on the device: start, before and after the wait on the
+    kernel before, tokens normalised, products complete, end; single-CTA forms only); None switches it off.
+    Returns the number of CTAs of the last such launch."""
+    if buffer is None:
+        return int(_lib("gemm_tc").r2_gemm_tc_set_cta_stamps(None, 0))
+    _need(buffer, "buffer", torch.int64, 2)
+    if buffer.shape[1] != 6 or not buffer.is_contiguous():
+        raise KernelError("gemm_cta_stamps: the buffer must be a contiguous int64 [n, 6]")
+    return int(_lib("gemm_tc").r2_gemm_tc_set_cta_stamps(C.c_void_p(buffer.data_ptr()), buffer.shape[0]))
+
+
 if os.environ.get("R2_PAIR_GEMM", "1") == "0":
     use_pair_gemm(False)
 
