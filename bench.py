@@ -414,7 +414,6 @@ def resident_phases(model, batch: int) -> dict:
 def logits_ctas(model, batch: int) -> dict:
     """How the CTAs of a decode step's last product (the logits) share the GPU: every CTA's own times
     (`ops.gemm_cta_stamps`), in microseconds from the first CTA's start."""
-    import numpy as np
     import torch
     from research_2_b200.kernels import ops
 
@@ -427,21 +426,9 @@ def logits_ctas(model, batch: int) -> dict:
         n = min(ops.gemm_cta_stamps(None), stamps.shape[0])
     finally:
         ops.gemm_cta_stamps(None)
-    t = stamps[:n].cpu().numpy().astype(np.int64)
-    t = (t - t[:, 0].min()) / 1e3
-    names = ["start", "before the wait", "after the wait", "tokens normalised", "products complete", "end"]
-    starts = np.sort(t[:, 0])
-    waves, at = [], 0
-    while at < n:   # CTAs that start within 2 us of one another
-        upto = int(np.searchsorted(starts, starts[at] + 2.0, side="right"))
-        waves.append({"ctas": upto - at, "from_us": round(float(starts[at]), 2)})
-        at = upto
-    seg = np.diff(t, axis=1)
-    return {"rows": batch, "ctas": n, "waves": waves,
-            "median_us": {name: round(float(np.median(t[:, i])), 2) for i, name in enumerate(names)},
-            "segments_median_us": {name: round(float(v), 2) for name, v in zip(["set-up", "wait", "norm", "products", "epilogue"], np.median(seg, axis=0))},
-            "cta_life_median_us": round(float(np.median(t[:, 5] - t[:, 0])), 2),
-            "kernel_us": round(float(t[:, 5].max()), 2), "after_the_wait_us": round(float(t[:, 5].max() - np.median(t[:, 2])), 2)}
+    from research_2_b200.profiling.kernel_cases import summarise_cta_stamps
+
+    return {"rows": batch, **summarise_cta_stamps(stamps, n)}
 
 
 def main() -> int:

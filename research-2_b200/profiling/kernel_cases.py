@@ -173,6 +173,29 @@ def configure(width: int, inner: int, heads: int, head_dim: int, vocab: int, pag
     D, F, H, HD, V, PS = width, inner, heads, head_dim, vocab, page_size
 
 
+def summarise_cta_stamps(stamps: torch.Tensor, n: int) -> dict:
+    """Every CTA's six times (`ops.gemm_cta_stamps`) as waves (CTAs that start within 2 us of one another),
+    medians and the kernel's span, in microseconds from the first CTA's start."""
+    import numpy as np
+
+    t = stamps[:n].cpu().numpy().astype(np.int64)
+    t = (t - t[:, 0].min()) / 1e3
+    t[:, 3] = np.maximum(t[:, 3], t[:, 2])   # (forms without a norm inside leave this time unset)
+    names = ["start", "before the wait", "after the wait", "tokens normalised", "products complete", "end"]
+    starts = np.sort(t[:, 0])
+    waves, at = [], 0
+    while at < n:
+        upto = int(np.searchsorted(starts, starts[at] + 2.0, side="right"))
+        waves.append({"ctas": upto - at, "from_us": round(float(starts[at]), 2)})
+        at = upto
+    seg = np.diff(t, axis=1)
+    return {"ctas": n, "waves": waves,
+            "median_us": {name: round(float(np.median(t[:, i])), 2) for i, name in enumerate(names)},
+            "segments_median_us": {name: round(float(v), 2) for name, v in zip(["set-up", "wait", "norm", "products", "epilogue"], np.median(seg, axis=0))},
+            "cta_life_median_us": round(float(np.median(t[:, 5] - t[:, 0])), 2),
+            "kernel_us": round(float(t[:, 5].max()), 2), "after_the_wait_us": round(float(t[:, 5].max() - np.median(t[:, 2])), 2)}
+
+
 def main(argv):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--width", type=int, required=True)
@@ -185,6 +208,7 @@ def main(argv):
     ap.add_argument("--case", default="", help="keep the cases whose name contains this text")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--ctas", action="store_true", help="for a case that is one tensor-core product (single-CTA form): when each of its CTAs starts and ends")
     args = ap.parse_args(argv)
     configure(args.width, args.inner, args.heads, args.head_dim, args.vocab, args.page_size)
     for name, fn, n_bytes, flops in cases(args.rows):
@@ -192,6 +216,19 @@ def main(argv):
             continue
         if args.list:
             print(name)
+        elif args.ctas:
+            import json
+
+            stamps = torch.zeros(4096, 6, dtype=torch.int64, device=dev)
+            fn()
+            ops.gemm_cta_stamps(stamps)
+            try:
+                fn()
+                torch.cuda.synchronize()
+                n = min(ops.gemm_cta_stamps(None), stamps.shape[0])
+            finally:
+                ops.gemm_cta_stamps(None)
+            print(name, json.dumps(summarise_cta_stamps(stamps, n)))
         elif args.time:
             us = time_in_graph(fn)
             rate = f"{n_bytes / us / 1e3:7.0f} GB/s" if n_bytes else f"{flops / us / 1e6:7.0f} TFLOP/s"
